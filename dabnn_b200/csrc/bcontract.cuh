@@ -1,0 +1,397 @@
+// Binary contraction core shared by bgemm and the binary convolutions.
+//
+//   cnt[p][n] = sum over K bits of  X[p][k] XOR Wt[n][k]        (p: pixel rows, n: output channels)
+//
+// X rows and Wt rows are streamed K-chunk by K-chunk (16 uint64 words = 1024 bits per stage) into
+// shared memory with 8-byte cp.async copies (zero-filled outside the operand, which is exactly the
+// reference's "padding = zero word" rule) through a 3-stage pipeline.  Three engines consume the
+// same shared-memory tiles and give identical integers:
+//
+//   POPC  CUDA cores: xor + popc per 64-bit word.
+//   B1    mma.sync.m16n8k256 b1 AND-popc.  xor = popc(x) + popc(w) - 2*and; the row popcounts are
+//         accumulated from the shared-memory tiles while they are resident.
+//   IMMA  mma.sync.m16n8k32 u8: each 32-bit chunk of a row is expanded in registers to {0,1} bytes
+//         ((chunk >> t) & 0x01010101), so the int8 tensor-core path computes the same AND count.
+//         Both operands use the same bit -> k-slot permutation, which a contraction is blind to.
+//
+// On B200 the b1 MMA is not a native tensor-core instruction any more (it runs at about 0.4
+// Pbit-op/s, the int8 MMA at about 1.1 and CUDA-core popc at about 0.28), which is why IMMA is
+// the default engine.
+//
+// The accumulators are turned into counts, staged through shared memory and written by a
+// cooperative, fully coalesced epilogue that can also apply the per-channel affine, add the
+// shortcut and emit the sign bits of the result (the next layer's packed input).
+#pragma once
+#include "common.cuh"
+
+namespace dabnn {
+
+constexpr int KC_WORDS = 16;               // uint64 words of K per pipeline stage
+constexpr int PITCH32 = KC_WORDS * 2 + 4;  // row pitch in 32-bit units (144 B): 8 rows x 64-bit reads hit 16 distinct banks
+constexpr int NSTAGES = 3;
+
+enum { ENG_POPC = DABNN_ENGINE_POPC, ENG_B1 = DABNN_ENGINE_B1, ENG_IMMA = DABNN_ENGINE_IMMA };
+
+// ---- operand addressing ------------------------------------------------------------------------
+struct RowCtx {
+    long long base;  // row-major/col-major: element offset of the row; conv: pixel index of image start
+    int iy0, ix0;    // conv: top-left input coordinate of the receptive field
+    int valid;
+};
+
+// rows contiguous: element (row, word) at p[row*ld + word]
+struct RowMajorOperand {
+    const uint64_t* p;
+    long long ld;
+    int rows, kwords;
+    __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row * ld, 0, 0, row < rows}; }
+    __device__ const uint64_t* addr(const RowCtx& r, int word) const {
+        return (r.valid && word < kwords) ? p + r.base + word : nullptr;
+    }
+};
+// the reference bgemm's `a`: element (row i, word h) at p[h*ld + i]
+struct ColMajorOperand {
+    const uint64_t* p;
+    long long ld;
+    int rows, kwords;
+    __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row, 0, 0, row < rows}; }
+    __device__ const uint64_t* addr(const RowCtx& r, int word) const {
+        return (r.valid && word < kwords) ? p + (long long)word * ld + r.base : nullptr;
+    }
+};
+// implicit im2col over packed NHWC bits: row = output pixel, word = (ky*kw + kx)*Cw + cw
+struct ConvOperand {
+    const uint64_t* p;
+    int n, H, W, Cw, OH, OW, kh, kw, pad_h, pad_w, stride_h, stride_w;
+    int rows, kwords;
+    __device__ RowCtx make_row(int row) const {
+        RowCtx r;
+        r.valid = row < rows;
+        const int img = row / (OH * OW), rem = row - img * (OH * OW);
+        const int oy = rem / OW, ox = rem - oy * OW;
+        r.base = (long long)img * H * W;
+        r.iy0 = oy * stride_h - pad_h;
+        r.ix0 = ox * stride_w - pad_w;
+        return r;
+    }
+    __device__ const uint64_t* addr(const RowCtx& r, int word) const {
+        if (!r.valid || word >= kwords) return nullptr;
+        const int tap = word / Cw, cw = word - tap * Cw;
+        const int ky = tap / kw, kx = tap - ky * kw;
+        const int y = r.iy0 + ky, x = r.ix0 + kx;
+        if (y < 0 || y >= H || x < 0 || x >= W) return nullptr;
+        return p + (r.base + (long long)y * W + x) * Cw + cw;
+    }
+};
+
+// ---- epilogue ------------------------------------------------------------------------------------
+struct EpilogueParams {
+    float* out;            // fp32 [rows][ld_out] or nullptr
+    long long ld_out;
+    int accumulate;        // 1: out += cnt (bgemm), 0: out = value
+    const float* a;        // per-channel affine (nullptr: none): v = a[n]*cnt + b[n]
+    const float* b;
+    const float* shortcut; // fp32 [rows][ld_sc] added after the affine, or nullptr
+    long long ld_sc;
+    uint64_t* bits;        // sign bits of the final value, [rows][ld_bits words], or nullptr
+    long long ld_bits;
+};
+
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void mma_b1_and(int* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k256.row.col.s32.b1.b1.s32.and.popc {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8(int* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int WM, int WN>
+struct TileCfg {
+    static constexpr int TM = WM * 64, TN = WN * 64, NT = WM * WN * 32;
+    static constexpr int STAGE_U32 = (TM + TN) * PITCH32;
+    static constexpr int CPITCH = TN + 4;  // staged count tile pitch (ints)
+    static constexpr size_t PIPE_BYTES = (size_t)NSTAGES * STAGE_U32 * 4;
+    static constexpr size_t CTILE_BYTES = (size_t)TM * CPITCH * 4;
+    static constexpr size_t SMEM_BYTES = (PIPE_BYTES > CTILE_BYTES ? PIPE_BYTES : CTILE_BYTES) +
+                                         (size_t)(TM + TN) * (sizeof(RowCtx) + sizeof(int));
+};
+
+// One CTA computes a TM x TN tile of counts.  grid = (ceil(M/TM), ceil(N/TN)).
+template <int ENGINE, int WM, int WN, class XOp, class WOp>
+__global__ void __launch_bounds__(WM* WN * 32)
+    bcontract_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
+                     const int kwords) {
+    using Cfg = TileCfg<WM, WN>;
+    constexpr int TM = Cfg::TM, TN = Cfg::TN, NT = Cfg::NT, ROWS = TM + TN;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint32_t* pipe = reinterpret_cast<uint32_t*>(smem_raw);
+    constexpr size_t MAIN_BYTES = Cfg::PIPE_BYTES > Cfg::CTILE_BYTES ? Cfg::PIPE_BYTES : Cfg::CTILE_BYTES;
+    RowCtx* rowctx = reinterpret_cast<RowCtx*>(smem_raw + MAIN_BYTES);
+    int* rowpop = reinterpret_cast<int*>(rowctx + ROWS);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
+
+    for (int r = tid; r < ROWS; r += NT)
+        rowctx[r] = r < TM ? xop.make_row(m0 + r) : wop.make_row(n0 + (r - TM));
+    __syncthreads();
+
+    const int nchunks = (kwords + KC_WORDS - 1) / KC_WORDS;
+    auto issue_chunk = [&](int chunk) {
+        if (chunk < nchunks) {
+            uint32_t* st = pipe + (chunk % NSTAGES) * Cfg::STAGE_U32;
+            const uint32_t st_addr = smem_u32(st);
+            const int w0 = chunk * KC_WORDS;
+#pragma unroll 4
+            for (int e = tid; e < ROWS * KC_WORDS; e += NT) {
+                const int r = e / KC_WORDS, wd = e % KC_WORDS;
+                const uint64_t* src = r < TM ? xop.addr(rowctx[r], w0 + wd) : wop.addr(rowctx[r], w0 + wd);
+                cp_async8(st_addr + (r * PITCH32 + wd * 2) * 4, src ? (const void*)src : (const void*)xop.p,
+                          src ? 8 : 0);
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < NSTAGES - 1; s++) issue_chunk(s);
+
+    // accumulators
+    constexpr bool MMA = ENGINE != ENG_POPC;
+    constexpr int PR = 16 / WN, PC = 8 * WN;  // POPC engine: rows / cols per thread
+    int acc[128];  // MMA engines: [(m-tile*8 + n-tile)*4 + frag]; POPC engine: [row*PC + col]
+#pragma unroll
+    for (int i = 0; i < 128; i++) acc[i] = 0;
+    constexpr int POPROWS = (ROWS + NT - 1) / NT;
+    int mypop[POPROWS];
+#pragma unroll
+    for (int i = 0; i < POPROWS; i++) mypop[i] = 0;
+
+    const int g = lane >> 2, tig = lane & 3;
+    const int wm = warp / WN, wn = warp % WN;
+    const int ty = tid >> 3, tx = tid & 7;  // POPC engine thread grid: (NT/8) x 8
+
+    for (int chunk = 0; chunk < nchunks; chunk++) {
+        cp_async_wait<NSTAGES - 2>();
+        __syncthreads();
+        issue_chunk(chunk + NSTAGES - 1);
+        const uint32_t* st = pipe + (chunk % NSTAGES) * Cfg::STAGE_U32;
+        const uint32_t* Xs = st;
+        const uint32_t* Ws = st + TM * PITCH32;
+        const int words = min(KC_WORDS, kwords - chunk * KC_WORDS);
+
+        if (MMA) {  // row popcounts of both operands for the AND engines
+#pragma unroll
+            for (int i = 0; i < POPROWS; i++) {
+                const int r = tid + i * NT;
+                if (r < ROWS) {
+                    const uint4* rp = reinterpret_cast<const uint4*>(st + r * PITCH32);
+                    int s = 0;
+#pragma unroll
+                    for (int q = 0; q < KC_WORDS / 2; q++) {
+                        const uint4 v = rp[q];
+                        s += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
+                    }
+                    mypop[i] += s;
+                }
+            }
+        }
+
+        if (ENGINE == ENG_IMMA) {
+            const uint32_t M1 = 0x01010101u;
+            for (int wd = 0; wd < words; wd++) {
+                uint2 xa[4][2], wb[8];
+#pragma unroll
+                for (int mt = 0; mt < 4; mt++) {
+                    const int r = wm * 64 + mt * 16 + g;
+                    xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + wd * 2);
+                    xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + wd * 2);
+                }
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++)
+                    wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + wd * 2);
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    uint32_t af[4][4], bf[8][2];
+#pragma unroll
+                    for (int mt = 0; mt < 4; mt++) {
+                        const uint32_t c0 = (half ? xa[mt][0].y : xa[mt][0].x) >> tig;
+                        const uint32_t c1 = (half ? xa[mt][1].y : xa[mt][1].x) >> tig;
+                        af[mt][0] = c0 & M1;
+                        af[mt][1] = c1 & M1;
+                        af[mt][2] = (c0 >> 4) & M1;
+                        af[mt][3] = (c1 >> 4) & M1;
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < 8; nt++) {
+                        const uint32_t c = (half ? wb[nt].y : wb[nt].x) >> tig;
+                        bf[nt][0] = c & M1;
+                        bf[nt][1] = (c >> 4) & M1;
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+                        for (int nt = 0; nt < 8; nt++)
+                            mma_u8(&acc[(mt * 8 + nt) * 4], af[mt][0], af[mt][1], af[mt][2], af[mt][3], bf[nt][0], bf[nt][1]);
+                }
+            }
+        } else if (ENGINE == ENG_B1) {
+            const int steps = (words + 3) / 4;  // 4 words = 256 bits per MMA; the tail words are zero
+            for (int s = 0; s < steps; s++) {
+                uint2 xa[4][2], wb[8];
+#pragma unroll
+                for (int mt = 0; mt < 4; mt++) {
+                    const int r = wm * 64 + mt * 16 + g;
+                    xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + (s * 4 + tig) * 2);
+                    xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + (s * 4 + tig) * 2);
+                }
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++)
+                    wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + (s * 4 + tig) * 2);
+#pragma unroll
+                for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+                    for (int nt = 0; nt < 8; nt++)
+                        mma_b1_and(&acc[(mt * 8 + nt) * 4], xa[mt][0].x, xa[mt][1].x, xa[mt][0].y, xa[mt][1].y, wb[nt].x,
+                                   wb[nt].y);
+            }
+        } else {
+            for (int wd = 0; wd < words; wd++) {
+                unsigned long long xr[PR], wc[PC];
+#pragma unroll
+                for (int i = 0; i < PR; i++)
+                    xr[i] = *reinterpret_cast<const unsigned long long*>(Xs + (i * (NT / 8) + ty) * PITCH32 + wd * 2);
+#pragma unroll
+                for (int j = 0; j < PC; j++)
+                    wc[j] = *reinterpret_cast<const unsigned long long*>(Ws + (j * 8 + tx) * PITCH32 + wd * 2);
+#pragma unroll
+                for (int i = 0; i < PR; i++)
+#pragma unroll
+                    for (int j = 0; j < PC; j++) acc[i * PC + j] += __popcll(xr[i] ^ wc[j]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every thread is done with the pipeline buffers: reuse them for the count tile
+
+    if (MMA) {
+#pragma unroll
+        for (int i = 0; i < POPROWS; i++) {
+            const int r = tid + i * NT;
+            if (r < ROWS) rowpop[r] = mypop[i];
+        }
+        __syncthreads();
+    }
+    int* ct = reinterpret_cast<int*>(smem_raw);
+    if (MMA) {
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++) {
+            const int r = wm * 64 + mt * 16 + g;
+            const int px0 = rowpop[r], px1 = rowpop[r + 8];
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const int c = wn * 64 + nt * 8 + tig * 2;
+                const int pw0 = rowpop[TM + c], pw1 = rowpop[TM + c + 1];
+                int2 v0, v1;
+                const int* d = &acc[(mt * 8 + nt) * 4];
+                v0.x = px0 + pw0 - 2 * d[0];
+                v0.y = px0 + pw1 - 2 * d[1];
+                v1.x = px1 + pw0 - 2 * d[2];
+                v1.y = px1 + pw1 - 2 * d[3];
+                *reinterpret_cast<int2*>(ct + r * Cfg::CPITCH + c) = v0;
+                *reinterpret_cast<int2*>(ct + (r + 8) * Cfg::CPITCH + c) = v1;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < PR; i++)
+#pragma unroll
+            for (int j = 0; j < PC; j++) ct[(i * (NT / 8) + ty) * Cfg::CPITCH + j * 8 + tx] = acc[i * PC + j];
+    }
+    __syncthreads();
+
+    // cooperative epilogue: each thread owns 4 consecutive channels of one row per step
+    constexpr int C4 = TN / 4;
+    const bool vec_ok = (N % 4 == 0) && (!ep.out || (ep.ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0)) &&
+                        (!ep.shortcut || (ep.ld_sc % 4 == 0 && (reinterpret_cast<uintptr_t>(ep.shortcut) & 15) == 0));
+    for (int it = tid; it < TM * C4; it += NT) {
+        const int r = it / C4, c = (it % C4) * 4;
+        const int row = m0 + r, col = n0 + c;
+        const int4 cnt = *reinterpret_cast<const int4*>(ct + r * Cfg::CPITCH + c);
+        float v[4] = {(float)cnt.x, (float)cnt.y, (float)cnt.z, (float)cnt.w};
+        const bool row_ok = row < M;
+        unsigned nib = 0;
+        if (row_ok && col < N) {
+            const int nvalid = min(4, N - col);
+            if (ep.a) {
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                    if (q < nvalid) v[q] = __fadd_rn(__fmul_rn(ep.a[col + q], v[q]), ep.b[col + q]);
+            }
+            if (ep.shortcut) {
+                const float* sp = ep.shortcut + (long long)row * ep.ld_sc + col;
+                if (vec_ok) {
+                    const float4 s4 = *reinterpret_cast<const float4*>(sp);
+                    v[0] = __fadd_rn(v[0], s4.x); v[1] = __fadd_rn(v[1], s4.y);
+                    v[2] = __fadd_rn(v[2], s4.z); v[3] = __fadd_rn(v[3], s4.w);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        if (q < nvalid) v[q] = __fadd_rn(v[q], sp[q]);
+                }
+            }
+            if (ep.out) {
+                float* op = ep.out + (long long)row * ep.ld_out + col;
+                if (vec_ok) {
+                    float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                    if (ep.accumulate) {
+                        const float4 old = *reinterpret_cast<const float4*>(op);
+                        o.x = __fadd_rn(old.x, o.x); o.y = __fadd_rn(old.y, o.y);
+                        o.z = __fadd_rn(old.z, o.z); o.w = __fadd_rn(old.w, o.w);
+                    }
+                    *reinterpret_cast<float4*>(op) = o;
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        if (q < nvalid) op[q] = ep.accumulate ? __fadd_rn(op[q], v[q]) : v[q];
+                }
+            }
+            nib = (v[0] > 0.f ? 1u : 0u) | (v[1] > 0.f ? 2u : 0u) | (v[2] > 0.f ? 4u : 0u) | (v[3] > 0.f ? 8u : 0u);
+        }
+        if (ep.bits) {  // 16 consecutive lanes hold the 64 channels of one word (uniform branch)
+            const int sub = lane & 15;
+            unsigned lo = sub < 8 ? nib << (4 * sub) : 0u, hi = sub >= 8 ? nib << (4 * (sub - 8)) : 0u;
+#pragma unroll
+            for (int off = 1; off < 16; off <<= 1) {
+                lo |= __shfl_xor_sync(0xffffffffu, lo, off);
+                hi |= __shfl_xor_sync(0xffffffffu, hi, off);
+            }
+            if (sub == 0 && row_ok && col < N)
+                ep.bits[(long long)row * ep.ld_bits + (col >> 6)] = ((unsigned long long)hi << 32) | lo;
+        }
+    }
+}
+
+// Host-side launcher: picks the tile shape from N and dispatches on the engine.
+template <class XOp, class WOp>
+int launch_bcontract(int engine, const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N,
+                     int kwords, cudaStream_t stream);
+
+}  // namespace dabnn

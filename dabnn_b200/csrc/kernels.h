@@ -1,0 +1,31 @@
+// Internal (C++) declarations shared between the .cu files and the Net runtime.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace dabnn {
+
+// bconv + optional affine + optional shortcut + optional sign-bit output (see dabnn_bconv_block).
+int bconv_block_impl(const uint64_t* in_bits, const uint64_t* weight, size_t weight_words, const float* a,
+                     const float* b, const float* shortcut, float* out_f32, uint64_t* out_bits, int n, int h,
+                     int w, int cw, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                     int stride_w, int engine, cudaStream_t stream);
+
+// Elementwise chain on an fp32 NHWC tensor, in one pass:  v = x;  if (a) v = a[c]*v + b[c];
+// if (add) v += add;  if (relu) v = max(v, 0);  optional fp32 store and optional sign-bit store.
+int elementwise_chain(const float* x, const float* a, const float* b, const float* add, int relu,
+                      float* out_f32, uint64_t* out_bits, size_t pixels, int c, cudaStream_t stream);
+
+// Float convolution with an optional fused per-channel affine and relu applied to the result
+// (conv (+bias) -> a*v+b -> max(v,0)); used for the stem and the downsample shortcuts.
+int fconv_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b,
+               int relu, float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
+               int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream);
+
+// Max pooling that also emits the sign bits of its output (the first binary conv's input).
+int maxpool_impl(const float* in, float* out, uint64_t* out_bits, int n, int h, int w, int c, int kh, int kw,
+                 int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream);
+
+}  // namespace dabnn

@@ -1,0 +1,771 @@
+// Host runtime: the counterpart of the reference's bnn::Net (dabnn/net.h:22-66, dabnn/net.cpp).
+//
+// read_buf()  parses the .dab model, uploads the initializers, infers blob shapes
+//             (reference common/Shaper.cpp) and compiles the layer list into a fixed sequence of
+//             kernel launches ("plan") over one device arena.
+// run()       copies the input to the device when it is a host pointer and enqueues the plan on
+//             the net's stream.
+//
+// Two plans exist.  optimize = false is the literal layer-by-layer sequence of the reference with
+// every blob kept (any blob can be fetched afterwards, Affine/Add/Relu/PRelu alias their first
+// input like the reference, common/flatbuffers_helper.h:68-73) and the CUDA-core popc engine.
+// optimize = true fuses BinConv + Affine (+ Add) into one kernel that also emits the sign bits the
+// next BinConv consumes, fuses FpConv + Affine (+ Relu), lets pooling / elementwise producers emit
+// sign bits, and reuses arena memory between blobs whose lifetimes do not overlap.  Both plans run
+// the same arithmetic in the same order, so their outputs are bit-identical.
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "dab_reader.h"
+#include "kernels.h"
+
+namespace dabnn {
+
+namespace {
+
+struct TensorInfo {
+    bool is_bit = false;
+    std::vector<uint32_t> shape;
+    size_t count = 0;        // elements (floats or words)
+    void* dev = nullptr;     // device copy
+};
+
+struct Blob {                // one activation buffer (aliases share a Blob)
+    int h = 0, w = 0, c = 0; // per image
+    int def_op = -1, last_use = -1;
+    bool keep = false;       // must survive the run (network output / unfused plan)
+    bool need_f32 = true;    // some op reads or exposes the float values
+    bool need_bits = false;  // some op reads the sign bits
+    size_t f32_off = (size_t)-1, bits_off = (size_t)-1;
+    size_t per_image() const { return (size_t)h * w * c; }
+};
+
+enum class OpKind { FConv, BConvBlock, BinConvIm2col, Pack, Chain, PRelu, MaxPool, AvePool, Concat };
+
+struct Op {
+    OpKind kind;
+    std::string cls;  // reference layer class, for per-class timing
+    int in = -1, in2 = -1, out = -1;
+    const TensorInfo *w = nullptr, *bias = nullptr, *a = nullptr, *b = nullptr, *slope = nullptr;
+    int kh = 0, kw = 0, pad_h = 0, pad_w = 0, stride_h = 1, stride_w = 1;
+    int relu = 0;
+    bool write_f32 = true, write_bits = false;
+};
+
+struct Layer {
+    LayerType type;
+    std::string name, input, input2, weight, bias, a, b, slope, output;
+    std::vector<int32_t> pads, strides, dilations, kernel;
+};
+
+}  // namespace
+
+struct NetImpl {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool optimize = true, run_fconv = true, strict = true;
+    int max_batch = 1, engine = DABNN_ENGINE_AUTO;
+    bool loaded = false, profiling = false;
+
+    std::string input_name;
+    int in_h = 0, in_w = 0, in_c = 0;
+    std::map<std::string, TensorInfo> tensors;
+    std::vector<Layer> layers;
+    std::map<std::string, int> blob_of;  // blob name -> index in blobs (aliases map to the same index)
+    std::vector<Blob> blobs;
+    std::vector<Op> plan;
+    std::vector<std::string> outputs;
+
+    unsigned char* arena = nullptr;
+    size_t arena_bytes = 0, weights_bytes = 0;
+    unsigned char* weights = nullptr;
+    const float* cur_input = nullptr;  // device pointer of the current run's input
+    int cur_batch = 0;
+    int input_blob = -1;
+
+    std::vector<cudaEvent_t> events;
+    std::vector<std::string> time_names;
+    std::vector<float> time_ms;
+
+    ~NetImpl() {
+        for (auto e : events) cudaEventDestroy(e);
+        if (arena) cudaFree(arena);
+        if (weights) cudaFree(weights);
+        if (stream) cudaStreamDestroy(stream);
+    }
+
+    int parse(const uint8_t* buf, size_t len);
+    int build();
+    int run(const float* input, int batch, bool is_device);
+    float* f32(int blob) const {
+        if (blob == input_blob && cur_input) return const_cast<float*>(cur_input);
+        return reinterpret_cast<float*>(arena + blobs[blob].f32_off);
+    }
+    uint64_t* bits(int blob) const { return reinterpret_cast<uint64_t*>(arena + blobs[blob].bits_off); }
+};
+
+// -------------------------------------------------------------------------------------------------
+int NetImpl::parse(const uint8_t* buf, size_t len) {
+    DABNN_REQUIRE(buf && len >= 8, DABNN_ERR_FORMAT, "dab: buffer too small");
+    try {
+        FbBuffer fb(buf, len);
+        FbTable model(&fb, fb.read<uint32_t>(0));
+        const uint32_t version = model.scalar<uint32_t>(3, 0);
+        DABNN_REQUIRE(version == 2, DABNN_ERR_FORMAT,
+                      "The model version should be 2, got " + std::to_string(version) + " instead.");  // net.cpp:56
+        const auto inputs = model.tables(2);
+        DABNN_REQUIRE(!inputs.empty(), DABNN_ERR_FORMAT, "dab: model has no input");
+        {   // only the first input is used (net.cpp:59-70)
+            const auto shape = inputs[0].vec<uint32_t>(0);
+            DABNN_REQUIRE(shape.size() == 4, DABNN_ERR_FORMAT, "dab: input shape must be NHWC");
+            in_h = shape[1]; in_w = shape[2]; in_c = shape[3];
+            input_name = inputs[0].str(1);
+        }
+        // ---- initializers: one device slab, 256-byte aligned entries ----
+        struct Pending { TensorInfo* t; const void* src; size_t bytes, off; };
+        std::vector<Pending> pend;
+        size_t off = 0;
+        for (const auto& t : model.tables(1)) {
+            TensorInfo ti;
+            ti.is_bit = t.scalar<int8_t>(0, 0) == 1;
+            ti.shape = t.vec<uint32_t>(3);
+            const std::string name = t.str(4);
+            size_t count = 0;
+            const void* src = ti.is_bit ? (const void*)t.vec_view<uint64_t>(1, &count)
+                                        : (const void*)t.vec_view<float>(2, &count);
+            DABNN_REQUIRE(src && count > 0, DABNN_ERR_FORMAT, "dab: tensor " + name + " has no data");
+            ti.count = count;
+            auto& slot = tensors[name];
+            slot = ti;
+            const size_t bytes = count * (ti.is_bit ? 8 : 4);
+            pend.push_back({&slot, src, bytes, off});
+            off += (bytes + 255) / 256 * 256;
+        }
+        weights_bytes = off;
+        if (off) {
+            if (cudaMalloc(&weights, off) != cudaSuccess) return fail(DABNN_ERR_OOM, "cannot allocate weights on the device");
+            for (auto& p : pend) {
+                DABNN_CUDA_OK(cudaMemcpyAsync(weights + p.off, p.src, p.bytes, cudaMemcpyHostToDevice, stream));
+                p.t->dev = weights + p.off;
+            }
+            DABNN_CUDA_OK(cudaStreamSynchronize(stream));  // the caller may free the buffer after read
+        }
+        // ---- layers ----
+        for (const auto& l : model.tables(0)) {
+            Layer L;
+            L.type = (LayerType)l.scalar<int8_t>(0, 0);
+            L.name = l.str(14);
+            auto conv = [&](const FbTable& p) {
+                L.input = p.str(0); L.weight = p.str(1); L.bias = p.str(2);
+                L.pads = p.vec<int32_t>(3); L.strides = p.vec<int32_t>(4); L.dilations = p.vec<int32_t>(5);
+                L.output = p.str(6);
+            };
+            auto pool = [&](const FbTable& p) {
+                L.input = p.str(0); L.kernel = p.vec<int32_t>(1); L.pads = p.vec<int32_t>(2);
+                L.strides = p.vec<int32_t>(3); L.output = p.str(4);
+            };
+            FbTable p;
+            switch (L.type) {
+                case LayerType::FpConv2D: p = l.table(1); break;
+                case LayerType::BinConv2D: p = l.table(2); break;
+                case LayerType::AvePool: p = l.table(3); break;
+                case LayerType::MaxPool: p = l.table(4); break;
+                case LayerType::Relu: p = l.table(5); break;
+                case LayerType::Softmax: p = l.table(6); break;
+                case LayerType::FC: p = l.table(7); break;
+                case LayerType::Add: p = l.table(8); break;
+                case LayerType::Concat: p = l.table(9); break;
+                case LayerType::Affine: p = l.table(10); break;
+                case LayerType::Binarize: p = l.table(11); break;
+                case LayerType::Split: p = l.table(12); break;
+                case LayerType::Shuffle: p = l.table(13); break;
+                case LayerType::PRelu: p = l.table(15); break;
+                default: return fail(DABNN_ERR_UNSUPPORTED, "Not supported op " + std::to_string((int)L.type));
+            }
+            DABNN_REQUIRE(p.valid(), DABNN_ERR_FORMAT, "param != nullptr is not satisfied!");  // flatbuffers_helper.h:43
+            switch (L.type) {
+                case LayerType::FpConv2D: case LayerType::BinConv2D: conv(p); break;
+                case LayerType::AvePool: case LayerType::MaxPool: pool(p); break;
+                case LayerType::Relu: case LayerType::Softmax: case LayerType::Binarize: case LayerType::Shuffle:
+                    L.input = p.str(0); L.output = p.str(1); break;
+                case LayerType::FC: L.input = p.str(0); L.weight = p.str(1); L.bias = p.str(2); L.output = p.str(3); break;
+                case LayerType::Add: L.input = p.str(0); L.input2 = p.str(1); L.output = p.str(2); break;
+                case LayerType::Concat: {
+                    const auto ins = p.strings(0);
+                    DABNN_REQUIRE(ins.size() == 2, DABNN_ERR_UNSUPPORTED, "concat takes exactly two inputs");
+                    DABNN_REQUIRE(p.scalar<int32_t>(1, 0) == 3, DABNN_ERR_SHAPE, "axis == 3 is not satisfied!");  // net.cpp:235
+                    L.input = ins[0]; L.input2 = ins[1]; L.output = p.str(2);
+                    break;
+                }
+                case LayerType::Affine: L.input = p.str(0); L.a = p.str(1); L.b = p.str(2); L.output = p.str(3); break;
+                case LayerType::PRelu: L.input = p.str(0); L.slope = p.str(1); L.output = p.str(2); break;
+                default: L.input = p.str(0); break;
+            }
+            layers.push_back(std::move(L));
+        }
+    } catch (const DabError& e) {
+        return fail(DABNN_ERR_FORMAT, e.what());
+    }
+    return DABNN_OK;
+}
+
+// -------------------------------------------------------------------------------------------------
+int NetImpl::build() {
+    DABNN_REQUIRE(!(strict && !run_fconv), DABNN_ERR_STATE, "fconv must be run in strict mode");  // net.cpp:55
+    auto new_blob = [&](const std::string& name, int h, int w, int c) {
+        Blob b; b.h = h; b.w = w; b.c = c;
+        blobs.push_back(b);
+        blob_of[name] = (int)blobs.size() - 1;
+        return (int)blobs.size() - 1;
+    };
+    auto find_blob = [&](const std::string& name, int* idx) -> int {
+        auto it = blob_of.find(name);
+        if (it == blob_of.end()) return fail(DABNN_ERR_NOT_FOUND, "Key " + name + " not found.");  // StrKeyMap.h:59-65
+        *idx = it->second;
+        return DABNN_OK;
+    };
+    auto find_tensor = [&](const std::string& name, const TensorInfo** t) -> int {
+        auto it = tensors.find(name);
+        if (it == tensors.end()) return fail(DABNN_ERR_NOT_FOUND, "Key " + name + " not found.");
+        *t = &it->second;
+        return DABNN_OK;
+    };
+    input_blob = new_blob(input_name, in_h, in_w, in_c);
+
+    // ---- 1. literal layer-by-layer op list with reference aliasing -------------------------------
+    struct LOp { Op op; LayerType type; };
+    std::vector<LOp> lops;
+    for (const auto& L : layers) {
+        Op op{};
+        int rc;
+        auto sym2 = [&](const std::vector<int32_t>& v, const char* what, int* a0, int* a1) -> int {
+            // pads: 2 values or 4 symmetric ones; strides likewise (net.cpp:148-155)
+            DABNN_REQUIRE(v.size() == 2 || (v.size() == 4 && v[0] == v[2] && v[1] == v[3]), DABNN_ERR_SHAPE,
+                          std::string(what) + " must have 2 entries or 4 symmetric ones");
+            *a0 = v[0]; *a1 = v[1];
+            return DABNN_OK;
+        };
+        switch (L.type) {
+            case LayerType::FpConv2D:
+            case LayerType::BinConv2D: {
+                const bool bin = L.type == LayerType::BinConv2D;
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                if ((rc = find_tensor(L.weight, &op.w))) return rc;
+                DABNN_REQUIRE(op.w->shape.size() == 4 && op.w->is_bit == bin, DABNN_ERR_FORMAT,
+                              "conv weight " + L.weight + " has the wrong type or rank");
+                if (!L.bias.empty() && !bin)
+                    if ((rc = find_tensor(L.bias, &op.bias))) return rc;
+                if ((rc = sym2(L.pads, "pads", &op.pad_h, &op.pad_w))) return rc;
+                if ((rc = sym2(L.strides, "strides", &op.stride_h, &op.stride_w))) return rc;
+                DABNN_REQUIRE(op.stride_h > 0 && op.stride_w > 0 && op.pad_h >= 0 && op.pad_w >= 0, DABNN_ERR_SHAPE,
+                              "conv: bad pads/strides");
+                for (int d : L.dilations) DABNN_REQUIRE(d == 1, DABNN_ERR_UNSUPPORTED, "conv: dilation must be 1");
+                const Blob& ib = blobs[op.in];
+                const int cout = op.w->shape[0];
+                op.kh = op.w->shape[1]; op.kw = op.w->shape[2];
+                DABNN_REQUIRE((int)op.w->shape[3] == ib.c, DABNN_ERR_SHAPE, "conv: weight channels != input channels");
+                const int oh = conv_out_dim(ib.h, op.pad_h, 1, op.kh, op.stride_h);
+                const int ow = conv_out_dim(ib.w, op.pad_w, 1, op.kw, op.stride_w);
+                DABNN_REQUIRE(oh > 0 && ow > 0, DABNN_ERR_SHAPE, "conv: empty output");
+                op.out = blob_of.count(L.output) ? blob_of[L.output] : new_blob(L.output, oh, ow, cout);
+                if (bin) {
+                    DABNN_REQUIRE(op.w->count % cout == 0, DABNN_ERR_SHAPE, "weight_mat->total() % m == 0 is not satisfied!");
+                    const size_t per = op.w->count / cout;
+                    if (ib.c % 64 == 0) {
+                        // cin == 64: the reference requires pack_mat (c % 64 == 0) - satisfied
+                        DABNN_REQUIRE(per >= (size_t)op.kh * op.kw * (ib.c / 64), DABNN_ERR_SHAPE, "binconv: filter too short");
+                        op.kind = OpKind::BConvBlock;
+                    } else {
+                        DABNN_REQUIRE(per == ((size_t)op.kh * op.kw * ib.c + 127) / 128 * 2, DABNN_ERR_SHAPE,
+                                      "binconv: filters must be packed in 128-bit padded rows");
+                        op.kind = OpKind::BinConvIm2col;
+                    }
+                    op.cls = "Bin Conv";
+                } else {
+                    if (!run_fconv) continue;  // net.cpp:157
+                    DABNN_REQUIRE(op.w->count == (size_t)cout * op.kh * op.kw * ib.c, DABNN_ERR_FORMAT, "fconv: weight size");
+                    op.kind = OpKind::FConv;
+                    op.cls = "Float Conv";
+                }
+                break;
+            }
+            case LayerType::Affine: {
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                if ((rc = find_tensor(L.a, &op.a))) return rc;
+                if ((rc = find_tensor(L.b, &op.b))) return rc;
+                DABNN_REQUIRE((int)op.a->count == blobs[op.in].c && (int)op.b->count == blobs[op.in].c, DABNN_ERR_SHAPE,
+                              "affine: coefficient length != channels");
+                blob_of[L.output] = op.in;  // in place (ADD_INPLACE_LAYER)
+                op.out = op.in; op.kind = OpKind::Chain; op.cls = "Affine";
+                break;
+            }
+            case LayerType::Add: {
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                if ((rc = find_blob(L.input2, &op.in2))) return rc;
+                const Blob &x = blobs[op.in], &y = blobs[op.in2];
+                DABNN_REQUIRE(x.h == y.h && x.w == y.w && x.c == y.c, DABNN_ERR_SHAPE, "add: shapes differ");
+                blob_of[L.output] = op.in;
+                op.out = op.in; op.kind = OpKind::Chain; op.cls = "Add";
+                break;
+            }
+            case LayerType::Relu: {
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                blob_of[L.output] = op.in;
+                op.out = op.in; op.relu = 1; op.kind = OpKind::Chain; op.cls = "Relu";
+                break;
+            }
+            case LayerType::PRelu: {
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                if ((rc = find_tensor(L.slope, &op.slope))) return rc;
+                DABNN_REQUIRE(op.slope->count == 1 || (int)op.slope->count == blobs[op.in].c, DABNN_ERR_SHAPE,
+                              "slope must have size 1 or input.channels");  // PRelu.cpp:7-9
+                blob_of[L.output] = op.in;
+                op.out = op.in; op.kind = OpKind::PRelu; op.cls = "PRelu";
+                break;
+            }
+            case LayerType::MaxPool:
+            case LayerType::AvePool: {
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                DABNN_REQUIRE(L.kernel.size() == 2 && L.pads.size() >= 2 && L.strides.size() >= 2, DABNN_ERR_SHAPE,
+                              "pool: kernel_shape/pads/strides");
+                op.kh = L.kernel[0]; op.kw = L.kernel[1]; op.pad_h = L.pads[0]; op.pad_w = L.pads[1];
+                op.stride_h = L.strides[0]; op.stride_w = L.strides[1];
+                const Blob& ib = blobs[op.in];
+                DABNN_REQUIRE(op.kh > 0 && op.kw > 0 && op.stride_h > 0 && op.stride_w > 0, DABNN_ERR_UNSUPPORTED,
+                              "pool: global pooling must be given as an explicit kernel");
+                const int oh = (ib.h + 2 * op.pad_h - op.kh) / op.stride_h + 1, ow = (ib.w + 2 * op.pad_w - op.kw) / op.stride_w + 1;
+                DABNN_REQUIRE(oh > 0 && ow > 0, DABNN_ERR_SHAPE, "pool: empty output");
+                op.out = blob_of.count(L.output) ? blob_of[L.output] : new_blob(L.output, oh, ow, ib.c);
+                op.kind = L.type == LayerType::MaxPool ? OpKind::MaxPool : OpKind::AvePool;
+                op.cls = L.type == LayerType::MaxPool ? "MaxPool" : "AvePool";
+                break;
+            }
+            case LayerType::Concat: {
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                if ((rc = find_blob(L.input2, &op.in2))) return rc;
+                const Blob &x = blobs[op.in], &y = blobs[op.in2];
+                DABNN_REQUIRE(x.h == y.h && x.w == y.w, DABNN_ERR_SHAPE, "Wrong input for concat");
+                op.out = blob_of.count(L.output) ? blob_of[L.output] : new_blob(L.output, x.h, x.w, x.c + y.c);
+                op.kind = OpKind::Concat; op.cls = "Concat";
+                break;
+            }
+            case LayerType::FC: {  // extension: the reference runtime has no FC handler (net.cpp:263)
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                if ((rc = find_tensor(L.weight, &op.w))) return rc;
+                if (!L.bias.empty())
+                    if ((rc = find_tensor(L.bias, &op.bias))) return rc;
+                const Blob& ib = blobs[op.in];
+                DABNN_REQUIRE(!op.w->is_bit && op.w->shape.size() == 2 && op.w->shape[1] == ib.per_image(), DABNN_ERR_SHAPE,
+                              "fc: weight must be [units][input_size]");
+                op.kh = ib.h; op.kw = ib.w;  // a full-size "valid" convolution
+                op.out = blob_of.count(L.output) ? blob_of[L.output] : new_blob(L.output, 1, 1, op.w->shape[0]);
+                op.kind = OpKind::FConv; op.cls = "FC";
+                break;
+            }
+            case LayerType::Binarize: {  // extension: exposes the sign bits of a blob (Binarize.cpp:9)
+                if ((rc = find_blob(L.input, &op.in))) return rc;
+                DABNN_REQUIRE(blobs[op.in].c % 64 == 0, DABNN_ERR_SHAPE, "float_mat.c % 64 == 0 is not satisfied!");
+                blob_of[L.output] = op.in;
+                op.out = op.in; op.kind = OpKind::Pack; op.cls = "Binarize";
+                break;
+            }
+            default:
+                return fail(DABNN_ERR_UNSUPPORTED, std::string("Not supported op ") + layer_type_name(L.type));  // net.cpp:264
+        }
+        lops.push_back({op, L.type});
+    }
+
+    // network outputs: blobs that no op reads
+    {
+        std::vector<char> read(blobs.size(), 0);
+        for (const auto& lo : lops) {
+            const Op& o = lo.op;
+            if (o.kind == OpKind::Chain || o.kind == OpKind::PRelu || o.kind == OpKind::Pack) {
+                if (o.in2 >= 0) read[o.in2] = 1;
+            } else {
+                if (o.in >= 0) read[o.in] = 1;
+                if (o.in2 >= 0) read[o.in2] = 1;
+            }
+        }
+        for (const auto& kv : blob_of)
+            if (!read[kv.second] && kv.second != input_blob) blobs[kv.second].keep = true;
+        // report the last name given to each output blob (in-place layers rename blobs)
+        for (size_t i = 0; i < blobs.size(); i++) {
+            if (!blobs[i].keep) continue;
+            std::string last;
+            for (const auto& L : layers)
+                if (!L.output.empty() && blob_of.count(L.output) && blob_of[L.output] == (int)i) last = L.output;
+            if (!last.empty()) outputs.push_back(last);
+        }
+    }
+
+    // ---- 2. plan ------------------------------------------------------------------------------------
+    if (!optimize) {
+        for (auto& lo : lops) {
+            Op o = lo.op;
+            if (o.kind == OpKind::BConvBlock) {  // literal: pack_mat, then the convolution
+                Op pk{}; pk.kind = OpKind::Pack; pk.in = pk.out = o.in; pk.cls = "Bin Conv";
+                plan.push_back(pk);
+                blobs[o.in].need_bits = true;
+            }
+            if (o.kind == OpKind::Pack) blobs[o.in].need_bits = true;
+            plan.push_back(o);
+        }
+        for (auto& b : blobs) b.keep = true;
+    } else {
+        // which op index consumes each blob, to decide what can be fused
+        const int nl = (int)lops.size();
+        std::vector<char> used(nl, 0);
+        for (int i = 0; i < nl; i++) {
+            if (used[i]) continue;
+            Op o = lops[i].op;
+            used[i] = 1;
+            int j = i + 1;
+            auto next_is = [&](LayerType t) {
+                return j < nl && !used[j] && lops[j].type == t && lops[j].op.in == o.out &&
+                       (lops[j].op.kind == OpKind::Chain);
+            };
+            if (o.kind == OpKind::BConvBlock) {
+                if (next_is(LayerType::Affine)) { o.a = lops[j].op.a; o.b = lops[j].op.b; used[j++] = 1; }
+                if (next_is(LayerType::Add) && lops[j].op.in2 != o.out) { o.in2 = lops[j].op.in2; used[j++] = 1; }
+                o.cls = "Bin Conv block";
+            } else if (o.kind == OpKind::FConv && lops[i].type == LayerType::FpConv2D) {
+                if (next_is(LayerType::Affine)) { o.a = lops[j].op.a; o.b = lops[j].op.b; used[j++] = 1; }
+                if (next_is(LayerType::Relu)) { o.relu = 1; used[j++] = 1; }
+            } else if (o.kind == OpKind::Chain) {
+                // merge a run of in-place elementwise layers on the same blob, in reference order:
+                // affine -> add -> relu is the only order one pass can express
+                int stage = lops[i].type == LayerType::Affine ? 0 : lops[i].type == LayerType::Add ? 1 : 2;
+                while (j < nl && !used[j] && lops[j].op.kind == OpKind::Chain && lops[j].op.in == o.out) {
+                    const int st = lops[j].type == LayerType::Affine ? 0 : lops[j].type == LayerType::Add ? 1 : 2;
+                    if (st <= stage || (st == 1 && lops[j].op.in2 == o.out)) break;
+                    if (st == 0) { o.a = lops[j].op.a; o.b = lops[j].op.b; }
+                    if (st == 1) o.in2 = lops[j].op.in2;
+                    if (st == 2) o.relu = 1;
+                    stage = st;
+                    used[j++] = 1;
+                }
+                o.cls = "Elementwise";
+            }
+            plan.push_back(o);
+        }
+        // sign bits: every blob read by a BConvBlock needs bits; let its producer emit them
+        for (auto& o : plan)
+            if (o.kind == OpKind::BConvBlock) blobs[o.in].need_bits = true;
+        std::vector<Op> with_packs;
+        std::vector<char> bits_ready(blobs.size(), 0);
+        for (auto& o : plan) {
+            if (o.kind == OpKind::BConvBlock && !bits_ready[o.in]) {
+                Op pk{}; pk.kind = OpKind::Pack; pk.in = pk.out = o.in; pk.cls = "Binarize";
+                with_packs.push_back(pk);
+                bits_ready[o.in] = 1;
+            }
+            if (o.out >= 0 && o.kind != OpKind::Pack) {
+                bool emits = false;
+                if (blobs[o.out].need_bits && blobs[o.out].c % 64 == 0 &&
+                    (o.kind == OpKind::BConvBlock || o.kind == OpKind::Chain || o.kind == OpKind::MaxPool)) {
+                    // only the blob's last writer emits the bits: an in-place writer later in the
+                    // plan would change the values
+                    bool later_writer = false, seen = false;
+                    for (auto& q : plan) {
+                        if (&q == &o) { seen = true; continue; }
+                        if (seen && q.out == o.out && q.kind != OpKind::Pack) later_writer = true;
+                    }
+                    emits = !later_writer;
+                }
+                o.write_bits = emits;
+                bits_ready[o.out] = emits;
+            }
+            with_packs.push_back(o);
+        }
+        plan.swap(with_packs);
+    }
+
+    // ---- 3. lifetimes and arena layout ------------------------------------------------------------
+    for (int i = 0; i < (int)plan.size(); i++) {
+        const Op& o = plan[i];
+        auto touch = [&](int b) {
+            if (b < 0) return;
+            if (blobs[b].def_op < 0) blobs[b].def_op = i;
+            blobs[b].last_use = i;
+        };
+        touch(o.in); touch(o.in2); touch(o.out);
+    }
+    blobs[input_blob].def_op = 0;
+    if (blobs[input_blob].last_use < 0) blobs[input_blob].last_use = 0;
+    struct Item { int blob; bool is_bits; size_t bytes; int a, b; size_t off; };
+    std::vector<Item> items;
+    for (int i = 0; i < (int)blobs.size(); i++) {
+        const Blob& b = blobs[i];
+        if (b.def_op < 0) continue;
+        const int last = b.keep ? (int)plan.size() : b.last_use;
+        const size_t fbytes = ((size_t)max_batch * b.per_image() * 4 + 255) / 256 * 256;
+        items.push_back({i, false, fbytes, b.def_op, last, 0});
+        if (b.need_bits) {
+            const size_t bb = ((size_t)max_batch * b.h * b.w * (b.c / 64) * 8 + 255) / 256 * 256;
+            items.push_back({i, true, bb, b.def_op, last, 0});
+        }
+    }
+    // BinConvIm2col scratch: one shared region sized for the largest user
+    size_t scratch = 0;
+    for (const auto& o : plan)
+        if (o.kind == OpKind::BinConvIm2col) {
+            const Blob& ib = blobs[o.in];
+            scratch = std::max(scratch, dabnn_binconv_workspace_bytes(max_batch, ib.h, ib.w, ib.c, o.kh, o.kw, o.pad_h,
+                                                                      o.pad_w, o.stride_h, o.stride_w));
+        }
+    // greedy first-fit by decreasing size; lifetimes [a, b] inclusive
+    std::vector<int> order(items.size());
+    for (size_t i = 0; i < order.size(); i++) order[i] = (int)i;
+    std::sort(order.begin(), order.end(), [&](int x, int y) { return items[x].bytes > items[y].bytes; });
+    std::vector<int> placed;
+    size_t top = (scratch + 255) / 256 * 256;
+    for (int idx : order) {
+        Item& it = items[idx];
+        std::vector<std::pair<size_t, size_t>> busy;
+        for (int p : placed) {
+            const Item& q = items[p];
+            if (q.a <= it.b && it.a <= q.b) busy.push_back({q.off, q.off + q.bytes});
+        }
+        std::sort(busy.begin(), busy.end());
+        size_t off = (scratch + 255) / 256 * 256;
+        for (auto& iv : busy) {
+            if (off + it.bytes <= iv.first) break;
+            off = std::max(off, iv.second);
+        }
+        it.off = off;
+        top = std::max(top, off + it.bytes);
+        placed.push_back(idx);
+    }
+    for (const auto& it : items) (it.is_bits ? blobs[it.blob].bits_off : blobs[it.blob].f32_off) = it.off;
+    arena_bytes = top;
+    if (cudaMalloc(&arena, arena_bytes ? arena_bytes : 256) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(DABNN_ERR_OOM, "cannot allocate a " + std::to_string(arena_bytes) + " byte device arena");
+    }
+    if (profiling) {
+        events.resize(plan.size() + 1);
+        for (auto& e : events) DABNN_CUDA_OK(cudaEventCreate(&e));
+    }
+    loaded = true;
+    return DABNN_OK;
+}
+
+// -------------------------------------------------------------------------------------------------
+int NetImpl::run(const float* input, int batch, bool is_device) {
+    DABNN_REQUIRE(loaded, DABNN_ERR_STATE, "run: no model has been read");
+    DABNN_REQUIRE(input, DABNN_ERR_ARG, "run: null input");
+    DABNN_REQUIRE(batch >= 1 && batch <= max_batch, DABNN_ERR_ARG,
+                  "run: batch must be between 1 and the configured max_batch");
+    DABNN_CUDA_OK(cudaSetDevice(device));
+    cur_batch = batch;
+    const size_t in_bytes = (size_t)batch * in_h * in_w * in_c * sizeof(float);
+    if (is_device) {
+        cur_input = input;
+    } else {
+        cur_input = nullptr;
+        DABNN_CUDA_OK(cudaMemcpyAsync(f32(input_blob), input, in_bytes, cudaMemcpyHostToDevice, stream));
+    }
+    const int eng = optimize ? engine : DABNN_ENGINE_POPC;
+    int rc = DABNN_OK;
+    for (size_t i = 0; i < plan.size() && rc == DABNN_OK; i++) {
+        const Op& o = plan[i];
+        if (profiling && !events.empty()) cudaEventRecord(events[i], stream);
+        const Blob& ib = blobs[o.in];
+        const size_t pixels_in = (size_t)batch * ib.h * ib.w;
+        switch (o.kind) {
+            case OpKind::Pack:
+                rc = dabnn_pack_64(f32(o.in), bits(o.in), pixels_in * ib.c, stream);
+                break;
+            case OpKind::BConvBlock: {
+                const Blob& ob = blobs[o.out];
+                rc = bconv_block_impl(bits(o.in), static_cast<const uint64_t*>(o.w->dev), o.w->count,
+                                      o.a ? static_cast<const float*>(o.a->dev) : nullptr,
+                                      o.b ? static_cast<const float*>(o.b->dev) : nullptr,
+                                      o.in2 >= 0 ? f32(o.in2) : nullptr, f32(o.out),
+                                      o.write_bits ? bits(o.out) : nullptr, batch, ib.h, ib.w, ib.c / 64, ob.c, o.kh,
+                                      o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, eng, stream);
+                break;
+            }
+            case OpKind::BinConvIm2col: {
+                const Blob& ob = blobs[o.out];
+                rc = dabnn_binconv_forward(f32(o.in), static_cast<const uint64_t*>(o.w->dev), o.w->count, f32(o.out),
+                                           batch, ib.h, ib.w, ib.c, ob.c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h,
+                                           o.stride_w, arena, arena_bytes, eng, stream);
+                break;
+            }
+            case OpKind::FConv: {
+                const Blob& ob = blobs[o.out];
+                rc = fconv_impl(f32(o.in), static_cast<const float*>(o.w->dev),
+                                o.bias ? static_cast<const float*>(o.bias->dev) : nullptr,
+                                o.a ? static_cast<const float*>(o.a->dev) : nullptr,
+                                o.b ? static_cast<const float*>(o.b->dev) : nullptr, o.relu, f32(o.out), batch, ib.h,
+                                ib.w, ib.c, ob.c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, 1, 1, stream);
+                break;
+            }
+            case OpKind::Chain:
+                rc = elementwise_chain(f32(o.in), o.a ? static_cast<const float*>(o.a->dev) : nullptr,
+                                       o.b ? static_cast<const float*>(o.b->dev) : nullptr,
+                                       o.in2 >= 0 ? f32(o.in2) : nullptr, o.relu, f32(o.out),
+                                       o.write_bits ? bits(o.out) : nullptr, pixels_in, ib.c, stream);
+                break;
+            case OpKind::PRelu:
+                rc = dabnn_prelu(f32(o.in), static_cast<const float*>(o.slope->dev), (int)o.slope->count, pixels_in,
+                                 ib.c, stream);
+                break;
+            case OpKind::MaxPool:
+                rc = maxpool_impl(f32(o.in), f32(o.out), o.write_bits ? bits(o.out) : nullptr, batch, ib.h, ib.w, ib.c,
+                                  o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, stream);
+                break;
+            case OpKind::AvePool:
+                rc = dabnn_avepool(f32(o.in), f32(o.out), batch, ib.h, ib.w, ib.c, o.kh, o.kw, o.pad_h, o.pad_w,
+                                   o.stride_h, o.stride_w, stream);
+                break;
+            case OpKind::Concat:
+                rc = dabnn_concat(f32(o.in), ib.c, f32(o.in2), blobs[o.in2].c, f32(o.out), pixels_in, stream);
+                break;
+        }
+    }
+    if (profiling && !events.empty()) cudaEventRecord(events[plan.size()], stream);
+    return rc;
+}
+
+}  // namespace dabnn
+
+using namespace dabnn;
+struct dabnn_net {
+    NetImpl impl;
+};
+
+extern "C" int dabnn_net_create(dabnn_net** out) {
+    DABNN_REQUIRE(out, DABNN_ERR_ARG, "net_create: null pointer");
+    *out = nullptr;
+    int dev = 0;
+    DABNN_CUDA_OK(cudaGetDevice(&dev));
+    std::unique_ptr<dabnn_net> n(new dabnn_net());
+    n->impl.device = dev;
+    DABNN_CUDA_OK(cudaStreamCreateWithFlags(&n->impl.stream, cudaStreamNonBlocking));
+    *out = n.release();
+    return DABNN_OK;
+}
+extern "C" void dabnn_net_destroy(dabnn_net* net) { delete net; }
+
+extern "C" int dabnn_net_set_flags(dabnn_net* net, int optimize, int run_fconv, int strict) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    DABNN_REQUIRE(!net->impl.loaded, DABNN_ERR_STATE, "flags must be set before the model is read");
+    net->impl.optimize = optimize != 0; net->impl.run_fconv = run_fconv != 0; net->impl.strict = strict != 0;
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_configure(dabnn_net* net, int max_batch, int engine) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    DABNN_REQUIRE(!net->impl.loaded, DABNN_ERR_STATE, "configure must precede read");
+    DABNN_REQUIRE(max_batch >= 1, DABNN_ERR_ARG, "max_batch must be >= 1");
+    DABNN_REQUIRE(engine >= DABNN_ENGINE_AUTO && engine <= DABNN_ENGINE_IMMA, DABNN_ERR_ARG, "unknown engine");
+    net->impl.max_batch = max_batch; net->impl.engine = engine;
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_read_buf(dabnn_net* net, const void* buf, size_t len) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    DABNN_REQUIRE(!net->impl.loaded, DABNN_ERR_STATE, "a model has already been read into this net");
+    DABNN_CUDA_OK(cudaSetDevice(net->impl.device));
+    int rc = net->impl.parse(static_cast<const uint8_t*>(buf), len);
+    if (rc) return rc;
+    return net->impl.build();
+}
+extern "C" int dabnn_net_read_file(dabnn_net* net, const char* path) {
+    DABNN_REQUIRE(net && path, DABNN_ERR_ARG, "null argument");
+    const int fd = open(path, O_RDONLY);
+    if (fd == -1) return fail(DABNN_ERR_IO, "Open file error " + std::to_string(errno));  // net.cpp:35
+    struct stat st;
+    if (fstat(fd, &st) != 0) { close(fd); return fail(DABNN_ERR_IO, "fstat failed, errno = " + std::to_string(errno)); }
+    std::vector<uint8_t> data((size_t)st.st_size);
+    size_t got = 0;
+    while (got < data.size()) {
+        const ssize_t r = read(fd, data.data() + got, data.size() - got);
+        if (r <= 0) { close(fd); return fail(DABNN_ERR_IO, "read failed, errno = " + std::to_string(errno)); }
+        got += (size_t)r;
+    }
+    close(fd);
+    return dabnn_net_read_buf(net, data.data(), data.size());
+}
+extern "C" int dabnn_net_run(dabnn_net* net, const float* input, int batch, int in_is_device) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    return net->impl.run(input, batch, in_is_device != 0);
+}
+extern "C" int dabnn_net_sync(dabnn_net* net) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    DABNN_CUDA_OK(cudaStreamSynchronize(net->impl.stream));
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4], const float** device_ptr,
+                                  float* to_host, size_t host_floats) {
+    DABNN_REQUIRE(net && name, DABNN_ERR_ARG, "null argument");
+    NetImpl& n = net->impl;
+    DABNN_REQUIRE(n.loaded, DABNN_ERR_STATE, "get_blob: no model has been read");
+    auto it = n.blob_of.find(name);
+    if (it == n.blob_of.end()) return fail(DABNN_ERR_NOT_FOUND, std::string("Key ") + name + " not found.");
+    const Blob& b = n.blobs[it->second];
+    if (!(b.keep || it->second == n.input_blob))
+        return fail(DABNN_ERR_NOT_FOUND, std::string("blob ") + name + " is not materialised in the fused plan; read the model with optimize = 0 to keep every blob");
+    const int batch = n.cur_batch > 0 ? n.cur_batch : 1;
+    if (dims) { dims[0] = batch; dims[1] = b.h; dims[2] = b.w; dims[3] = b.c; }
+    if (device_ptr) *device_ptr = n.f32(it->second);
+    if (to_host) {
+        const size_t cnt = (size_t)batch * b.per_image();
+        DABNN_REQUIRE(host_floats >= cnt, DABNN_ERR_ARG, "get_blob: host buffer too small");
+        DABNN_CUDA_OK(cudaMemcpyAsync(to_host, n.f32(it->second), cnt * 4, cudaMemcpyDeviceToHost, n.stream));
+        DABNN_CUDA_OK(cudaStreamSynchronize(n.stream));
+    }
+    return DABNN_OK;
+}
+extern "C" const char* dabnn_net_output_name(dabnn_net* net, int i) {
+    if (!net || i < 0 || i >= (int)net->impl.outputs.size()) return nullptr;
+    return net->impl.outputs[i].c_str();
+}
+extern "C" dabnn_stream_t dabnn_net_stream(dabnn_net* net) { return net ? net->impl.stream : nullptr; }
+extern "C" int dabnn_net_stats(dabnn_net* net, int* kernels_per_run, size_t* arena_bytes) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    int k = 0;
+    for (const auto& o : net->impl.plan) k += o.kind == OpKind::BinConvIm2col ? 2 : 1;
+    if (kernels_per_run) *kernels_per_run = k;
+    if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes;
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_set_profiling(dabnn_net* net, int on) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    NetImpl& n = net->impl;
+    n.profiling = on != 0;
+    if (n.profiling && n.loaded && n.events.empty()) {
+        n.events.resize(n.plan.size() + 1);
+        for (auto& e : n.events) DABNN_CUDA_OK(cudaEventCreate(&e));
+    }
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_layer_times(dabnn_net* net, const char** names, float* ms, int cap, int* count) {
+    DABNN_REQUIRE(net && count, DABNN_ERR_ARG, "null argument");
+    NetImpl& n = net->impl;
+    DABNN_REQUIRE(n.profiling && !n.events.empty(), DABNN_ERR_STATE, "profiling is off");
+    DABNN_CUDA_OK(cudaStreamSynchronize(n.stream));
+    std::map<std::string, float> acc;
+    for (size_t i = 0; i < n.plan.size(); i++) {
+        float t = 0.f;
+        DABNN_CUDA_OK(cudaEventElapsedTime(&t, n.events[i], n.events[i + 1]));
+        acc[n.plan[i].cls] += t;
+    }
+    n.time_names.clear(); n.time_ms.clear();
+    for (auto& kv : acc) { n.time_names.push_back(kv.first); n.time_ms.push_back(kv.second); }
+    *count = (int)n.time_names.size();
+    for (int i = 0; i < *count && i < cap; i++) {
+        if (names) names[i] = n.time_names[i].c_str();
+        if (ms) ms[i] = n.time_ms[i];
+    }
+    return DABNN_OK;
+}
