@@ -268,7 +268,7 @@ int NetImpl::build() {
                 DABNN_REQUIRE(op.stride_h > 0 && op.stride_w > 0 && op.pad_h >= 0 && op.pad_w >= 0, DABNN_ERR_SHAPE,
                               "conv: bad pads/strides");
                 for (int d : L.dilations) DABNN_REQUIRE(d == 1, DABNN_ERR_UNSUPPORTED, "conv: dilation must be 1");
-                const Blob& ib = blobs[op.in];
+                const Blob ib = blobs[op.in];
                 const int cout = op.w->shape[0];
                 op.kh = op.w->shape[1]; op.kw = op.w->shape[2];
                 DABNN_REQUIRE((int)op.w->shape[3] == ib.c, DABNN_ERR_SHAPE, "conv: weight channels != input channels");
@@ -310,7 +310,7 @@ int NetImpl::build() {
             case LayerType::Add: {
                 if ((rc = find_blob(L.input, &op.in))) return rc;
                 if ((rc = find_blob(L.input2, &op.in2))) return rc;
-                const Blob &x = blobs[op.in], &y = blobs[op.in2];
+                const Blob x = blobs[op.in], y = blobs[op.in2];
                 DABNN_REQUIRE(x.h == y.h && x.w == y.w && x.c == y.c, DABNN_ERR_SHAPE, "add: shapes differ");
                 blob_of[L.output] = op.in;
                 op.out = op.in; op.kind = OpKind::Chain; op.cls = "Add";
@@ -338,7 +338,7 @@ int NetImpl::build() {
                               "pool: kernel_shape/pads/strides");
                 op.kh = L.kernel[0]; op.kw = L.kernel[1]; op.pad_h = L.pads[0]; op.pad_w = L.pads[1];
                 op.stride_h = L.strides[0]; op.stride_w = L.strides[1];
-                const Blob& ib = blobs[op.in];
+                const Blob ib = blobs[op.in];
                 DABNN_REQUIRE(op.kh > 0 && op.kw > 0 && op.stride_h > 0 && op.stride_w > 0, DABNN_ERR_UNSUPPORTED,
                               "pool: global pooling must be given as an explicit kernel");
                 const int oh = (ib.h + 2 * op.pad_h - op.kh) / op.stride_h + 1, ow = (ib.w + 2 * op.pad_w - op.kw) / op.stride_w + 1;
@@ -351,7 +351,7 @@ int NetImpl::build() {
             case LayerType::Concat: {
                 if ((rc = find_blob(L.input, &op.in))) return rc;
                 if ((rc = find_blob(L.input2, &op.in2))) return rc;
-                const Blob &x = blobs[op.in], &y = blobs[op.in2];
+                const Blob x = blobs[op.in], y = blobs[op.in2];
                 DABNN_REQUIRE(x.h == y.h && x.w == y.w, DABNN_ERR_SHAPE, "Wrong input for concat");
                 op.out = blob_of.count(L.output) ? blob_of[L.output] : new_blob(L.output, x.h, x.w, x.c + y.c);
                 op.kind = OpKind::Concat; op.cls = "Concat";
@@ -362,7 +362,7 @@ int NetImpl::build() {
                 if ((rc = find_tensor(L.weight, &op.w))) return rc;
                 if (!L.bias.empty())
                     if ((rc = find_tensor(L.bias, &op.bias))) return rc;
-                const Blob& ib = blobs[op.in];
+                const Blob ib = blobs[op.in];
                 DABNN_REQUIRE(!op.w->is_bit && op.w->shape.size() == 2 && op.w->shape[1] == ib.per_image(), DABNN_ERR_SHAPE,
                               "fc: weight must be [units][input_size]");
                 op.kh = ib.h; op.kw = ib.w;  // a full-size "valid" convolution
