@@ -1,0 +1,333 @@
+#!/usr/bin/env python
+"""Throughput benchmark: Bi-Real-Net-18-shaped inference (images/s), batch-sharded over N GPUs.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+           --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the reference's own CPU code on the host cores
+
+One step = one pass of the network over a fixed batch of seeded synthetic images (fp32 N(0,1),
+224x224x3, random-init weights) per GPU.  Every rank is an independent replica (no collective on
+the data path); per-GPU work is fixed, so scaling is weak.  Rank 0 prints ONE JSON line.
+
+  value     images/s with the inputs already resident in HBM, timed with CUDA events on the stream
+            the kernels run on, barrier + synchronize on both sides, max over ranks.
+  e2e       the same through the public Net API from pinned HOST memory: host->device copy of the
+            batch and device->host read of the logits inside the timed region, every step.
+  roofline  for the class of launches that takes most of the step (per-op CUDA events).
+  cpu_baseline  the reference's CPU implementation timed on this box's host cores (N=1 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+IMAGE_HW, CLASSES = 224, 1000
+BITOPS_PER_IMAGE = 3.353e9   # 16 binary 3x3 convolutions, 2*M*N*K each (K = true bits)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock, max SM clock and throttle reasons of one GPU through NVML while running."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, device_index):
+        super().__init__(daemon=True)
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            pass
+
+    def run(self):
+        while self.ok and not self._halt.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._halt.wait(0.05)
+
+    def stop(self):
+        self._halt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def algorithmic_bytes(spec, batch):
+    """Per layer class: bytes one step must move (each tensor read or written once), from the model
+    description.  fp32 activations 4 B/element, packed bits 1/8 B/element, weights once."""
+    shapes = {spec.input_name: spec.input_shape[1:]}
+    t = {x.name: x for x in spec.tensors}
+    out = {}
+
+    def add(cls, n):
+        out[cls] = out.get(cls, 0) + n
+
+    for l in spec.layers:
+        f = l.fields
+        if l.type in ("FpConv2D", "BinConv2D"):
+            h, w, c = shapes[f["input"]]
+            o, kh, kw, _ = t[f["weight"]].shape
+            oh = (h + 2 * f["pads"][0] - kh) // f["strides"][0] + 1
+            ow = (w + 2 * f["pads"][1] - kw) // f["strides"][1] + 1
+            shapes[f["output"]] = (oh, ow, o)
+            if l.type == "FpConv2D":
+                add("Float Conv", batch * (h * w * c + oh * ow * o) * 4 + t[f["weight"]].data.size * 4)
+            else:   # fused block: packed input, fp32 shortcut in, fp32 + packed out
+                add("Bin Conv block", batch * (h * w * c / 8 + oh * ow * o * (4 + 4 + 1 / 8)) + t[f["weight"]].data.size * 8)
+        elif l.type in ("MaxPool", "AvePool"):
+            h, w, c = shapes[f["input"]]
+            oh = (h + 2 * f["pads"][0] - f["kernel_shape"][0]) // f["strides"][0] + 1
+            ow = (w + 2 * f["pads"][1] - f["kernel_shape"][1]) // f["strides"][1] + 1
+            shapes[f["output"]] = (oh, ow, c)
+            add(l.type, batch * (h * w * c + oh * ow * c) * 4)
+        elif l.type == "Add":
+            shapes[f["output"]] = shapes[f["input1"]]
+        else:
+            shapes[f["output"]] = shapes[f["input"]]
+    return out
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from dabnn_b200 import ops
+    from dabnn_b200.bireal import OUTPUT_BLOB, build_bireal18
+    from dabnn_b200.dab_format import write_dab
+    from dabnn_b200.net import Net
+    from dabnn_b200.replicas import gather_logits
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    B = args.batch
+    spec = build_bireal18(image_hw=IMAGE_HW, num_classes=CLASSES)
+    net = Net.create()
+    net.max_batch, net.engine, net.optimize = B, args.engine, True
+    net.read_buf(write_dab(spec))
+    stream = torch.cuda.ExternalStream(net.cuda_stream)
+
+    # seeded synthetic inputs: one generator per rank, images indexed globally
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    x_dev = torch.randn((B, IMAGE_HW, IMAGE_HW, 3), device="cuda", generator=gen)
+    x_host = torch.empty((B, IMAGE_HW, IMAGE_HW, 3), dtype=torch.float32, pin_memory=True)
+    x_host.copy_(x_dev)
+    logits_host = torch.empty((B, CLASSES), dtype=torch.float32, pin_memory=True)
+    torch.cuda.synchronize()
+
+    x_ptr = x_dev.data_ptr()
+
+    def step_device():
+        net.run_device_ptr(x_ptr, B)
+
+    def step_e2e():
+        net.run_host_ptr(x_host.data_ptr(), B)
+        net.get_blob_to_ptr(OUTPUT_BLOB, logits_host.data_ptr(), B * CLASSES)
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+        net.sync()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    net.sync()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_dev = timed(step_device, args.steps)
+    clocks = sampler.stop()
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+
+    # per-class device time of one step (CUDA events around every launch) -> roofline of the top class
+    net.set_profiling(True)
+    net.run(x_dev); net.sync()
+    net.run(x_dev); net.sync()
+    classes = net.layer_times()
+    net.set_profiling(False)
+    stats = net.stats()
+
+    # the final gather of logits (not on the data path): check replica r's first images on rank 0
+    gathered_ok = None
+    if world > 1:
+        logits = torch.from_numpy(net.run(x_dev).get_blob(OUTPUT_BLOB).reshape(B, CLASSES)).cuda()
+        allv = gather_logits(logits[:8].contiguous(), 8 * world)
+        gen1 = torch.Generator(device="cuda").manual_seed(1234 + 1)
+        if rank == 0:
+            x1 = torch.randn((B, IMAGE_HW, IMAGE_HW, 3), device="cuda", generator=gen1)
+            mine = torch.from_numpy(net.run(x1).get_blob(OUTPUT_BLOB).reshape(B, CLASSES)[:8]).cuda()
+            gathered_ok = bool(torch.equal(mine, allv[8:16]))
+
+    result = None
+    if rank == 0:
+        hbm_gbs, peak_src = measured_peaks()
+        total_ms = sum(classes.values())
+        top = max(classes, key=classes.get)
+        alg = algorithmic_bytes(spec, B)
+        layers = {k: {"ms": round(v, 4), "share": round(v / total_ms, 4),
+                      "GBps": round(alg[k] / (v * 1e-3) / 1e9, 1) if k in alg else None} for k, v in classes.items()}
+        peaks = {e: ops.measure_engine_peak(e) / 1e12 for e in ("imma", "b1", "popc")}
+        eng = "imma" if args.engine == "auto" else args.engine
+        conv_ms = classes.get("Bin Conv block", 0.0)
+        conv_tops = BITOPS_PER_IMAGE * B / (conv_ms * 1e-3) / 1e12 if conv_ms else None
+        if top == "Bin Conv block":
+            roof = {"bound": "tensor", "kernel": f"bcontract_kernel<{eng}> (16 fused binary conv launches)",
+                    "achieved": round(conv_tops, 1), "peak": round(peaks[eng], 1), "unit": "Tbit-op/s",
+                    "frac": round(conv_tops / peaks[eng], 4),
+                    "peak_source": "mma.sync register-resident peak of the engine's instruction, measured in this run",
+                    "traffic": None}
+        else:
+            gbps = alg[top] / (classes[top] * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": top, "achieved": round(gbps, 1), "peak": hbm_gbs, "unit": "GB/s",
+                    "frac": round(gbps / hbm_gbs, 4), "peak_source": peak_src, "traffic": None}
+        result = {
+            "metric": "Bi-Real-18-shape images/s", "value": round(world * B * args.steps / (ms_dev * 1e-3), 1),
+            "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_dev / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "b1 x b1 -> s32 (int8 mma.sync on expanded bits) + fp32",
+            "data": "synthetic",
+            "config": {"workload": f"Bi-Real-Net-18-shaped BNN, 224x224x3 fp32 N(0,1) inputs, random-init, batch {B} per GPU, "
+                                   "independent replicas",
+                       "global_batch": B * world, "per_gpu_batch": B, "engine": eng,
+                       "l2": "inputs (617 MB) and activations (GBs) exceed the 126 MB L2; no flush needed"},
+            "e2e": {"value": round(world * B * args.steps / (ms_e2e * 1e-3), 1), "unit": "images/s",
+                    "h2d_bytes_per_step": B * IMAGE_HW * IMAGE_HW * 3 * 4, "d2h_bytes_per_step": B * CLASSES * 4,
+                    "ms_per_step": round(ms_e2e / args.steps, 4)},
+            "gpu_launches": stats["kernels_per_run"] * args.steps,
+            "clocks": clocks, "roofline": roof,
+            "bconv_total": {"Tbit_op_per_s": round(conv_tops, 1) if conv_tops else None,
+                            "engine_peaks_Tbit_op_per_s": {k: round(v, 1) for k, v in peaks.items()}},
+            "layers": layers, "device_bytes": stats["device_bytes"], "replica_check": gathered_ok,
+        }
+    return result, world, rank
+
+
+def run_reference(args, rounds, warmup):
+    """The reference's CPU implementation, all host cores (P single-threaded processes)."""
+    from oracle.cpu_baseline import ReferencePool
+    pool = ReferencePool(IMAGE_HW, CLASSES, images_per_proc=args.cpu_images, rounds=rounds + warmup, native=True)
+    try:
+        for _ in range(warmup):
+            pool.run_round()
+        secs, imgs = 0.0, 0
+        for _ in range(rounds):
+            dt, n = pool.run_round()
+            secs += dt
+            imgs += n
+    finally:
+        pool.close()
+    return {"value": round(imgs / secs, 2), "unit": "images/s", "cores": pool.procs_n, "kind": pool.kind,
+            "sample": f"{pool.procs_n} single-threaded processes x {args.cpu_images} images x {rounds} rounds of the same "
+                      f"network, reference sources built -O3 -march=native"}, secs / rounds
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1024, help="images per GPU per step")
+    ap.add_argument("--engine", default="auto", choices=["auto", "imma", "b1", "popc"])
+    ap.add_argument("--cpu-images", type=int, default=4, help="images per host process in the CPU baseline")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        base, sec_per_round = run_reference(args, rounds=max(1, args.steps), warmup=max(1, args.warmup))
+        line = {"impl": "reference", "metric": "Bi-Real-18-shape images/s", "value": base["value"], "unit": "images/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec_per_round * 1e3, 2),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64 xor-popcount + fp32 (CPU)",
+                "data": "synthetic",
+                "config": {"workload": "Bi-Real-Net-18-shaped BNN, 224x224x3 fp32 N(0,1) inputs, random-init; one step = a bounded "
+                                       "sample of the batch on the host cores"},
+                "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+
+    if args.gpus > 1 and world == 1:   # convenience: launch the ranks ourselves
+        import subprocess
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29517", str(Path(__file__).resolve()), *sys.argv[1:]]
+        raise SystemExit(subprocess.call(cmd))
+
+    result, world, rank = run_ours(args)
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                result["cpu_baseline"], _ = run_reference(args, rounds=2, warmup=1)
+            except Exception as e:  # the GPU numbers stand on their own
+                result["cpu_baseline"] = {"unavailable": str(e)}
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

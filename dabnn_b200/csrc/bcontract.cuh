@@ -28,11 +28,13 @@ namespace dabnn {
 
 constexpr int KC_WORDS = 16;               // uint64 words of K per pipeline stage
 constexpr int PITCH32 = KC_WORDS * 2 + 4;  // row pitch in 32-bit units (144 B): 8 rows x 64-bit reads hit 16 distinct banks
-constexpr int NSTAGES = 3;
+constexpr int NSTAGES = 2;                 // two CTAs of 4 warps fit one SM (shared memory and registers)
 
 enum { ENG_POPC = DABNN_ENGINE_POPC, ENG_B1 = DABNN_ENGINE_B1, ENG_IMMA = DABNN_ENGINE_IMMA };
 
 // ---- operand addressing ------------------------------------------------------------------------
+// A loader thread owns one pair of K words (w, w+1; w even) of the current chunk for many rows.
+// decode() is called once per chunk for each word of the pair, addr() once per row.
 struct RowCtx {
     long long base;  // row-major/col-major: element offset of the row; conv: pixel index of image start
     int iy0, ix0;    // conv: top-left input coordinate of the receptive field
@@ -44,26 +46,34 @@ struct RowMajorOperand {
     const uint64_t* p;
     long long ld;
     int rows, kwords;
+    struct Dec { int word; };
+    __device__ bool pairable() const { return (ld & 1) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+    __device__ Dec decode(int word) const { return Dec{word}; }
     __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row * ld, 0, 0, row < rows}; }
-    __device__ const uint64_t* addr(const RowCtx& r, int word) const {
-        return (r.valid && word < kwords) ? p + r.base + word : nullptr;
-    }
+    __device__ const uint64_t* addr(const RowCtx& r, const Dec& d) const { return r.valid ? p + r.base + d.word : nullptr; }
 };
 // the reference bgemm's `a`: element (row i, word h) at p[h*ld + i]
 struct ColMajorOperand {
     const uint64_t* p;
     long long ld;
     int rows, kwords;
+    struct Dec { long long off; };
+    __device__ bool pairable() const { return false; }
+    __device__ Dec decode(int word) const { return Dec{(long long)word * ld}; }
     __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row, 0, 0, row < rows}; }
-    __device__ const uint64_t* addr(const RowCtx& r, int word) const {
-        return (r.valid && word < kwords) ? p + (long long)word * ld + r.base : nullptr;
-    }
+    __device__ const uint64_t* addr(const RowCtx& r, const Dec& d) const { return r.valid ? p + d.off + r.base : nullptr; }
 };
 // implicit im2col over packed NHWC bits: row = output pixel, word = (ky*kw + kx)*Cw + cw
 struct ConvOperand {
     const uint64_t* p;
     int n, H, W, Cw, OH, OW, kh, kw, pad_h, pad_w, stride_h, stride_w;
     int rows, kwords;
+    struct Dec { int ky, kx, cw; };
+    __device__ bool pairable() const { return (Cw & 1) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+    __device__ Dec decode(int word) const {
+        const int tap = word / Cw, ky = tap / kw;
+        return Dec{ky, tap - ky * kw, word - tap * Cw};
+    }
     __device__ RowCtx make_row(int row) const {
         RowCtx r;
         r.valid = row < rows;
@@ -74,13 +84,10 @@ struct ConvOperand {
         r.ix0 = ox * stride_w - pad_w;
         return r;
     }
-    __device__ const uint64_t* addr(const RowCtx& r, int word) const {
-        if (!r.valid || word >= kwords) return nullptr;
-        const int tap = word / Cw, cw = word - tap * Cw;
-        const int ky = tap / kw, kx = tap - ky * kw;
-        const int y = r.iy0 + ky, x = r.ix0 + kx;
-        if (y < 0 || y >= H || x < 0 || x >= W) return nullptr;
-        return p + (r.base + (long long)y * W + x) * Cw + cw;
+    __device__ const uint64_t* addr(const RowCtx& r, const Dec& d) const {
+        const int y = r.iy0 + d.ky, x = r.ix0 + d.kx;
+        if (!r.valid || (unsigned)y >= (unsigned)H || (unsigned)x >= (unsigned)W) return nullptr;
+        return p + (r.base + (long long)y * W + x) * Cw + d.cw;
     }
 };
 
@@ -99,6 +106,9 @@ struct EpilogueParams {
 
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -123,6 +133,11 @@ __device__ __forceinline__ void mma_u8(int* d, uint32_t a0, uint32_t a1, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// exact int -> float for 0 <= v < 2^23 on the FP32 pipe (I2F runs on the quarter-rate XU pipe)
+__device__ __forceinline__ float small_int_to_float(int v) {
+    return __fsub_rn(__int_as_float(0x4B000000 | v), 8388608.0f);
+}
+
 template <int WM, int WN>
 struct TileCfg {
     static constexpr int TM = WM * 64, TN = WN * 64, NT = WM * WN * 32;
@@ -130,21 +145,50 @@ struct TileCfg {
     static constexpr int CPITCH = TN + 4;  // staged count tile pitch (ints)
     static constexpr size_t PIPE_BYTES = (size_t)NSTAGES * STAGE_U32 * 4;
     static constexpr size_t CTILE_BYTES = (size_t)TM * CPITCH * 4;
-    static constexpr size_t SMEM_BYTES = (PIPE_BYTES > CTILE_BYTES ? PIPE_BYTES : CTILE_BYTES) +
-                                         (size_t)(TM + TN) * (sizeof(RowCtx) + sizeof(int));
+    static constexpr size_t MAIN_BYTES = PIPE_BYTES > CTILE_BYTES ? PIPE_BYTES : CTILE_BYTES;
+    static constexpr size_t SMEM_BYTES = MAIN_BYTES + (size_t)(TM + TN) * (sizeof(RowCtx) + sizeof(int));
 };
+
+// Copies one K chunk of `NROWS` operand rows into a pipeline stage.  Thread t owns word pair
+// (t & 7) of the chunk for rows (t >> 3), (t >> 3) + NT/8, ...
+template <int NROWS, int NT, class Op>
+__device__ __forceinline__ void load_rows(const Op& op, const RowCtx* ctx, uint32_t stage_addr, int w0,
+                                          int kwords, int kfill, bool pair_ok, int tid) {
+    const int wp = tid & 7, w = w0 + 2 * wp;
+    if (w >= kfill) return;
+    const bool v0 = w < kwords, v1 = w + 1 < kwords, f1 = w + 1 < kfill;
+    const typename Op::Dec d0 = op.decode(v0 ? w : 0), d1 = op.decode(v1 ? w + 1 : 0);
+    const uint32_t col = stage_addr + wp * 16;
+    if (pair_ok && v1) {
+#pragma unroll 4
+        for (int r = tid >> 3; r < NROWS; r += NT / 8) {
+            const uint64_t* src = op.addr(ctx[r], d0);
+            cp_async16(col + r * (PITCH32 * 4), src ? (const void*)src : (const void*)op.p, src ? 16 : 0);
+        }
+    } else {
+#pragma unroll 4
+        for (int r = tid >> 3; r < NROWS; r += NT / 8) {
+            const RowCtx c = ctx[r];
+            const uint64_t* s0 = v0 ? op.addr(c, d0) : nullptr;
+            cp_async8(col + r * (PITCH32 * 4), s0 ? (const void*)s0 : (const void*)op.p, s0 ? 8 : 0);
+            if (f1) {
+                const uint64_t* s1 = v1 ? op.addr(c, d1) : nullptr;
+                cp_async8(col + r * (PITCH32 * 4) + 8, s1 ? (const void*)s1 : (const void*)op.p, s1 ? 8 : 0);
+            }
+        }
+    }
+}
 
 // One CTA computes a TM x TN tile of counts.  grid = (ceil(M/TM), ceil(N/TN)).
 template <int ENGINE, int WM, int WN, class XOp, class WOp>
-__global__ void __launch_bounds__(WM* WN * 32)
+__global__ void __launch_bounds__(WM* WN * 32, 2)
     bcontract_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
                      const int kwords) {
     using Cfg = TileCfg<WM, WN>;
     constexpr int TM = Cfg::TM, TN = Cfg::TN, NT = Cfg::NT, ROWS = TM + TN;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t* pipe = reinterpret_cast<uint32_t*>(smem_raw);
-    constexpr size_t MAIN_BYTES = Cfg::PIPE_BYTES > Cfg::CTILE_BYTES ? Cfg::PIPE_BYTES : Cfg::CTILE_BYTES;
-    RowCtx* rowctx = reinterpret_cast<RowCtx*>(smem_raw + MAIN_BYTES);
+    RowCtx* rowctx = reinterpret_cast<RowCtx*>(smem_raw + Cfg::MAIN_BYTES);
     int* rowpop = reinterpret_cast<int*>(rowctx + ROWS);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -154,27 +198,22 @@ __global__ void __launch_bounds__(WM* WN * 32)
         rowctx[r] = r < TM ? xop.make_row(m0 + r) : wop.make_row(n0 + (r - TM));
     __syncthreads();
 
+    constexpr bool MMA = ENGINE != ENG_POPC;
+    // the b1 MMA consumes 4 words per step: its K tail is zero-filled up to a multiple of 4 words
+    const int kfill = ENGINE == ENG_B1 ? (kwords + 3) / 4 * 4 : kwords;
     const int nchunks = (kwords + KC_WORDS - 1) / KC_WORDS;
+    const bool xpair = xop.pairable(), wpair = wop.pairable();
     auto issue_chunk = [&](int chunk) {
         if (chunk < nchunks) {
-            uint32_t* st = pipe + (chunk % NSTAGES) * Cfg::STAGE_U32;
-            const uint32_t st_addr = smem_u32(st);
-            const int w0 = chunk * KC_WORDS;
-#pragma unroll 4
-            for (int e = tid; e < ROWS * KC_WORDS; e += NT) {
-                const int r = e / KC_WORDS, wd = e % KC_WORDS;
-                const uint64_t* src = r < TM ? xop.addr(rowctx[r], w0 + wd) : wop.addr(rowctx[r], w0 + wd);
-                cp_async8(st_addr + (r * PITCH32 + wd * 2) * 4, src ? (const void*)src : (const void*)xop.p,
-                          src ? 8 : 0);
-            }
+            const uint32_t st_addr = smem_u32(pipe + (chunk % NSTAGES) * Cfg::STAGE_U32);
+            load_rows<TM, NT>(xop, rowctx, st_addr, chunk * KC_WORDS, kwords, kfill, xpair, tid);
+            load_rows<TN, NT>(wop, rowctx + TM, st_addr + TM * PITCH32 * 4, chunk * KC_WORDS, kwords, kfill, wpair, tid);
         }
         cp_async_commit();
     };
 #pragma unroll
     for (int s = 0; s < NSTAGES - 1; s++) issue_chunk(s);
 
-    // accumulators
-    constexpr bool MMA = ENGINE != ENG_POPC;
     constexpr int PR = 16 / WN, PC = 8 * WN;  // POPC engine: rows / cols per thread
     int acc[128];  // MMA engines: [(m-tile*8 + n-tile)*4 + frag]; POPC engine: [row*PC + col]
 #pragma unroll
@@ -202,12 +241,11 @@ __global__ void __launch_bounds__(WM* WN * 32)
             for (int i = 0; i < POPROWS; i++) {
                 const int r = tid + i * NT;
                 if (r < ROWS) {
-                    const uint4* rp = reinterpret_cast<const uint4*>(st + r * PITCH32);
+                    const uint2* rp = reinterpret_cast<const uint2*>(st + r * PITCH32);
                     int s = 0;
-#pragma unroll
-                    for (int q = 0; q < KC_WORDS / 2; q++) {
-                        const uint4 v = rp[q];
-                        s += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
+                    for (int q = 0; q < words; q++) {
+                        const uint2 v = rp[q];
+                        s += __popc(v.x) + __popc(v.y);
                     }
                     mypop[i] += s;
                 }
@@ -309,8 +347,8 @@ __global__ void __launch_bounds__(WM* WN * 32)
             for (int nt = 0; nt < 8; nt++) {
                 const int c = wn * 64 + nt * 8 + tig * 2;
                 const int pw0 = rowpop[TM + c], pw1 = rowpop[TM + c + 1];
-                int2 v0, v1;
                 const int* d = &acc[(mt * 8 + nt) * 4];
+                int2 v0, v1;
                 v0.x = px0 + pw0 - 2 * d[0];
                 v0.y = px0 + pw1 - 2 * d[1];
                 v1.x = px1 + pw0 - 2 * d[2];
@@ -327,64 +365,76 @@ __global__ void __launch_bounds__(WM* WN * 32)
     }
     __syncthreads();
 
-    // cooperative epilogue: each thread owns 4 consecutive channels of one row per step
-    constexpr int C4 = TN / 4;
+    // Cooperative epilogue: a thread owns 4 consecutive channels of one row per item and handles
+    // EU items per round so that EU independent 16-byte loads are in flight before any is used.
+    constexpr int C4 = TN / 4, EU = 8;
     const bool vec_ok = (N % 4 == 0) && (!ep.out || (ep.ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0)) &&
                         (!ep.shortcut || (ep.ld_sc % 4 == 0 && (reinterpret_cast<uintptr_t>(ep.shortcut) & 15) == 0));
-    for (int it = tid; it < TM * C4; it += NT) {
-        const int r = it / C4, c = (it % C4) * 4;
-        const int row = m0 + r, col = n0 + c;
-        const int4 cnt = *reinterpret_cast<const int4*>(ct + r * Cfg::CPITCH + c);
-        float v[4] = {(float)cnt.x, (float)cnt.y, (float)cnt.z, (float)cnt.w};
-        const bool row_ok = row < M;
-        unsigned nib = 0;
-        if (row_ok && col < N) {
-            const int nvalid = min(4, N - col);
-            if (ep.a) {
+    const int c = (tid % C4) * 4, col = n0 + c;   // NT is a multiple of C4: a thread keeps its channels
+    const bool col_ok = col < N;
+    const int nvalid = min(4, N - col);
+    float av[4] = {1.f, 1.f, 1.f, 1.f}, bv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ep.a && col_ok) {
 #pragma unroll
-                for (int q = 0; q < 4; q++)
-                    if (q < nvalid) v[q] = __fadd_rn(__fmul_rn(ep.a[col + q], v[q]), ep.b[col + q]);
-            }
-            if (ep.shortcut) {
-                const float* sp = ep.shortcut + (long long)row * ep.ld_sc + col;
-                if (vec_ok) {
-                    const float4 s4 = *reinterpret_cast<const float4*>(sp);
-                    v[0] = __fadd_rn(v[0], s4.x); v[1] = __fadd_rn(v[1], s4.y);
-                    v[2] = __fadd_rn(v[2], s4.z); v[3] = __fadd_rn(v[3], s4.w);
-                } else {
+        for (int q = 0; q < 4; q++)
+            if (q < nvalid) { av[q] = __ldg(ep.a + col + q); bv[q] = __ldg(ep.b + col + q); }
+    }
+    for (int it0 = tid; it0 < TM * C4; it0 += NT * EU) {
+        float4 add4[EU];
+        if (vec_ok && col_ok && (ep.shortcut || ep.accumulate)) {
+            const float* src = ep.shortcut ? ep.shortcut : ep.out;
+            const long long lds = ep.shortcut ? ep.ld_sc : ep.ld_out;
 #pragma unroll
-                    for (int q = 0; q < 4; q++)
-                        if (q < nvalid) v[q] = __fadd_rn(v[q], sp[q]);
-                }
+            for (int u = 0; u < EU; u++) {
+                const int row = m0 + (it0 + u * NT) / C4;
+                add4[u] = row < M ? __ldcs(reinterpret_cast<const float4*>(src + (long long)row * lds + col))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            if (ep.out) {
-                float* op = ep.out + (long long)row * ep.ld_out + col;
-                if (vec_ok) {
-                    float4 o = make_float4(v[0], v[1], v[2], v[3]);
-                    if (ep.accumulate) {
-                        const float4 old = *reinterpret_cast<const float4*>(op);
-                        o.x = __fadd_rn(old.x, o.x); o.y = __fadd_rn(old.y, o.y);
-                        o.z = __fadd_rn(old.z, o.z); o.w = __fadd_rn(old.w, o.w);
-                    }
-                    *reinterpret_cast<float4*>(op) = o;
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 4; q++)
-                        if (q < nvalid) op[q] = ep.accumulate ? __fadd_rn(op[q], v[q]) : v[q];
-                }
-            }
-            nib = (v[0] > 0.f ? 1u : 0u) | (v[1] > 0.f ? 2u : 0u) | (v[2] > 0.f ? 4u : 0u) | (v[3] > 0.f ? 8u : 0u);
         }
-        if (ep.bits) {  // 16 consecutive lanes hold the 64 channels of one word (uniform branch)
-            const int sub = lane & 15;
-            unsigned lo = sub < 8 ? nib << (4 * sub) : 0u, hi = sub >= 8 ? nib << (4 * (sub - 8)) : 0u;
 #pragma unroll
-            for (int off = 1; off < 16; off <<= 1) {
-                lo |= __shfl_xor_sync(0xffffffffu, lo, off);
-                hi |= __shfl_xor_sync(0xffffffffu, hi, off);
+        for (int u = 0; u < EU; u++) {
+            const int r = (it0 + u * NT) / C4, row = m0 + r;
+            const int4 cnt = *reinterpret_cast<const int4*>(ct + r * Cfg::CPITCH + c);
+            float v[4] = {small_int_to_float(cnt.x), small_int_to_float(cnt.y), small_int_to_float(cnt.z),
+                          small_int_to_float(cnt.w)};
+            const bool ok = row < M && col_ok;
+            unsigned nib = 0;
+            if (ok) {
+                if (ep.a) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) v[q] = __fadd_rn(__fmul_rn(av[q], v[q]), bv[q]);
+                }
+                if (vec_ok) {
+                    if (ep.shortcut || ep.accumulate) {
+                        v[0] = __fadd_rn(add4[u].x, v[0]); v[1] = __fadd_rn(add4[u].y, v[1]);
+                        v[2] = __fadd_rn(add4[u].z, v[2]); v[3] = __fadd_rn(add4[u].w, v[3]);
+                    }
+                    if (ep.out)
+                        __stcs(reinterpret_cast<float4*>(ep.out + (long long)row * ep.ld_out + col),
+                               make_float4(v[0], v[1], v[2], v[3]));
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if (q >= nvalid) continue;
+                        if (ep.shortcut) v[q] = __fadd_rn(v[q], ep.shortcut[(long long)row * ep.ld_sc + col + q]);
+                        if (ep.out) {
+                            float* op = ep.out + (long long)row * ep.ld_out + col + q;
+                            *op = ep.accumulate ? __fadd_rn(*op, v[q]) : v[q];
+                        }
+                    }
+                }
+                nib = (v[0] > 0.f ? 1u : 0u) | (v[1] > 0.f ? 2u : 0u) | (v[2] > 0.f ? 4u : 0u) | (v[3] > 0.f ? 8u : 0u);
             }
-            if (sub == 0 && row_ok && col < N)
-                ep.bits[(long long)row * ep.ld_bits + (col >> 6)] = ((unsigned long long)hi << 32) | lo;
+            if (ep.bits) {  // 16 consecutive lanes hold the 64 channels of one word (uniform branch)
+                const int sub = lane & 15;
+                unsigned lo = sub < 8 ? nib << (4 * sub) : 0u, hi = sub >= 8 ? nib << (4 * (sub - 8)) : 0u;
+#pragma unroll
+                for (int off = 1; off < 16; off <<= 1) {
+                    lo |= __shfl_xor_sync(0xffffffffu, lo, off);
+                    hi |= __shfl_xor_sync(0xffffffffu, hi, off);
+                }
+                if (sub == 0 && ok) ep.bits[(long long)row * ep.ld_bits + (col >> 6)] = ((unsigned long long)hi << 32) | lo;
+            }
         }
     }
 }

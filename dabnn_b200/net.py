@@ -73,6 +73,10 @@ class Net:
             check(lib.dabnn_net_run(self._h, C.c_void_p(images.data_ptr()), batch, 1))
         return self
 
+    def run_device_ptr(self, ptr: int, batch: int):
+        """run() on a raw device pointer; the caller orders it after whatever produced the data."""
+        check(capi.load().dabnn_net_run(self._h, C.c_void_p(ptr), batch, 1))
+
     def run_host_ptr(self, ptr: int, batch: int):
         """run() on a raw host pointer (e.g. pinned memory), no Python-side copies."""
         check(capi.load().dabnn_net_run(self._h, C.c_void_p(ptr), batch, 0))
