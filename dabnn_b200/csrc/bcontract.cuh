@@ -18,9 +18,9 @@
 // Pbit-op/s, the int8 MMA at about 1.1 and CUDA-core popc at about 0.28), which is why IMMA is
 // the default engine.
 //
-// The accumulators are turned into counts, staged through shared memory and written by a
-// cooperative, fully coalesced epilogue that can also apply the per-channel affine, add the
-// shortcut and emit the sign bits of the result (the next layer's packed input).
+// The accumulators are turned into counts and written straight from the MMA fragment layout by an
+// epilogue that can also apply the per-channel affine, add the shortcut and emit the sign bits of
+// the result (the next layer's packed input).
 #pragma once
 #include "common.cuh"
 
@@ -142,11 +142,10 @@ template <int WM, int WN>
 struct TileCfg {
     static constexpr int TM = WM * 64, TN = WN * 64, NT = WM * WN * 32;
     static constexpr int STAGE_U32 = (TM + TN) * PITCH32;
-    static constexpr int CPITCH = TN + 4;  // staged count tile pitch (ints)
     static constexpr size_t PIPE_BYTES = (size_t)NSTAGES * STAGE_U32 * 4;
-    static constexpr size_t CTILE_BYTES = (size_t)TM * CPITCH * 4;
-    static constexpr size_t MAIN_BYTES = PIPE_BYTES > CTILE_BYTES ? PIPE_BYTES : CTILE_BYTES;
-    static constexpr size_t SMEM_BYTES = MAIN_BYTES + (size_t)(TM + TN) * (sizeof(RowCtx) + sizeof(int));
+    // two sets of pixel-row contexts (current / next tile), one set of channel-row contexts, row popcounts
+    static constexpr size_t SMEM_BYTES = PIPE_BYTES + (size_t)(2 * TM + TN) * sizeof(RowCtx) + (size_t)(TM + TN) * sizeof(int) +
+                                         (size_t)2 * TN * sizeof(float);
 };
 
 // Copies one K chunk of `NROWS` operand rows into a pipeline stage.  Thread t owns word pair
@@ -179,264 +178,288 @@ __device__ __forceinline__ void load_rows(const Op& op, const RowCtx* ctx, uint3
     }
 }
 
-// One CTA computes a TM x TN tile of counts.  grid = (ceil(M/TM), ceil(N/TN)).
+// Persistent kernel.  CTA (bx, by) owns channel tile `by` and walks pixel tiles bx, bx + gridDim.x,
+// ...; each tile is TM pixels x TN channels, each of the 4 warps a 64 x 64 sub-tile.  While a tile
+// is being computed and written out, the first K chunk of the next tile is already in flight, so
+// neither the operand loads nor the output traffic sit on the critical path of the MMAs of the
+// co-resident CTA.
+//
+// Accumulator layout (all engines): acc[(mt*8 + nt)*4 + h*2 + q] is pixel row mt*16 + g + 8*h,
+// channel nt*8 + 2*tig + q of the warp's sub-tile (g = lane / 4, tig = lane % 4), the fragment
+// layout of mma.sync.  The epilogue works straight from these registers: per m-tile it first
+// issues all shortcut loads (16 independent 8-byte loads per thread), then converts, applies the
+// affine, adds, stores, and ORs the sign bits of a row together across the four lanes of a quad.
 template <int ENGINE, int WM, int WN, class XOp, class WOp>
 __global__ void __launch_bounds__(WM* WN * 32, 2)
     bcontract_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
-                     const int kwords) {
+                     const int kwords, const int ntiles_m) {
     using Cfg = TileCfg<WM, WN>;
     constexpr int TM = Cfg::TM, TN = Cfg::TN, NT = Cfg::NT, ROWS = TM + TN;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t* pipe = reinterpret_cast<uint32_t*>(smem_raw);
-    RowCtx* rowctx = reinterpret_cast<RowCtx*>(smem_raw + Cfg::MAIN_BYTES);
-    int* rowpop = reinterpret_cast<int*>(rowctx + ROWS);
+    RowCtx* xctx = reinterpret_cast<RowCtx*>(smem_raw + Cfg::PIPE_BYTES);  // [2][TM]
+    RowCtx* wctx = xctx + 2 * TM;                                           // [TN]
+    int* rowpop = reinterpret_cast<int*>(wctx + TN);                        // [TM + TN]
+    float* chan_a = reinterpret_cast<float*>(rowpop + ROWS);                // [TN] affine scale
+    float* chan_b = chan_a + TN;                                            // [TN] affine shift
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
-
-    for (int r = tid; r < ROWS; r += NT)
-        rowctx[r] = r < TM ? xop.make_row(m0 + r) : wop.make_row(n0 + (r - TM));
-    __syncthreads();
+    const int g = lane >> 2, tig = lane & 3;
+    const int wm = warp / WN, wn = warp % WN;
+    const int n0 = blockIdx.y * TN;
+    int tile = blockIdx.x;
+    if (tile >= ntiles_m) return;
 
     constexpr bool MMA = ENGINE != ENG_POPC;
     // the b1 MMA consumes 4 words per step: its K tail is zero-filled up to a multiple of 4 words
     const int kfill = ENGINE == ENG_B1 ? (kwords + 3) / 4 * 4 : kwords;
     const int nchunks = (kwords + KC_WORDS - 1) / KC_WORDS;
     const bool xpair = xop.pairable(), wpair = wop.pairable();
-    auto issue_chunk = [&](int chunk) {
-        if (chunk < nchunks) {
-            const uint32_t st_addr = smem_u32(pipe + (chunk % NSTAGES) * Cfg::STAGE_U32);
-            load_rows<TM, NT>(xop, rowctx, st_addr, chunk * KC_WORDS, kwords, kfill, xpair, tid);
-            load_rows<TN, NT>(wop, rowctx + TM, st_addr + TM * PITCH32 * 4, chunk * KC_WORDS, kwords, kfill, wpair, tid);
-        }
-        cp_async_commit();
+
+    for (int r = tid; r < TN; r += NT) {
+        wctx[r] = wop.make_row(n0 + r);
+        const bool have = ep.a && n0 + r < N;
+        chan_a[r] = have ? __ldg(ep.a + n0 + r) : 1.f;
+        chan_b[r] = have ? __ldg(ep.b + n0 + r) : 0.f;
+    }
+    for (int r = tid; r < TM; r += NT) xctx[r] = xop.make_row(tile * TM + r);
+    __syncthreads();
+
+    auto issue = [&](int set, int chunk, int stage) {
+        const uint32_t st_addr = smem_u32(pipe + stage * Cfg::STAGE_U32);
+        load_rows<TM, NT>(xop, xctx + set * TM, st_addr, chunk * KC_WORDS, kwords, kfill, xpair, tid);
+        load_rows<TN, NT>(wop, wctx, st_addr + TM * PITCH32 * 4, chunk * KC_WORDS, kwords, kfill, wpair, tid);
     };
-#pragma unroll
-    for (int s = 0; s < NSTAGES - 1; s++) issue_chunk(s);
+    issue(0, 0, 0);
+    cp_async_commit();
 
-    constexpr int PR = 16 / WN, PC = 8 * WN;  // POPC engine: rows / cols per thread
-    int acc[128];  // MMA engines: [(m-tile*8 + n-tile)*4 + frag]; POPC engine: [row*PC + col]
-#pragma unroll
-    for (int i = 0; i < 128; i++) acc[i] = 0;
+    // per-thread channel constants: 8 n-tiles x 2 channels
+    const int colbase = n0 + wn * 64 + tig * 2;
+    const float* addsrc = ep.shortcut ? ep.shortcut : (ep.accumulate ? ep.out : nullptr);
+    const long long ld_add = ep.shortcut ? ep.ld_sc : ep.ld_out;
+    const bool vec2 = (N % 2 == 0) && (!ep.out || (ep.ld_out % 2 == 0 && (reinterpret_cast<uintptr_t>(ep.out) & 7) == 0)) &&
+                      (!addsrc || (ld_add % 2 == 0 && (reinterpret_cast<uintptr_t>(addsrc) & 7) == 0));
+
     constexpr int POPROWS = (ROWS + NT - 1) / NT;
-    int mypop[POPROWS];
+    int item = 0;
+    for (int lt = 0; tile < ntiles_m; tile += gridDim.x, lt++) {
+        const int next = tile + gridDim.x;
+        const bool has_next = next < ntiles_m;
+        const int set = lt & 1;
+        if (has_next)
+            for (int r = tid; r < TM; r += NT) xctx[(set ^ 1) * TM + r] = xop.make_row(next * TM + r);
+
+        int acc[128];
 #pragma unroll
-    for (int i = 0; i < POPROWS; i++) mypop[i] = 0;
-
-    const int g = lane >> 2, tig = lane & 3;
-    const int wm = warp / WN, wn = warp % WN;
-    const int ty = tid >> 3, tx = tid & 7;  // POPC engine thread grid: (NT/8) x 8
-
-    for (int chunk = 0; chunk < nchunks; chunk++) {
-        cp_async_wait<NSTAGES - 2>();
-        __syncthreads();
-        issue_chunk(chunk + NSTAGES - 1);
-        const uint32_t* st = pipe + (chunk % NSTAGES) * Cfg::STAGE_U32;
-        const uint32_t* Xs = st;
-        const uint32_t* Ws = st + TM * PITCH32;
-        const int words = min(KC_WORDS, kwords - chunk * KC_WORDS);
-
-        if (MMA) {  // row popcounts of both operands for the AND engines
+        for (int i = 0; i < 128; i++) acc[i] = 0;
+        int mypop[POPROWS];
 #pragma unroll
-            for (int i = 0; i < POPROWS; i++) {
-                const int r = tid + i * NT;
-                if (r < ROWS) {
-                    const uint2* rp = reinterpret_cast<const uint2*>(st + r * PITCH32);
-                    int s = 0;
-                    for (int q = 0; q < words; q++) {
-                        const uint2 v = rp[q];
-                        s += __popc(v.x) + __popc(v.y);
+        for (int i = 0; i < POPROWS; i++) mypop[i] = 0;
+
+        for (int chunk = 0; chunk < nchunks; chunk++, item++) {
+            cp_async_wait<0>();
+            __syncthreads();
+            if (chunk + 1 < nchunks) issue(set, chunk + 1, (item + 1) & 1);
+            else if (has_next) issue(set ^ 1, 0, (item + 1) & 1);
+            cp_async_commit();
+
+            const uint32_t* st = pipe + (item & 1) * Cfg::STAGE_U32;
+            const uint32_t* Xs = st;
+            const uint32_t* Ws = st + TM * PITCH32;
+            const int words = min(KC_WORDS, kwords - chunk * KC_WORDS);
+
+            if (MMA) {  // row popcounts of both operands for the AND engines
+#pragma unroll
+                for (int i = 0; i < POPROWS; i++) {
+                    const int r = tid + i * NT;
+                    if (r < ROWS) {
+                        const uint2* rp = reinterpret_cast<const uint2*>(st + r * PITCH32);
+                        int s = 0;
+                        for (int q = 0; q < words; q++) {
+                            const uint2 v = rp[q];
+                            s += __popc(v.x) + __popc(v.y);
+                        }
+                        mypop[i] += s;
                     }
-                    mypop[i] += s;
                 }
             }
-        }
 
-        if (ENGINE == ENG_IMMA) {
-            const uint32_t M1 = 0x01010101u;
-            for (int wd = 0; wd < words; wd++) {
-                uint2 xa[4][2], wb[8];
-#pragma unroll
-                for (int mt = 0; mt < 4; mt++) {
-                    const int r = wm * 64 + mt * 16 + g;
-                    xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + wd * 2);
-                    xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + wd * 2);
-                }
-#pragma unroll
-                for (int nt = 0; nt < 8; nt++)
-                    wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + wd * 2);
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    uint32_t af[4][4], bf[8][2];
+            if (ENGINE == ENG_IMMA) {
+                const uint32_t M1 = 0x01010101u;
+                for (int wd = 0; wd < words; wd++) {
+                    uint2 xa[4][2], wb[8];
 #pragma unroll
                     for (int mt = 0; mt < 4; mt++) {
-                        const uint32_t c0 = (half ? xa[mt][0].y : xa[mt][0].x) >> tig;
-                        const uint32_t c1 = (half ? xa[mt][1].y : xa[mt][1].x) >> tig;
-                        af[mt][0] = c0 & M1;
-                        af[mt][1] = c1 & M1;
-                        af[mt][2] = (c0 >> 4) & M1;
-                        af[mt][3] = (c1 >> 4) & M1;
+                        const int r = wm * 64 + mt * 16 + g;
+                        xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + wd * 2);
+                        xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + wd * 2);
                     }
 #pragma unroll
-                    for (int nt = 0; nt < 8; nt++) {
-                        const uint32_t c = (half ? wb[nt].y : wb[nt].x) >> tig;
-                        bf[nt][0] = c & M1;
-                        bf[nt][1] = (c >> 4) & M1;
+                    for (int nt = 0; nt < 8; nt++)
+                        wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + wd * 2);
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t af[4][4], bf[8][2];
+#pragma unroll
+                        for (int mt = 0; mt < 4; mt++) {
+                            const uint32_t c0 = (half ? xa[mt][0].y : xa[mt][0].x) >> tig;
+                            const uint32_t c1 = (half ? xa[mt][1].y : xa[mt][1].x) >> tig;
+                            af[mt][0] = c0 & M1;
+                            af[mt][1] = c1 & M1;
+                            af[mt][2] = (c0 >> 4) & M1;
+                            af[mt][3] = (c1 >> 4) & M1;
+                        }
+#pragma unroll
+                        for (int nt = 0; nt < 8; nt++) {
+                            const uint32_t c = (half ? wb[nt].y : wb[nt].x) >> tig;
+                            bf[nt][0] = c & M1;
+                            bf[nt][1] = (c >> 4) & M1;
+                        }
+#pragma unroll
+                        for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+                            for (int nt = 0; nt < 8; nt++)
+                                mma_u8(&acc[(mt * 8 + nt) * 4], af[mt][0], af[mt][1], af[mt][2], af[mt][3], bf[nt][0], bf[nt][1]);
                     }
+                }
+            } else if (ENGINE == ENG_B1) {
+                const int steps = (words + 3) / 4;  // 4 words = 256 bits per MMA; the tail words are zero
+                for (int s = 0; s < steps; s++) {
+                    uint2 xa[4][2], wb[8];
+#pragma unroll
+                    for (int mt = 0; mt < 4; mt++) {
+                        const int r = wm * 64 + mt * 16 + g;
+                        xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + (s * 4 + tig) * 2);
+                        xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + (s * 4 + tig) * 2);
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < 8; nt++)
+                        wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + (s * 4 + tig) * 2);
 #pragma unroll
                     for (int mt = 0; mt < 4; mt++)
 #pragma unroll
                         for (int nt = 0; nt < 8; nt++)
-                            mma_u8(&acc[(mt * 8 + nt) * 4], af[mt][0], af[mt][1], af[mt][2], af[mt][3], bf[nt][0], bf[nt][1]);
+                            mma_b1_and(&acc[(mt * 8 + nt) * 4], xa[mt][0].x, xa[mt][1].x, xa[mt][0].y, xa[mt][1].y,
+                                       wb[nt].x, wb[nt].y);
                 }
-            }
-        } else if (ENGINE == ENG_B1) {
-            const int steps = (words + 3) / 4;  // 4 words = 256 bits per MMA; the tail words are zero
-            for (int s = 0; s < steps; s++) {
-                uint2 xa[4][2], wb[8];
+            } else {
+                for (int wd = 0; wd < words; wd++) {
+                    unsigned long long xr[4][2], wc[8][2];
 #pragma unroll
-                for (int mt = 0; mt < 4; mt++) {
-                    const int r = wm * 64 + mt * 16 + g;
-                    xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + (s * 4 + tig) * 2);
-                    xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + (s * 4 + tig) * 2);
-                }
-#pragma unroll
-                for (int nt = 0; nt < 8; nt++)
-                    wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + (s * 4 + tig) * 2);
-#pragma unroll
-                for (int mt = 0; mt < 4; mt++)
+                    for (int mt = 0; mt < 4; mt++) {
+                        const int r = wm * 64 + mt * 16 + g;
+                        xr[mt][0] = *reinterpret_cast<const unsigned long long*>(Xs + r * PITCH32 + wd * 2);
+                        xr[mt][1] = *reinterpret_cast<const unsigned long long*>(Xs + (r + 8) * PITCH32 + wd * 2);
+                    }
 #pragma unroll
                     for (int nt = 0; nt < 8; nt++)
-                        mma_b1_and(&acc[(mt * 8 + nt) * 4], xa[mt][0].x, xa[mt][1].x, xa[mt][0].y, xa[mt][1].y, wb[nt].x,
-                                   wb[nt].y);
+#pragma unroll
+                        for (int q = 0; q < 2; q++)
+                            wc[nt][q] = *reinterpret_cast<const unsigned long long*>(
+                                Ws + (wn * 64 + nt * 8 + tig * 2 + q) * PITCH32 + wd * 2);
+#pragma unroll
+                    for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+                        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                            for (int h = 0; h < 2; h++)
+#pragma unroll
+                                for (int q = 0; q < 2; q++)
+                                    acc[(mt * 8 + nt) * 4 + h * 2 + q] += __popcll(xr[mt][h] ^ wc[nt][q]);
+                }
             }
-        } else {
-            for (int wd = 0; wd < words; wd++) {
-                unsigned long long xr[PR], wc[PC];
+        }
+
+        if (MMA) {
 #pragma unroll
-                for (int i = 0; i < PR; i++)
-                    xr[i] = *reinterpret_cast<const unsigned long long*>(Xs + (i * (NT / 8) + ty) * PITCH32 + wd * 2);
+            for (int i = 0; i < POPROWS; i++) {
+                const int r = tid + i * NT;
+                if (r < ROWS) rowpop[r] = mypop[i];
+            }
+            __syncthreads();
+        }
+
+        // ---- epilogue, straight from the accumulator fragments ----
+        const int m0 = tile * TM + wm * 64;
+        int pw[16];
+        if (MMA) {
 #pragma unroll
-                for (int j = 0; j < PC; j++)
-                    wc[j] = *reinterpret_cast<const unsigned long long*>(Ws + (j * 8 + tx) * PITCH32 + wd * 2);
+            for (int nt = 0; nt < 8; nt++) {
+                pw[nt * 2] = rowpop[TM + wn * 64 + nt * 8 + tig * 2];
+                pw[nt * 2 + 1] = rowpop[TM + wn * 64 + nt * 8 + tig * 2 + 1];
+            }
+        }
 #pragma unroll
-                for (int i = 0; i < PR; i++)
+        for (int mt = 0; mt < 4; mt++) {
+            const int rloc = wm * 64 + mt * 16 + g;
+            const int row0 = m0 + mt * 16 + g, row1 = row0 + 8;
+            const bool ok0 = row0 < M, ok1 = row1 < M;
+            float2 ad[2][8];
+            if (addsrc && vec2) {
 #pragma unroll
-                    for (int j = 0; j < PC; j++) acc[i * PC + j] += __popcll(xr[i] ^ wc[j]);
+                for (int nt = 0; nt < 8; nt++) {
+                    const int col = colbase + nt * 8;
+                    ad[0][nt] = (ok0 && col < N) ? __ldcs(reinterpret_cast<const float2*>(addsrc + (long long)row0 * ld_add + col))
+                                                 : make_float2(0.f, 0.f);
+                    ad[1][nt] = (ok1 && col < N) ? __ldcs(reinterpret_cast<const float2*>(addsrc + (long long)row1 * ld_add + col))
+                                                 : make_float2(0.f, 0.f);
+                }
+            }
+            int px[2] = {0, 0};
+            if (MMA) { px[0] = rowpop[rloc]; px[1] = rowpop[rloc + 8]; }
+            unsigned lo[2] = {0u, 0u}, hi[2] = {0u, 0u};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int row = h ? row1 : row0;
+                const bool ok = h ? ok1 : ok0;
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++) {
+                    const int col = colbase + nt * 8;
+                    float v[2];
+                    const float2 sa = *reinterpret_cast<const float2*>(chan_a + wn * 64 + nt * 8 + tig * 2);
+                    const float2 sb = *reinterpret_cast<const float2*>(chan_b + wn * 64 + nt * 8 + tig * 2);
+#pragma unroll
+                    for (int q = 0; q < 2; q++) {
+                        const int raw = acc[(mt * 8 + nt) * 4 + h * 2 + q];
+                        const int cnt = MMA ? px[h] + pw[nt * 2 + q] - 2 * raw : raw;
+                        v[q] = small_int_to_float(cnt);
+                        if (ep.a) v[q] = __fadd_rn(__fmul_rn(q ? sa.y : sa.x, v[q]), q ? sb.y : sb.x);
+                    }
+                    if (ok && col < N) {
+                        if (vec2) {
+                            if (addsrc) { v[0] = __fadd_rn(ad[h][nt].x, v[0]); v[1] = __fadd_rn(ad[h][nt].y, v[1]); }
+                            if (ep.out) __stcs(reinterpret_cast<float2*>(ep.out + (long long)row * ep.ld_out + col), make_float2(v[0], v[1]));
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 2; q++) {
+                                if (col + q >= N) continue;
+                                if (addsrc) v[q] = __fadd_rn(addsrc[(long long)row * ld_add + col + q], v[q]);
+                                if (ep.out) ep.out[(long long)row * ep.ld_out + col + q] = v[q];
+                            }
+                        }
+                        const unsigned b2 = (v[0] > 0.f ? 1u : 0u) | (v[1] > 0.f ? 2u : 0u);
+                        if (nt < 4) lo[h] |= b2 << (nt * 8 + tig * 2);
+                        else hi[h] |= b2 << ((nt - 4) * 8 + tig * 2);
+                    }
+                }
+            }
+            if (ep.bits) {  // a quad holds the 64 channels of a row: OR the four lanes together
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    lo[h] |= __shfl_xor_sync(0xffffffffu, lo[h], 1);
+                    hi[h] |= __shfl_xor_sync(0xffffffffu, hi[h], 1);
+                    lo[h] |= __shfl_xor_sync(0xffffffffu, lo[h], 2);
+                    hi[h] |= __shfl_xor_sync(0xffffffffu, hi[h], 2);
+                }
+                const int wcol = (n0 + wn * 64) >> 6;
+                if (tig == 0 && n0 + wn * 64 < N) {
+                    if (ok0) ep.bits[(long long)row0 * ep.ld_bits + wcol] = ((unsigned long long)hi[0] << 32) | lo[0];
+                    if (ok1) ep.bits[(long long)row1 * ep.ld_bits + wcol] = ((unsigned long long)hi[1] << 32) | lo[1];
+                }
             }
         }
     }
     cp_async_wait<0>();
-    __syncthreads();  // every thread is done with the pipeline buffers: reuse them for the count tile
-
-    if (MMA) {
-#pragma unroll
-        for (int i = 0; i < POPROWS; i++) {
-            const int r = tid + i * NT;
-            if (r < ROWS) rowpop[r] = mypop[i];
-        }
-        __syncthreads();
-    }
-    int* ct = reinterpret_cast<int*>(smem_raw);
-    if (MMA) {
-#pragma unroll
-        for (int mt = 0; mt < 4; mt++) {
-            const int r = wm * 64 + mt * 16 + g;
-            const int px0 = rowpop[r], px1 = rowpop[r + 8];
-#pragma unroll
-            for (int nt = 0; nt < 8; nt++) {
-                const int c = wn * 64 + nt * 8 + tig * 2;
-                const int pw0 = rowpop[TM + c], pw1 = rowpop[TM + c + 1];
-                const int* d = &acc[(mt * 8 + nt) * 4];
-                int2 v0, v1;
-                v0.x = px0 + pw0 - 2 * d[0];
-                v0.y = px0 + pw1 - 2 * d[1];
-                v1.x = px1 + pw0 - 2 * d[2];
-                v1.y = px1 + pw1 - 2 * d[3];
-                *reinterpret_cast<int2*>(ct + r * Cfg::CPITCH + c) = v0;
-                *reinterpret_cast<int2*>(ct + (r + 8) * Cfg::CPITCH + c) = v1;
-            }
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < PR; i++)
-#pragma unroll
-            for (int j = 0; j < PC; j++) ct[(i * (NT / 8) + ty) * Cfg::CPITCH + j * 8 + tx] = acc[i * PC + j];
-    }
-    __syncthreads();
-
-    // Cooperative epilogue: a thread owns 4 consecutive channels of one row per item and handles
-    // EU items per round so that EU independent 16-byte loads are in flight before any is used.
-    constexpr int C4 = TN / 4, EU = 8;
-    const bool vec_ok = (N % 4 == 0) && (!ep.out || (ep.ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0)) &&
-                        (!ep.shortcut || (ep.ld_sc % 4 == 0 && (reinterpret_cast<uintptr_t>(ep.shortcut) & 15) == 0));
-    const int c = (tid % C4) * 4, col = n0 + c;   // NT is a multiple of C4: a thread keeps its channels
-    const bool col_ok = col < N;
-    const int nvalid = min(4, N - col);
-    float av[4] = {1.f, 1.f, 1.f, 1.f}, bv[4] = {0.f, 0.f, 0.f, 0.f};
-    if (ep.a && col_ok) {
-#pragma unroll
-        for (int q = 0; q < 4; q++)
-            if (q < nvalid) { av[q] = __ldg(ep.a + col + q); bv[q] = __ldg(ep.b + col + q); }
-    }
-    for (int it0 = tid; it0 < TM * C4; it0 += NT * EU) {
-        float4 add4[EU];
-        if (vec_ok && col_ok && (ep.shortcut || ep.accumulate)) {
-            const float* src = ep.shortcut ? ep.shortcut : ep.out;
-            const long long lds = ep.shortcut ? ep.ld_sc : ep.ld_out;
-#pragma unroll
-            for (int u = 0; u < EU; u++) {
-                const int row = m0 + (it0 + u * NT) / C4;
-                add4[u] = row < M ? __ldcs(reinterpret_cast<const float4*>(src + (long long)row * lds + col))
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < EU; u++) {
-            const int r = (it0 + u * NT) / C4, row = m0 + r;
-            const int4 cnt = *reinterpret_cast<const int4*>(ct + r * Cfg::CPITCH + c);
-            float v[4] = {small_int_to_float(cnt.x), small_int_to_float(cnt.y), small_int_to_float(cnt.z),
-                          small_int_to_float(cnt.w)};
-            const bool ok = row < M && col_ok;
-            unsigned nib = 0;
-            if (ok) {
-                if (ep.a) {
-#pragma unroll
-                    for (int q = 0; q < 4; q++) v[q] = __fadd_rn(__fmul_rn(av[q], v[q]), bv[q]);
-                }
-                if (vec_ok) {
-                    if (ep.shortcut || ep.accumulate) {
-                        v[0] = __fadd_rn(add4[u].x, v[0]); v[1] = __fadd_rn(add4[u].y, v[1]);
-                        v[2] = __fadd_rn(add4[u].z, v[2]); v[3] = __fadd_rn(add4[u].w, v[3]);
-                    }
-                    if (ep.out)
-                        __stcs(reinterpret_cast<float4*>(ep.out + (long long)row * ep.ld_out + col),
-                               make_float4(v[0], v[1], v[2], v[3]));
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        if (q >= nvalid) continue;
-                        if (ep.shortcut) v[q] = __fadd_rn(v[q], ep.shortcut[(long long)row * ep.ld_sc + col + q]);
-                        if (ep.out) {
-                            float* op = ep.out + (long long)row * ep.ld_out + col + q;
-                            *op = ep.accumulate ? __fadd_rn(*op, v[q]) : v[q];
-                        }
-                    }
-                }
-                nib = (v[0] > 0.f ? 1u : 0u) | (v[1] > 0.f ? 2u : 0u) | (v[2] > 0.f ? 4u : 0u) | (v[3] > 0.f ? 8u : 0u);
-            }
-            if (ep.bits) {  // 16 consecutive lanes hold the 64 channels of one word (uniform branch)
-                const int sub = lane & 15;
-                unsigned lo = sub < 8 ? nib << (4 * sub) : 0u, hi = sub >= 8 ? nib << (4 * (sub - 8)) : 0u;
-#pragma unroll
-                for (int off = 1; off < 16; off <<= 1) {
-                    lo |= __shfl_xor_sync(0xffffffffu, lo, off);
-                    hi |= __shfl_xor_sync(0xffffffffu, hi, off);
-                }
-                if (sub == 0 && ok) ep.bits[(long long)row * ep.ld_bits + (col >> 6)] = ((unsigned long long)hi << 32) | lo;
-            }
-        }
-    }
 }
 
 // Host-side launcher: picks the tile shape from N and dispatches on the engine.

@@ -1,5 +1,7 @@
 // C-ABI entry points built on the binary contraction core: bgemm, bconv, the fused residual
 // block and the BinConv operator.
+#include <algorithm>
+
 #include "bcontract.cuh"
 #include "kernels.h"
 
@@ -18,8 +20,11 @@ static int launch_one(const XOp& xop, const WOp& wop, const EpilogueParams& ep, 
                                            (int)Cfg::SMEM_BYTES));
         configured_device = dev;
     }
-    dim3 grid((M + Cfg::TM - 1) / Cfg::TM, (N + Cfg::TN - 1) / Cfg::TN);
-    kern<<<grid, Cfg::NT, Cfg::SMEM_BYTES, stream>>>(xop, wop, ep, M, N, kwords);
+    // persistent CTAs: two per SM in total, spread over the channel tiles
+    const int tiles_m = (M + Cfg::TM - 1) / Cfg::TM, tiles_n = (N + Cfg::TN - 1) / Cfg::TN;
+    const int per_n = std::max(1, 2 * sm_count() / tiles_n);
+    dim3 grid(std::min(tiles_m, per_n), tiles_n);
+    kern<<<grid, Cfg::NT, Cfg::SMEM_BYTES, stream>>>(xop, wop, ep, M, N, kwords, tiles_m);
     return check_launch("bcontract_kernel");
 }
 

@@ -208,79 +208,189 @@ __global__ void concat_kernel(const float* __restrict__ x1, int c1, const float*
 }
 
 // ---- float convolution -----------------------------------------------------------------------------
-// Implicit-GEMM on CUDA cores in fp32: C[pixel][cout] = sum_k A[pixel][k] * W[cout][k],
-// k = (ky*kw + kx)*cin + ci.  64x64 tile per CTA, 16-deep K slices in shared memory, 4x4 outputs
-// per thread.  The epilogue adds the bias and can apply a per-channel affine and a relu.
-constexpr int FT = 64, FK = 16;
-__global__ void __launch_bounds__(256) fconv_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
+// Implicit GEMM  C[pixel][cout] = sum_k A[pixel][k] * W[cout][k],  k = (ky*kw + kx)*cin + ci, on the
+// tensor cores with fp32-grade accuracy: every fp32 operand is split into a TF32 head and a TF32
+// tail (x = hi + lo, 21+ significant bits) and each product is formed as lo*hi + hi*lo + hi*hi
+// with mma.sync.m16n8k8 TF32 MMAs accumulating in fp32 ("3xTF32").  The dropped lo*lo term is
+// below 2^-22 relative, i.e. the result differs from an fp32 FMA chain by summation order only.
+// CTA tile 128 pixels x 64 channels, 4 warps of 32 x 64, K slices of 16 staged in shared memory
+// (register double buffering).  The epilogue adds the bias and can apply a per-channel affine
+// (product and sum rounded separately, like the Affine layer) and a relu.
+constexpr int FTM = 128, FTN = 64, FKC = 16, FPITCH = FKC + 4;
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float* d, const uint32_t* a, const uint32_t* b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128) fconv_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
                                                     const float* __restrict__ bias, const float* __restrict__ a,
                                                     const float* __restrict__ b, int relu, float* __restrict__ out,
                                                     int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
                                                     int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, int oh,
                                                     int ow) {
-    __shared__ float As[FK][FT + 4];
-    __shared__ float Bs[FK][FT + 4];
+    __shared__ __align__(16) float As[FTM * FPITCH];
+    __shared__ __align__(16) float Bs[FTN * FPITCH];
     const int K = kh * kw * cin, M = n * oh * ow;
-    const int m0 = blockIdx.x * FT, n0 = blockIdx.y * FT;
-    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    // loader: thread -> (tile row = tid / 4, k offsets (tid % 4) * 4 .. +3)
-    const int lr = tid >> 2, lk = (tid & 3) * 4;
-    const int pm = m0 + lr;
-    int img = 0, iy0 = 0, ix0 = 0;
-    const bool prow = pm < M;
-    if (prow) {
-        img = pm / (oh * ow);
-        const int rem = pm - img * (oh * ow);
-        const int oy = rem / ow, ox = rem - oy * ow;
-        iy0 = oy * stride_h - pad_h;
-        ix0 = ox * stride_w - pad_w;
-    }
-    const int wn = n0 + lr;
-    float acc[4][4] = {};
-    for (int k0 = 0; k0 < K; k0 += FK) {
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int k = k0 + lk + q;
-            float av = 0.f, bv = 0.f;
-            if (k < K) {
-                if (prow) {
-                    const int tap = k / cin, ci = k - tap * cin;
-                    const int ky = tap / kw, kx = tap - ky * kw;
-                    const int y = iy0 + ky * dil_h, x = ix0 + kx * dil_w;
-                    if (y >= 0 && y < h && x >= 0 && x < w) av = __ldg(in + (((size_t)img * h + y) * w + x) * cin + ci);
-                }
-                if (wn < cout) bv = __ldg(wgt + (size_t)wn * K + k);
-            }
-            As[lk + q][lr] = av;
-            Bs[lk + q][lr] = bv;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int kk = 0; kk < FK; kk++) {
-            const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
-            const float4 bv = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
-            const float ar[4] = {av.x, av.y, av.z, av.w}, br[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
-        }
-        __syncthreads();
-    }
+    const int m0 = blockIdx.x * FTM, n0 = blockIdx.y * FTN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+    // loader: thread -> k quad (tid & 3) of the slice, rows (tid >> 2) + 32*i
+    const int kq = (tid & 3) * 4, lr = tid >> 2;
+    long long abase[4];
+    int aiy[4], aix[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const int row = m0 + ty * 4 + i;
-        if (row >= M) continue;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int col = n0 + tx * 4 + j;
-            if (col >= cout) continue;
-            float v = acc[i][j];
-            if (bias) v = __fadd_rn(v, __ldg(bias + col));
-            if (a) v = __fadd_rn(__fmul_rn(__ldg(a + col), v), __ldg(b + col));
-            if (relu) v = relu_ref(v);
-            out[(size_t)row * cout + col] = v;
+        const int pm = m0 + lr + 32 * i;
+        if (pm < M) {
+            const int img = pm / (oh * ow), rem = pm - img * (oh * ow);
+            const int oy = rem / ow, ox = rem - oy * ow;
+            abase[i] = (long long)img * h * w;
+            aiy[i] = oy * stride_h - pad_h;
+            aix[i] = ox * stride_w - pad_w;
+        } else {
+            abase[i] = 0; aiy[i] = -(1 << 28); aix[i] = 0;   // every tap out of range -> zeros
         }
+    }
+    const bool vec4 = (cin % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    const bool wvec4 = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(wgt) & 15) == 0);
+    float ra[4][4], rb[2][4];
+
+    auto gload = [&](int k0) {
+        const int k = k0 + kq;
+        int ky[4], kx[4], ci[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int kk = k + q, tap = kk / cin;
+            ci[q] = kk - tap * cin;
+            ky[q] = (tap / kw);
+            kx[q] = (tap - ky[q] * kw) * dil_w;
+            ky[q] *= dil_h;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (vec4 && k + 3 < K) {   // the four k share one tap: one 16-byte load
+                const int y = aiy[i] + ky[0], x = aix[i] + kx[0];
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if ((unsigned)y < (unsigned)h && (unsigned)x < (unsigned)w)
+                    v = __ldg(reinterpret_cast<const float4*>(in + (abase[i] + (long long)y * w + x) * cin + ci[0]));
+                ra[i][0] = v.x; ra[i][1] = v.y; ra[i][2] = v.z; ra[i][3] = v.w;
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int y = aiy[i] + ky[q], x = aix[i] + kx[q];
+                    float v = 0.f;
+                    if (k + q < K && (unsigned)y < (unsigned)h && (unsigned)x < (unsigned)w)
+                        v = __ldg(in + (abase[i] + (long long)y * w + x) * cin + ci[q]);
+                    ra[i][q] = v;
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int wn = n0 + lr + 32 * i;
+            if (wvec4 && wn < cout && k + 3 < K) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(wgt + (size_t)wn * K + k));
+                rb[i][0] = v.x; rb[i][1] = v.y; rb[i][2] = v.z; rb[i][3] = v.w;
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; q++) rb[i][q] = (wn < cout && k + q < K) ? __ldg(wgt + (size_t)wn * K + k + q) : 0.f;
+            }
+        }
+    };
+    auto sstore = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            *reinterpret_cast<float4*>(&As[(lr + 32 * i) * FPITCH + kq]) = make_float4(ra[i][0], ra[i][1], ra[i][2], ra[i][3]);
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+            *reinterpret_cast<float4*>(&Bs[(lr + 32 * i) * FPITCH + kq]) = make_float4(rb[i][0], rb[i][1], rb[i][2], rb[i][3]);
+    };
+
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) acc[i][j][q] = 0.f;
+
+    gload(0);
+    for (int k0 = 0; k0 < K; k0 += FKC) {
+        __syncthreads();   // the previous slice has been consumed
+        sstore();
+        __syncthreads();
+        if (k0 + FKC < K) gload(k0 + FKC);   // overlaps the MMAs below
+#pragma unroll
+        for (int ks = 0; ks < FKC; ks += 8) {
+            uint32_t ahi[2][4], alo[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                const float* ap = &As[(warp * 32 + mt * 16 + g) * FPITCH + ks + tig];
+                const float v[4] = {ap[0], ap[8 * FPITCH], ap[4], ap[8 * FPITCH + 4]};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    ahi[mt][q] = to_tf32(v[q]);
+                    alo[mt][q] = to_tf32(v[q] - __uint_as_float(ahi[mt][q]));
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const float* bp = &Bs[(nt * 8 + g) * FPITCH + ks + tig];
+                const float v[2] = {bp[0], bp[4]};
+                uint32_t bhi[2], blo[2];
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    bhi[q] = to_tf32(v[q]);
+                    blo[q] = to_tf32(v[q] - __uint_as_float(bhi[q]));
+                }
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    mma_tf32(acc[mt][nt], alo[mt], bhi);
+                    mma_tf32(acc[mt][nt], ahi[mt], blo);
+                    mma_tf32(acc[mt][nt], ahi[mt], bhi);
+                }
+            }
+        }
+    }
+    // epilogue straight from the fragments: thread holds (row g / g+8, cols 2*tig, 2*tig+1) per tile
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) {
+        const int col = n0 + nt * 8 + tig * 2;
+        float bb[2] = {0.f, 0.f}, ca[2] = {1.f, 1.f}, cb[2] = {0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < 2; q++)
+            if (col + q < cout) {
+                if (bias) bb[q] = __ldg(bias + col + q);
+                if (a) { ca[q] = __ldg(a + col + q); cb[q] = __ldg(b + col + q); }
+            }
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const int row = m0 + warp * 32 + mt * 16 + g + hh * 8;
+                if (row >= M) continue;
+                float v[2] = {acc[mt][nt][hh * 2], acc[mt][nt][hh * 2 + 1]};
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    if (bias) v[q] = __fadd_rn(v[q], bb[q]);
+                    if (a) v[q] = __fadd_rn(__fmul_rn(ca[q], v[q]), cb[q]);
+                    if (relu) v[q] = relu_ref(v[q]);
+                }
+                float* op = out + (size_t)row * cout + col;
+                if (col + 1 < cout && (cout & 1) == 0) {
+                    *reinterpret_cast<float2*>(op) = make_float2(v[0], v[1]);
+                } else {
+                    if (col < cout) op[0] = v[0];
+                    if (col + 1 < cout) op[1] = v[1];
+                }
+            }
     }
 }
 
@@ -295,8 +405,9 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     const int oh = conv_out_dim(h, pad_h, dil_h, kh, stride_h), ow = conv_out_dim(w, pad_w, dil_w, kw, stride_w);
     DABNN_REQUIRE(oh > 0 && ow > 0, DABNN_ERR_SHAPE, "fconv: empty output");
     DABNN_REQUIRE((long long)n * oh * ow < (1ll << 31), DABNN_ERR_SHAPE, "fconv: too many output pixels");
-    dim3 grid((n * oh * ow + FT - 1) / FT, (cout + FT - 1) / FT);
-    fconv_kernel<<<grid, 256, 0, stream>>>(in, weight, bias, a, b, relu, out, n, h, w, cin, cout, kh, kw, pad_h,
+    DABNN_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7) == 0, DABNN_ERR_ARG, "fconv: output must be 8-byte aligned");
+    dim3 grid((n * oh * ow + FTM - 1) / FTM, (cout + FTN - 1) / FTN);
+    fconv_kernel<<<grid, 128, 0, stream>>>(in, weight, bias, a, b, relu, out, n, h, w, cin, cout, kh, kw, pad_h,
                                            pad_w, stride_h, stride_w, dil_h, dil_w, oh, ow);
     return check_launch("fconv_kernel");
 }

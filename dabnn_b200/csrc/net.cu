@@ -85,11 +85,18 @@ struct NetImpl {
     std::vector<std::string> outputs;
 
     unsigned char* arena = nullptr;
-    size_t arena_bytes = 0, weights_bytes = 0;
+    size_t arena_bytes = 0, weights_bytes = 0, arena_bytes_extra = 0;
     unsigned char* weights = nullptr;
-    const float* cur_input = nullptr;  // device pointer of the current run's input
+    const float* cur_input = nullptr;  // device pointer of the images the plan is currently reading
     int cur_batch = 0;
     int input_blob = -1;
+    size_t out_offset = 0;             // first image of the sub-batch being computed (kept blobs are full-batch)
+
+    // host inputs are streamed in sub-batches: copy of sub-batch k+1 overlaps the kernels of k
+    static constexpr int kHostChunk = 256;
+    cudaStream_t copy_stream = nullptr;
+    float* staging[2] = {nullptr, nullptr};
+    cudaEvent_t copied[2] = {nullptr, nullptr}, consumed[2] = {nullptr, nullptr};
 
     std::vector<cudaEvent_t> events;
     std::vector<std::string> time_names;
@@ -97,6 +104,12 @@ struct NetImpl {
 
     ~NetImpl() {
         for (auto e : events) cudaEventDestroy(e);
+        for (int i = 0; i < 2; i++) {
+            if (copied[i]) cudaEventDestroy(copied[i]);
+            if (consumed[i]) cudaEventDestroy(consumed[i]);
+            if (staging[i]) cudaFree(staging[i]);
+        }
+        if (copy_stream) cudaStreamDestroy(copy_stream);
         if (arena) cudaFree(arena);
         if (weights) cudaFree(weights);
         if (stream) cudaStreamDestroy(stream);
@@ -105,11 +118,17 @@ struct NetImpl {
     int parse(const uint8_t* buf, size_t len);
     int build();
     int run(const float* input, int batch, bool is_device);
+    int run_plan(int batch);
+    // blobs that outlive the run hold the whole batch; everything else is reused per sub-batch
     float* f32(int blob) const {
-        if (blob == input_blob && cur_input) return const_cast<float*>(cur_input);
-        return reinterpret_cast<float*>(arena + blobs[blob].f32_off);
+        if (blob == input_blob) return const_cast<float*>(cur_input);
+        const Blob& b = blobs[blob];
+        return reinterpret_cast<float*>(arena + b.f32_off) + (b.keep ? out_offset * b.per_image() : 0);
     }
-    uint64_t* bits(int blob) const { return reinterpret_cast<uint64_t*>(arena + blobs[blob].bits_off); }
+    uint64_t* bits(int blob) const {
+        const Blob& b = blobs[blob];
+        return reinterpret_cast<uint64_t*>(arena + b.bits_off) + (b.keep ? out_offset * b.h * b.w * (b.c / 64) : 0);
+    }
 };
 
 // -------------------------------------------------------------------------------------------------
@@ -507,11 +526,15 @@ int NetImpl::build() {
         const Blob& b = blobs[i];
         if (b.def_op < 0) continue;
         const int last = b.keep ? (int)plan.size() : b.last_use;
+        if (i == input_blob && !b.need_bits) continue;   // read in place (device input or staging buffer)
         const size_t fbytes = ((size_t)max_batch * b.per_image() * 4 + 255) / 256 * 256;
-        items.push_back({i, false, fbytes, b.def_op, last, 0});
+        // a kept blob holds the whole batch across sub-batch executions of the plan, so its memory
+        // is never shared with another blob
+        const int first = b.keep ? 0 : b.def_op;
+        if (i != input_blob) items.push_back({i, false, fbytes, first, last, 0});
         if (b.need_bits) {
             const size_t bb = ((size_t)max_batch * b.h * b.w * (b.c / 64) * 8 + 255) / 256 * 256;
-            items.push_back({i, true, bb, b.def_op, last, 0});
+            items.push_back({i, true, bb, first, last, 0});
         }
     }
     // BinConvIm2col scratch: one shared region sized for the largest user
@@ -551,6 +574,19 @@ int NetImpl::build() {
         cudaGetLastError();
         return fail(DABNN_ERR_OOM, "cannot allocate a " + std::to_string(arena_bytes) + " byte device arena");
     }
+    {   // double-buffered staging for host inputs
+        const size_t sb = (size_t)std::min(max_batch, kHostChunk) * in_h * in_w * in_c * sizeof(float);
+        DABNN_CUDA_OK(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; i++) {
+            if (cudaMalloc(&staging[i], sb) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(DABNN_ERR_OOM, "cannot allocate the input staging buffers");
+            }
+            DABNN_CUDA_OK(cudaEventCreateWithFlags(&copied[i], cudaEventDisableTiming));
+            DABNN_CUDA_OK(cudaEventCreateWithFlags(&consumed[i], cudaEventDisableTiming));
+        }
+        arena_bytes_extra = 2 * sb;
+    }
     if (profiling) {
         events.resize(plan.size() + 1);
         for (auto& e : events) DABNN_CUDA_OK(cudaEventCreate(&e));
@@ -567,13 +603,43 @@ int NetImpl::run(const float* input, int batch, bool is_device) {
                   "run: batch must be between 1 and the configured max_batch");
     DABNN_CUDA_OK(cudaSetDevice(device));
     cur_batch = batch;
-    const size_t in_bytes = (size_t)batch * in_h * in_w * in_c * sizeof(float);
+    const size_t img_floats = (size_t)in_h * in_w * in_c;
     if (is_device) {
         cur_input = input;
-    } else {
-        cur_input = nullptr;
-        DABNN_CUDA_OK(cudaMemcpyAsync(f32(input_blob), input, in_bytes, cudaMemcpyHostToDevice, stream));
+        out_offset = 0;
+        return run_plan(batch);
     }
+    // host input: sub-batches through two staging buffers; the copy of sub-batch k+1 is issued
+    // before the kernels of sub-batch k so that PCIe transfer and compute overlap
+    const int chunk = std::min(max_batch, kHostChunk);
+    const int nchunks = (batch + chunk - 1) / chunk;
+    auto issue_copy = [&](int k) -> int {
+        const int i0 = k * chunk, cnt = std::min(chunk, batch - i0), sb = k & 1;
+        if (k >= 2) DABNN_CUDA_OK(cudaStreamWaitEvent(copy_stream, consumed[sb], 0));
+        DABNN_CUDA_OK(cudaMemcpyAsync(staging[sb], input + (size_t)i0 * img_floats, (size_t)cnt * img_floats * sizeof(float),
+                                      cudaMemcpyHostToDevice, copy_stream));
+        DABNN_CUDA_OK(cudaEventRecord(copied[sb], copy_stream));
+        return DABNN_OK;
+    };
+    // the staging buffers may still be read by the previous run's kernels
+    DABNN_CUDA_OK(cudaEventRecord(consumed[0], stream));
+    DABNN_CUDA_OK(cudaStreamWaitEvent(copy_stream, consumed[0], 0));
+    int rc = issue_copy(0);
+    for (int k = 0; k < nchunks && rc == DABNN_OK; k++) {
+        if (k + 1 < nchunks) rc = issue_copy(k + 1);
+        if (rc) break;
+        const int i0 = k * chunk, cnt = std::min(chunk, batch - i0), sb = k & 1;
+        DABNN_CUDA_OK(cudaStreamWaitEvent(stream, copied[sb], 0));
+        cur_input = staging[sb];
+        out_offset = (size_t)i0;
+        rc = run_plan(cnt);
+        DABNN_CUDA_OK(cudaEventRecord(consumed[sb], stream));
+    }
+    out_offset = 0;
+    return rc;
+}
+
+int NetImpl::run_plan(int batch) {
     const int eng = optimize ? engine : DABNN_ENGINE_POPC;
     int rc = DABNN_OK;
     for (size_t i = 0; i < plan.size() && rc == DABNN_OK; i++) {
@@ -713,7 +779,9 @@ extern "C" int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4],
     auto it = n.blob_of.find(name);
     if (it == n.blob_of.end()) return fail(DABNN_ERR_NOT_FOUND, std::string("Key ") + name + " not found.");
     const Blob& b = n.blobs[it->second];
-    if (!(b.keep || it->second == n.input_blob))
+    if (it->second == n.input_blob)
+        return fail(DABNN_ERR_NOT_FOUND, std::string("blob ") + name + " is the caller's input; it is read in place and not kept");
+    if (!b.keep)
         return fail(DABNN_ERR_NOT_FOUND, std::string("blob ") + name + " is not materialised in the fused plan; read the model with optimize = 0 to keep every blob");
     const int batch = n.cur_batch > 0 ? n.cur_batch : 1;
     if (dims) { dims[0] = batch; dims[1] = b.h; dims[2] = b.w; dims[3] = b.c; }
@@ -736,7 +804,7 @@ extern "C" int dabnn_net_stats(dabnn_net* net, int* kernels_per_run, size_t* are
     int k = 0;
     for (const auto& o : net->impl.plan) k += o.kind == OpKind::BinConvIm2col ? 2 : 1;
     if (kernels_per_run) *kernels_per_run = k;
-    if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes;
+    if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes + net->impl.arena_bytes_extra;
     return DABNN_OK;
 }
 extern "C" int dabnn_net_set_profiling(dabnn_net* net, int on) {
