@@ -138,9 +138,10 @@ __device__ __forceinline__ float small_int_to_float(int v) {
     return __fsub_rn(__int_as_float(0x4B000000 | v), 8388608.0f);
 }
 
+// A CTA has WM x WN warps; every warp owns a 32-pixel x 64-channel sub-tile (2 x 8 MMA tiles).
 template <int WM, int WN>
 struct TileCfg {
-    static constexpr int TM = WM * 64, TN = WN * 64, NT = WM * WN * 32;
+    static constexpr int TM = WM * 32, TN = WN * 64, NT = WM * WN * 32;
     static constexpr int STAGE_U32 = (TM + TN) * PITCH32;
     static constexpr size_t PIPE_BYTES = (size_t)NSTAGES * STAGE_U32 * 4;
     // two sets of pixel-row contexts (current / next tile), one set of channel-row contexts, row popcounts
@@ -179,17 +180,19 @@ __device__ __forceinline__ void load_rows(const Op& op, const RowCtx* ctx, uint3
 }
 
 // Persistent kernel.  CTA (bx, by) owns channel tile `by` and walks pixel tiles bx, bx + gridDim.x,
-// ...; each tile is TM pixels x TN channels, each of the 4 warps a 64 x 64 sub-tile.  While a tile
-// is being computed and written out, the first K chunk of the next tile is already in flight, so
-// neither the operand loads nor the output traffic sit on the critical path of the MMAs of the
-// co-resident CTA.
+// ...; each tile is TM pixels x TN channels, each of the 8 warps a 32 x 64 sub-tile.  While a tile
+// is being computed and written out, the first K chunk of the next tile is already in flight.
+// Two CTAs (16 warps) share an SM; the register budget is 128 per thread.
 //
 // Accumulator layout (all engines): acc[(mt*8 + nt)*4 + h*2 + q] is pixel row mt*16 + g + 8*h,
 // channel nt*8 + 2*tig + q of the warp's sub-tile (g = lane / 4, tig = lane % 4), the fragment
 // layout of mma.sync.  The epilogue works straight from these registers: per m-tile it first
 // issues all shortcut loads (16 independent 8-byte loads per thread), then converts, applies the
 // affine, adds, stores, and ORs the sign bits of a row together across the four lanes of a quad.
-template <int ENGINE, int WM, int WN, class XOp, class WOp>
+//
+// FAST = true assumes N % 8 == 0 and 8-byte aligned, even-pitched output / shortcut rows (every
+// network layer); FAST = false handles any N and alignment with scalar accesses.
+template <int ENGINE, int WM, int WN, bool FAST, class XOp, class WOp>
 __global__ void __launch_bounds__(WM* WN * 32, 2)
     bcontract_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
                      const int kwords, const int ntiles_m) {
@@ -233,12 +236,9 @@ __global__ void __launch_bounds__(WM* WN * 32, 2)
     issue(0, 0, 0);
     cp_async_commit();
 
-    // per-thread channel constants: 8 n-tiles x 2 channels
     const int colbase = n0 + wn * 64 + tig * 2;
     const float* addsrc = ep.shortcut ? ep.shortcut : (ep.accumulate ? ep.out : nullptr);
     const long long ld_add = ep.shortcut ? ep.ld_sc : ep.ld_out;
-    const bool vec2 = (N % 2 == 0) && (!ep.out || (ep.ld_out % 2 == 0 && (reinterpret_cast<uintptr_t>(ep.out) & 7) == 0)) &&
-                      (!addsrc || (ld_add % 2 == 0 && (reinterpret_cast<uintptr_t>(addsrc) & 7) == 0));
 
     constexpr int POPROWS = (ROWS + NT - 1) / NT;
     int item = 0;
@@ -249,9 +249,9 @@ __global__ void __launch_bounds__(WM* WN * 32, 2)
         if (has_next)
             for (int r = tid; r < TM; r += NT) xctx[(set ^ 1) * TM + r] = xop.make_row(next * TM + r);
 
-        int acc[128];
+        int acc[64];
 #pragma unroll
-        for (int i = 0; i < 128; i++) acc[i] = 0;
+        for (int i = 0; i < 64; i++) acc[i] = 0;
         int mypop[POPROWS];
 #pragma unroll
         for (int i = 0; i < POPROWS; i++) mypop[i] = 0;
@@ -264,8 +264,8 @@ __global__ void __launch_bounds__(WM* WN * 32, 2)
             cp_async_commit();
 
             const uint32_t* st = pipe + (item & 1) * Cfg::STAGE_U32;
-            const uint32_t* Xs = st;
-            const uint32_t* Ws = st + TM * PITCH32;
+            const uint32_t* Xs = st + (wm * 32 + g) * PITCH32;
+            const uint32_t* Ws = st + (TM + wn * 64 + g) * PITCH32;
             const int words = min(KC_WORDS, kwords - chunk * KC_WORDS);
 
             if (MMA) {  // row popcounts of both operands for the AND engines
@@ -286,22 +286,22 @@ __global__ void __launch_bounds__(WM* WN * 32, 2)
 
             if (ENGINE == ENG_IMMA) {
                 const uint32_t M1 = 0x01010101u;
+#pragma unroll 1
                 for (int wd = 0; wd < words; wd++) {
-                    uint2 xa[4][2], wb[8];
+                    uint2 xa[2][2], wb[8];
 #pragma unroll
-                    for (int mt = 0; mt < 4; mt++) {
-                        const int r = wm * 64 + mt * 16 + g;
-                        xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + wd * 2);
-                        xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + wd * 2);
+                    for (int mt = 0; mt < 2; mt++) {
+                        xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + (mt * 16) * PITCH32 + wd * 2);
+                        xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (mt * 16 + 8) * PITCH32 + wd * 2);
                     }
 #pragma unroll
                     for (int nt = 0; nt < 8; nt++)
-                        wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + wd * 2);
+                        wb[nt] = *reinterpret_cast<const uint2*>(Ws + (nt * 8) * PITCH32 + wd * 2);
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
-                        uint32_t af[4][4], bf[8][2];
+                        uint32_t af[2][4];
 #pragma unroll
-                        for (int mt = 0; mt < 4; mt++) {
+                        for (int mt = 0; mt < 2; mt++) {
                             const uint32_t c0 = (half ? xa[mt][0].y : xa[mt][0].x) >> tig;
                             const uint32_t c1 = (half ? xa[mt][1].y : xa[mt][1].x) >> tig;
                             af[mt][0] = c0 & M1;
@@ -312,60 +312,52 @@ __global__ void __launch_bounds__(WM* WN * 32, 2)
 #pragma unroll
                         for (int nt = 0; nt < 8; nt++) {
                             const uint32_t c = (half ? wb[nt].y : wb[nt].x) >> tig;
-                            bf[nt][0] = c & M1;
-                            bf[nt][1] = (c >> 4) & M1;
+                            const uint32_t b0 = c & M1, b1 = (c >> 4) & M1;
+#pragma unroll
+                            for (int mt = 0; mt < 2; mt++)
+                                mma_u8(&acc[(mt * 8 + nt) * 4], af[mt][0], af[mt][1], af[mt][2], af[mt][3], b0, b1);
                         }
-#pragma unroll
-                        for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-                            for (int nt = 0; nt < 8; nt++)
-                                mma_u8(&acc[(mt * 8 + nt) * 4], af[mt][0], af[mt][1], af[mt][2], af[mt][3], bf[nt][0], bf[nt][1]);
                     }
                 }
             } else if (ENGINE == ENG_B1) {
                 const int steps = (words + 3) / 4;  // 4 words = 256 bits per MMA; the tail words are zero
+#pragma unroll 1
                 for (int s = 0; s < steps; s++) {
-                    uint2 xa[4][2], wb[8];
+                    uint2 xa[2][2];
 #pragma unroll
-                    for (int mt = 0; mt < 4; mt++) {
-                        const int r = wm * 64 + mt * 16 + g;
-                        xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + r * PITCH32 + (s * 4 + tig) * 2);
-                        xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (r + 8) * PITCH32 + (s * 4 + tig) * 2);
+                    for (int mt = 0; mt < 2; mt++) {
+                        xa[mt][0] = *reinterpret_cast<const uint2*>(Xs + (mt * 16) * PITCH32 + (s * 4 + tig) * 2);
+                        xa[mt][1] = *reinterpret_cast<const uint2*>(Xs + (mt * 16 + 8) * PITCH32 + (s * 4 + tig) * 2);
                     }
 #pragma unroll
-                    for (int nt = 0; nt < 8; nt++)
-                        wb[nt] = *reinterpret_cast<const uint2*>(Ws + (wn * 64 + nt * 8 + g) * PITCH32 + (s * 4 + tig) * 2);
+                    for (int nt = 0; nt < 8; nt++) {
+                        const uint2 wb = *reinterpret_cast<const uint2*>(Ws + (nt * 8) * PITCH32 + (s * 4 + tig) * 2);
 #pragma unroll
-                    for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-                        for (int nt = 0; nt < 8; nt++)
-                            mma_b1_and(&acc[(mt * 8 + nt) * 4], xa[mt][0].x, xa[mt][1].x, xa[mt][0].y, xa[mt][1].y,
-                                       wb[nt].x, wb[nt].y);
+                        for (int mt = 0; mt < 2; mt++)
+                            mma_b1_and(&acc[(mt * 8 + nt) * 4], xa[mt][0].x, xa[mt][1].x, xa[mt][0].y, xa[mt][1].y, wb.x, wb.y);
+                    }
                 }
             } else {
+                const uint32_t* Wq = st + (TM + wn * 64 + tig * 2) * PITCH32;
+#pragma unroll 1
                 for (int wd = 0; wd < words; wd++) {
-                    unsigned long long xr[4][2], wc[8][2];
+                    unsigned long long xr[2][2];
 #pragma unroll
-                    for (int mt = 0; mt < 4; mt++) {
-                        const int r = wm * 64 + mt * 16 + g;
-                        xr[mt][0] = *reinterpret_cast<const unsigned long long*>(Xs + r * PITCH32 + wd * 2);
-                        xr[mt][1] = *reinterpret_cast<const unsigned long long*>(Xs + (r + 8) * PITCH32 + wd * 2);
+                    for (int mt = 0; mt < 2; mt++) {
+                        xr[mt][0] = *reinterpret_cast<const unsigned long long*>(Xs + (mt * 16) * PITCH32 + wd * 2);
+                        xr[mt][1] = *reinterpret_cast<const unsigned long long*>(Xs + (mt * 16 + 8) * PITCH32 + wd * 2);
                     }
 #pragma unroll
                     for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-                        for (int q = 0; q < 2; q++)
-                            wc[nt][q] = *reinterpret_cast<const unsigned long long*>(
-                                Ws + (wn * 64 + nt * 8 + tig * 2 + q) * PITCH32 + wd * 2);
+                        for (int q = 0; q < 2; q++) {
+                            const unsigned long long wc =
+                                *reinterpret_cast<const unsigned long long*>(Wq + (nt * 8 + q) * PITCH32 + wd * 2);
 #pragma unroll
-                    for (int mt = 0; mt < 4; mt++)
+                            for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-                        for (int nt = 0; nt < 8; nt++)
-#pragma unroll
-                            for (int h = 0; h < 2; h++)
-#pragma unroll
-                                for (int q = 0; q < 2; q++)
-                                    acc[(mt * 8 + nt) * 4 + h * 2 + q] += __popcll(xr[mt][h] ^ wc[nt][q]);
+                                for (int h = 0; h < 2; h++) acc[(mt * 8 + nt) * 4 + h * 2 + q] += __popcll(xr[mt][h] ^ wc);
+                        }
                 }
             }
         }
@@ -380,67 +372,63 @@ __global__ void __launch_bounds__(WM* WN * 32, 2)
         }
 
         // ---- epilogue, straight from the accumulator fragments ----
-        const int m0 = tile * TM + wm * 64;
-        int pw[16];
-        if (MMA) {
+        const int m0 = tile * TM + wm * 32;
+        const int* popw = rowpop + TM + wn * 64 + tig * 2;
+        const float* cha = chan_a + wn * 64 + tig * 2;
+        const float* chb = chan_b + wn * 64 + tig * 2;
 #pragma unroll
-            for (int nt = 0; nt < 8; nt++) {
-                pw[nt * 2] = rowpop[TM + wn * 64 + nt * 8 + tig * 2];
-                pw[nt * 2 + 1] = rowpop[TM + wn * 64 + nt * 8 + tig * 2 + 1];
-            }
-        }
-#pragma unroll
-        for (int mt = 0; mt < 4; mt++) {
-            const int rloc = wm * 64 + mt * 16 + g;
+        for (int mt = 0; mt < 2; mt++) {
+            const int rloc = wm * 32 + mt * 16 + g;
             const int row0 = m0 + mt * 16 + g, row1 = row0 + 8;
             const bool ok0 = row0 < M, ok1 = row1 < M;
             float2 ad[2][8];
-            if (addsrc && vec2) {
+            if (FAST && addsrc) {
+                const float* a0p = addsrc + (long long)row0 * ld_add + colbase;
+                const float* a1p = addsrc + (long long)row1 * ld_add + colbase;
 #pragma unroll
                 for (int nt = 0; nt < 8; nt++) {
-                    const int col = colbase + nt * 8;
-                    ad[0][nt] = (ok0 && col < N) ? __ldcs(reinterpret_cast<const float2*>(addsrc + (long long)row0 * ld_add + col))
-                                                 : make_float2(0.f, 0.f);
-                    ad[1][nt] = (ok1 && col < N) ? __ldcs(reinterpret_cast<const float2*>(addsrc + (long long)row1 * ld_add + col))
-                                                 : make_float2(0.f, 0.f);
+                    const bool cok = colbase + nt * 8 < N;
+                    ad[0][nt] = (ok0 && cok) ? __ldcs(reinterpret_cast<const float2*>(a0p + nt * 8)) : make_float2(0.f, 0.f);
+                    ad[1][nt] = (ok1 && cok) ? __ldcs(reinterpret_cast<const float2*>(a1p + nt * 8)) : make_float2(0.f, 0.f);
                 }
             }
             int px[2] = {0, 0};
             if (MMA) { px[0] = rowpop[rloc]; px[1] = rowpop[rloc + 8]; }
             unsigned lo[2] = {0u, 0u}, hi[2] = {0u, 0u};
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int row = h ? row1 : row0;
-                const bool ok = h ? ok1 : ok0;
+            for (int nt = 0; nt < 8; nt++) {
+                const int col = colbase + nt * 8;
+                int2 pw = make_int2(0, 0);
+                if (MMA) pw = *reinterpret_cast<const int2*>(popw + nt * 8);
+                const float2 sa = *reinterpret_cast<const float2*>(cha + nt * 8);
+                const float2 sb = *reinterpret_cast<const float2*>(chb + nt * 8);
 #pragma unroll
-                for (int nt = 0; nt < 8; nt++) {
-                    const int col = colbase + nt * 8;
-                    float v[2];
-                    const float2 sa = *reinterpret_cast<const float2*>(chan_a + wn * 64 + nt * 8 + tig * 2);
-                    const float2 sb = *reinterpret_cast<const float2*>(chan_b + wn * 64 + nt * 8 + tig * 2);
-#pragma unroll
-                    for (int q = 0; q < 2; q++) {
-                        const int raw = acc[(mt * 8 + nt) * 4 + h * 2 + q];
-                        const int cnt = MMA ? px[h] + pw[nt * 2 + q] - 2 * raw : raw;
-                        v[q] = small_int_to_float(cnt);
-                        if (ep.a) v[q] = __fadd_rn(__fmul_rn(q ? sa.y : sa.x, v[q]), q ? sb.y : sb.x);
+                for (int h = 0; h < 2; h++) {
+                    const int row = h ? row1 : row0;
+                    const bool ok = (h ? ok1 : ok0) && col < N;
+                    const int r0 = acc[(mt * 8 + nt) * 4 + h * 2], r1 = acc[(mt * 8 + nt) * 4 + h * 2 + 1];
+                    float v0 = small_int_to_float(MMA ? px[h] + pw.x - 2 * r0 : r0);
+                    float v1 = small_int_to_float(MMA ? px[h] + pw.y - 2 * r1 : r1);
+                    if (ep.a) {
+                        v0 = __fadd_rn(__fmul_rn(sa.x, v0), sb.x);
+                        v1 = __fadd_rn(__fmul_rn(sa.y, v1), sb.y);
                     }
-                    if (ok && col < N) {
-                        if (vec2) {
-                            if (addsrc) { v[0] = __fadd_rn(ad[h][nt].x, v[0]); v[1] = __fadd_rn(ad[h][nt].y, v[1]); }
-                            if (ep.out) __stcs(reinterpret_cast<float2*>(ep.out + (long long)row * ep.ld_out + col), make_float2(v[0], v[1]));
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 2; q++) {
-                                if (col + q >= N) continue;
-                                if (addsrc) v[q] = __fadd_rn(addsrc[(long long)row * ld_add + col + q], v[q]);
-                                if (ep.out) ep.out[(long long)row * ep.ld_out + col + q] = v[q];
-                            }
+                    if (FAST) {
+                        if (addsrc) { v0 = __fadd_rn(ad[h][nt].x, v0); v1 = __fadd_rn(ad[h][nt].y, v1); }
+                        if (ep.out && ok) __stcs(reinterpret_cast<float2*>(ep.out + (long long)row * ep.ld_out + col), make_float2(v0, v1));
+                    } else if (ok) {
+                        if (addsrc) {
+                            v0 = __fadd_rn(addsrc[(long long)row * ld_add + col], v0);
+                            if (col + 1 < N) v1 = __fadd_rn(addsrc[(long long)row * ld_add + col + 1], v1);
                         }
-                        const unsigned b2 = (v[0] > 0.f ? 1u : 0u) | (v[1] > 0.f ? 2u : 0u);
-                        if (nt < 4) lo[h] |= b2 << (nt * 8 + tig * 2);
-                        else hi[h] |= b2 << ((nt - 4) * 8 + tig * 2);
+                        if (ep.out) {
+                            ep.out[(long long)row * ep.ld_out + col] = v0;
+                            if (col + 1 < N) ep.out[(long long)row * ep.ld_out + col + 1] = v1;
+                        }
                     }
+                    const unsigned b2 = (v0 > 0.f ? 1u : 0u) | (v1 > 0.f ? 2u : 0u);
+                    if (nt < 4) lo[h] |= b2 << (nt * 8 + tig * 2);
+                    else hi[h] |= b2 << ((nt - 4) * 8 + tig * 2);
                 }
             }
             if (ep.bits) {  // a quad holds the 64 channels of a row: OR the four lanes together

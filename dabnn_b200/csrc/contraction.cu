@@ -7,11 +7,11 @@
 
 namespace dabnn {
 
-template <int ENGINE, int WM, int WN, class XOp, class WOp>
+template <int ENGINE, int WM, int WN, bool FAST, class XOp, class WOp>
 static int launch_one(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
                       cudaStream_t stream) {
     using Cfg = TileCfg<WM, WN>;
-    auto kern = bcontract_kernel<ENGINE, WM, WN, XOp, WOp>;
+    auto kern = bcontract_kernel<ENGINE, WM, WN, FAST, XOp, WOp>;
     static thread_local int configured_device = -1;  // per (instantiation, thread): opt in once per device
     int dev = 0;
     DABNN_CUDA_OK(cudaGetDevice(&dev));
@@ -28,24 +28,31 @@ static int launch_one(const XOp& xop, const WOp& wop, const EpilogueParams& ep, 
     return check_launch("bcontract_kernel");
 }
 
+template <int ENGINE, class XOp, class WOp>
+static int launch_engine(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
+                         cudaStream_t stream) {
+    auto al8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7) == 0; };
+    const bool fast = N % 8 == 0 && (!ep.out || (ep.ld_out % 2 == 0 && al8(ep.out))) &&
+                      (!ep.shortcut || (ep.ld_sc % 2 == 0 && al8(ep.shortcut)));
+    const bool narrow = N <= 64;  // 256 x 64 tiles for 64-channel layers, 128 x 128 otherwise
+    if (fast)
+        return narrow ? launch_one<ENGINE, 8, 1, true>(xop, wop, ep, M, N, kwords, stream)
+                      : launch_one<ENGINE, 4, 2, true>(xop, wop, ep, M, N, kwords, stream);
+    return narrow ? launch_one<ENGINE, 8, 1, false>(xop, wop, ep, M, N, kwords, stream)
+                  : launch_one<ENGINE, 4, 2, false>(xop, wop, ep, M, N, kwords, stream);
+}
+
 template <class XOp, class WOp>
 int launch_bcontract(int engine, const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N,
                      int kwords, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return DABNN_OK;
+    DABNN_REQUIRE(kwords < (1 << 17), DABNN_ERR_SHAPE, "contraction: K must be below 2^23 bits");
     if (engine == DABNN_ENGINE_AUTO) engine = DABNN_ENGINE_IMMA;
-    const bool narrow = N <= 64;  // 256 x 64 tiles for 64-channel layers, 128 x 128 otherwise
     switch (engine) {
-        case DABNN_ENGINE_POPC:
-            return narrow ? launch_one<ENG_POPC, 4, 1>(xop, wop, ep, M, N, kwords, stream)
-                          : launch_one<ENG_POPC, 2, 2>(xop, wop, ep, M, N, kwords, stream);
-        case DABNN_ENGINE_B1:
-            return narrow ? launch_one<ENG_B1, 4, 1>(xop, wop, ep, M, N, kwords, stream)
-                          : launch_one<ENG_B1, 2, 2>(xop, wop, ep, M, N, kwords, stream);
-        case DABNN_ENGINE_IMMA:
-            return narrow ? launch_one<ENG_IMMA, 4, 1>(xop, wop, ep, M, N, kwords, stream)
-                          : launch_one<ENG_IMMA, 2, 2>(xop, wop, ep, M, N, kwords, stream);
-        default:
-            return fail(DABNN_ERR_ARG, "unknown contraction engine");
+        case DABNN_ENGINE_POPC: return launch_engine<ENG_POPC>(xop, wop, ep, M, N, kwords, stream);
+        case DABNN_ENGINE_B1: return launch_engine<ENG_B1>(xop, wop, ep, M, N, kwords, stream);
+        case DABNN_ENGINE_IMMA: return launch_engine<ENG_IMMA>(xop, wop, ep, M, N, kwords, stream);
+        default: return fail(DABNN_ERR_ARG, "unknown contraction engine");
     }
 }
 
