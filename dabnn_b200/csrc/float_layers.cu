@@ -213,10 +213,14 @@ __global__ void concat_kernel(const float* __restrict__ x1, int c1, const float*
 // tail (x = hi + lo, 21+ significant bits) and each product is formed as lo*hi + hi*lo + hi*hi
 // with mma.sync.m16n8k8 TF32 MMAs accumulating in fp32 ("3xTF32").  The dropped lo*lo term is
 // below 2^-22 relative, i.e. the result differs from an fp32 FMA chain by summation order only.
-// CTA tile 128 pixels x 64 channels, 4 warps of 32 x 64, K slices of 16 staged in shared memory
-// (register double buffering).  The epilogue adds the bias and can apply a per-channel affine
-// (product and sum rounded separately, like the Affine layer) and a relu.
-constexpr int FTM = 128, FTN = 64, FKC = 16, FPITCH = FKC + 4;
+//
+// CTA tile 256 pixels x 64 channels, 8 warps of 32 x 64, K slices of 16 staged in shared memory
+// (register double buffering).  Weights are split into head and tail once, when a slice is
+// stored to shared memory; pixels are split per fragment (each is used by one warp only).  The
+// k -> (ky, kx, ci) decomposition comes from a table built once per CTA, so the gather loop has no
+// integer division.  The epilogue adds the bias and can apply a per-channel affine (product and
+// sum rounded separately, like the Affine layer) and a relu.
+constexpr int FTM = 256, FTN = 64, FKC = 16, FPITCH = FKC + 4, FNT = 256, FTABLE = 2048;
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
     uint32_t r;
@@ -230,87 +234,94 @@ __device__ __forceinline__ void mma_tf32(float* d, const uint32_t* a, const uint
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-__global__ void __launch_bounds__(128) fconv_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
-                                                    const float* __restrict__ bias, const float* __restrict__ a,
-                                                    const float* __restrict__ b, int relu, float* __restrict__ out,
-                                                    int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
-                                                    int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, int oh,
-                                                    int ow) {
+struct FconvParams {
+    const float *in, *wgt, *bias, *a, *b;
+    float* out;
+    int relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, oh, ow;
+};
+
+__global__ void __launch_bounds__(FNT, 2) fconv_kernel(const FconvParams p) {
     __shared__ __align__(16) float As[FTM * FPITCH];
-    __shared__ __align__(16) float Bs[FTN * FPITCH];
-    const int K = kh * kw * cin, M = n * oh * ow;
+    __shared__ __align__(16) uint32_t Bhi[FTN * FPITCH];
+    __shared__ __align__(16) uint32_t Blo[FTN * FPITCH];
+    __shared__ uint32_t ktab[FTABLE];  // k -> ci << 16 | (kx*dil_w) << 8 | (ky*dil_h)
+    const int K = p.kh * p.kw * p.cin, M = p.n * p.oh * p.ow;
+    const int h = p.h, w = p.w, cin = p.cin, cout = p.cout;
     const int m0 = blockIdx.x * FTM, n0 = blockIdx.y * FTN;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
-    // loader: thread -> k quad (tid & 3) of the slice, rows (tid >> 2) + 32*i
+    const bool use_tab = K <= FTABLE && p.cin < 65536 && p.kh * p.dil_h < 256 && p.kw * p.dil_w < 256;
+    auto decode = [&](int k) -> uint32_t {
+        const int tap = k / cin, ky = tap / p.kw;
+        return ((uint32_t)(k - tap * cin) << 16) | ((uint32_t)((tap - ky * p.kw) * p.dil_w) << 8) | (uint32_t)(ky * p.dil_h);
+    };
+    if (use_tab)
+        for (int k = tid; k < K; k += FNT) ktab[k] = decode(k);
+    // loader: thread -> k quad (tid & 3) of the slice, pixel rows (tid >> 2) + 64*i, weight row tid >> 2
     const int kq = (tid & 3) * 4, lr = tid >> 2;
     long long abase[4];
     int aiy[4], aix[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const int pm = m0 + lr + 32 * i;
+        const int pm = m0 + lr + 64 * i;
         if (pm < M) {
-            const int img = pm / (oh * ow), rem = pm - img * (oh * ow);
-            const int oy = rem / ow, ox = rem - oy * ow;
+            const int img = pm / (p.oh * p.ow), rem = pm - img * (p.oh * p.ow);
+            const int oy = rem / p.ow, ox = rem - oy * p.ow;
             abase[i] = (long long)img * h * w;
-            aiy[i] = oy * stride_h - pad_h;
-            aix[i] = ox * stride_w - pad_w;
+            aiy[i] = oy * p.stride_h - p.pad_h;
+            aix[i] = ox * p.stride_w - p.pad_w;
         } else {
             abase[i] = 0; aiy[i] = -(1 << 28); aix[i] = 0;   // every tap out of range -> zeros
         }
     }
-    const bool vec4 = (cin % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
-    const bool wvec4 = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(wgt) & 15) == 0);
-    float ra[4][4], rb[2][4];
+    const bool vec4 = (cin % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.in) & 15) == 0);
+    const bool wvec4 = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.wgt) & 15) == 0);
+    const int wrow = n0 + lr;
+    float ra[4][4], rb[4];
+    __syncthreads();   // ktab
 
     auto gload = [&](int k0) {
         const int k = k0 + kq;
-        int ky[4], kx[4], ci[4];
+        uint32_t e[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int kk = k + q, tap = kk / cin;
-            ci[q] = kk - tap * cin;
-            ky[q] = (tap / kw);
-            kx[q] = (tap - ky[q] * kw) * dil_w;
-            ky[q] *= dil_h;
-        }
+        for (int q = 0; q < 4; q++) e[q] = (k + q < K) ? (use_tab ? ktab[k + q] : decode(k + q)) : 0u;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             if (vec4 && k + 3 < K) {   // the four k share one tap: one 16-byte load
-                const int y = aiy[i] + ky[0], x = aix[i] + kx[0];
+                const int y = aiy[i] + (int)(e[0] & 255u), x = aix[i] + (int)((e[0] >> 8) & 255u);
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if ((unsigned)y < (unsigned)h && (unsigned)x < (unsigned)w)
-                    v = __ldg(reinterpret_cast<const float4*>(in + (abase[i] + (long long)y * w + x) * cin + ci[0]));
+                    v = __ldg(reinterpret_cast<const float4*>(p.in + (abase[i] + (long long)y * w + x) * cin + (e[0] >> 16)));
                 ra[i][0] = v.x; ra[i][1] = v.y; ra[i][2] = v.z; ra[i][3] = v.w;
             } else {
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const int y = aiy[i] + ky[q], x = aix[i] + kx[q];
+                    const int y = aiy[i] + (int)(e[q] & 255u), x = aix[i] + (int)((e[q] >> 8) & 255u);
                     float v = 0.f;
                     if (k + q < K && (unsigned)y < (unsigned)h && (unsigned)x < (unsigned)w)
-                        v = __ldg(in + (abase[i] + (long long)y * w + x) * cin + ci[q]);
+                        v = __ldg(p.in + (abase[i] + (long long)y * w + x) * cin + (e[q] >> 16));
                     ra[i][q] = v;
                 }
             }
         }
+        if (wvec4 && wrow < cout && k + 3 < K) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(p.wgt + (size_t)wrow * K + k));
+            rb[0] = v.x; rb[1] = v.y; rb[2] = v.z; rb[3] = v.w;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int wn = n0 + lr + 32 * i;
-            if (wvec4 && wn < cout && k + 3 < K) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(wgt + (size_t)wn * K + k));
-                rb[i][0] = v.x; rb[i][1] = v.y; rb[i][2] = v.z; rb[i][3] = v.w;
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; q++) rb[i][q] = (wn < cout && k + q < K) ? __ldg(wgt + (size_t)wn * K + k + q) : 0.f;
-            }
+            for (int q = 0; q < 4; q++) rb[q] = (wrow < cout && k + q < K) ? __ldg(p.wgt + (size_t)wrow * K + k + q) : 0.f;
         }
     };
     auto sstore = [&]() {
 #pragma unroll
         for (int i = 0; i < 4; i++)
-            *reinterpret_cast<float4*>(&As[(lr + 32 * i) * FPITCH + kq]) = make_float4(ra[i][0], ra[i][1], ra[i][2], ra[i][3]);
-#pragma unroll
-        for (int i = 0; i < 2; i++)
-            *reinterpret_cast<float4*>(&Bs[(lr + 32 * i) * FPITCH + kq]) = make_float4(rb[i][0], rb[i][1], rb[i][2], rb[i][3]);
+            *reinterpret_cast<float4*>(&As[(lr + 64 * i) * FPITCH + kq]) = make_float4(ra[i][0], ra[i][1], ra[i][2], ra[i][3]);
+        uint4 hi, lo;
+        hi.x = to_tf32(rb[0]); lo.x = to_tf32(rb[0] - __uint_as_float(hi.x));
+        hi.y = to_tf32(rb[1]); lo.y = to_tf32(rb[1] - __uint_as_float(hi.y));
+        hi.z = to_tf32(rb[2]); lo.z = to_tf32(rb[2] - __uint_as_float(hi.z));
+        hi.w = to_tf32(rb[3]); lo.w = to_tf32(rb[3] - __uint_as_float(hi.w));
+        *reinterpret_cast<uint4*>(&Bhi[lr * FPITCH + kq]) = hi;
+        *reinterpret_cast<uint4*>(&Blo[lr * FPITCH + kq]) = lo;
     };
 
     float acc[2][8][4];
@@ -342,14 +353,8 @@ __global__ void __launch_bounds__(128) fconv_kernel(const float* __restrict__ in
             }
 #pragma unroll
             for (int nt = 0; nt < 8; nt++) {
-                const float* bp = &Bs[(nt * 8 + g) * FPITCH + ks + tig];
-                const float v[2] = {bp[0], bp[4]};
-                uint32_t bhi[2], blo[2];
-#pragma unroll
-                for (int q = 0; q < 2; q++) {
-                    bhi[q] = to_tf32(v[q]);
-                    blo[q] = to_tf32(v[q] - __uint_as_float(bhi[q]));
-                }
+                const int bo = (nt * 8 + g) * FPITCH + ks + tig;
+                const uint32_t bhi[2] = {Bhi[bo], Bhi[bo + 4]}, blo[2] = {Blo[bo], Blo[bo + 4]};
 #pragma unroll
                 for (int mt = 0; mt < 2; mt++) {
                     mma_tf32(acc[mt][nt], alo[mt], bhi);
@@ -367,8 +372,8 @@ __global__ void __launch_bounds__(128) fconv_kernel(const float* __restrict__ in
 #pragma unroll
         for (int q = 0; q < 2; q++)
             if (col + q < cout) {
-                if (bias) bb[q] = __ldg(bias + col + q);
-                if (a) { ca[q] = __ldg(a + col + q); cb[q] = __ldg(b + col + q); }
+                if (p.bias) bb[q] = __ldg(p.bias + col + q);
+                if (p.a) { ca[q] = __ldg(p.a + col + q); cb[q] = __ldg(p.b + col + q); }
             }
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
@@ -379,11 +384,11 @@ __global__ void __launch_bounds__(128) fconv_kernel(const float* __restrict__ in
                 float v[2] = {acc[mt][nt][hh * 2], acc[mt][nt][hh * 2 + 1]};
 #pragma unroll
                 for (int q = 0; q < 2; q++) {
-                    if (bias) v[q] = __fadd_rn(v[q], bb[q]);
-                    if (a) v[q] = __fadd_rn(__fmul_rn(ca[q], v[q]), cb[q]);
-                    if (relu) v[q] = relu_ref(v[q]);
+                    if (p.bias) v[q] = __fadd_rn(v[q], bb[q]);
+                    if (p.a) v[q] = __fadd_rn(__fmul_rn(ca[q], v[q]), cb[q]);
+                    if (p.relu) v[q] = relu_ref(v[q]);
                 }
-                float* op = out + (size_t)row * cout + col;
+                float* op = p.out + (size_t)row * cout + col;
                 if (col + 1 < cout && (cout & 1) == 0) {
                     *reinterpret_cast<float2*>(op) = make_float2(v[0], v[1]);
                 } else {
@@ -407,8 +412,9 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     DABNN_REQUIRE((long long)n * oh * ow < (1ll << 31), DABNN_ERR_SHAPE, "fconv: too many output pixels");
     DABNN_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7) == 0, DABNN_ERR_ARG, "fconv: output must be 8-byte aligned");
     dim3 grid((n * oh * ow + FTM - 1) / FTM, (cout + FTN - 1) / FTN);
-    fconv_kernel<<<grid, 128, 0, stream>>>(in, weight, bias, a, b, relu, out, n, h, w, cin, cout, kh, kw, pad_h,
-                                           pad_w, stride_h, stride_w, dil_h, dil_w, oh, ow);
+    const FconvParams prm{in, weight, bias, a, b, out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w,
+                          stride_h, stride_w, dil_h, dil_w, oh, ow};
+    fconv_kernel<<<grid, FNT, 0, stream>>>(prm);
     return check_launch("fconv_kernel");
 }
 
