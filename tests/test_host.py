@@ -91,6 +91,19 @@ def test_argument_checks_need_no_gpu():
     assert lib.dabnn_binconv_workspace_bytes(1, 8, 8, 32, 3, 3, 1, 1, 1, 1) == 64 * 6 * 8
 
 
+def test_cpp_net_shim_compiles_and_fails_loudly_without_gpu(tmp_path):
+    from dabnn_b200 import capi
+    exe = tmp_path / "shim_check"
+    lib_dir = capi.LIB_PATH.parent
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", f"-I{ROOT / 'include'}", str(ROOT / "tests" / "cpp_shim_check.cpp"),
+                    "-o", str(exe), f"-L{lib_dir}", "-ldabnn_b200", f"-Wl,-rpath,{lib_dir}"], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    if capi.load().dabnn_device_count() == 0:
+        assert r.returncode == 3 and "runtime_error" in r.stdout      # no device: loud failure, no fallback
+    else:
+        assert r.returncode == 0 and "created" in r.stdout
+
+
 def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     from dabnn_b200 import capi
     monkeypatch.setattr(capi, "_lib", None)
