@@ -12,6 +12,7 @@ HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "lib" / "libdabnn_b200.so"
 
 ENGINE_AUTO, ENGINE_POPC, ENGINE_B1, ENGINE_IMMA = 0, 1, 2, 3
+BINCONV_STATIC_BYTES = 16 << 20   # DABNN_BINCONV_STATIC_BYTES
 ENGINES = {"auto": ENGINE_AUTO, "popc": ENGINE_POPC, "b1": ENGINE_B1, "imma": ENGINE_IMMA}
 ERROR_NAMES = {1: "ARG", 2: "SHAPE", 3: "IO", 4: "FORMAT", 5: "UNSUPPORTED", 6: "NOT_FOUND", 7: "CUDA",
                8: "OOM", 9: "STATE"}
@@ -37,6 +38,7 @@ _SIGNATURES = {
     "dabnn_bconv": [_p, _p, _z, _p] + [_i] * 12 + [_p],
     "dabnn_binconv_workspace_bytes": [_i] * 10,
     "dabnn_binconv_forward": [_p, _p, _z, _p] + [_i] * 11 + [_p, _z, _i, _p],
+    "dabnn_binconv_forward_static": [_p, _p, _z, _p] + [_i] * 11 + [_i, _p],
     "dabnn_bconv_block": [_p, _p, _z, _p, _p, _p, _p, _p] + [_i] * 12 + [_p],
     "dabnn_affine": [_p, _p, _p, _z, _i, _p],
     "dabnn_add": [_p, _p, _z, _p],

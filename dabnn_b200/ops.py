@@ -125,6 +125,21 @@ def binconv_forward(x, weight, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, e
     return out if x.dim() == 4 else out[0]
 
 
+def binconv_forward_static(x, weight, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, engine="auto"):
+    """`binconv_forward` without any allocation inside the library: the packed intermediate lives
+    in the library's built-in 16 MiB device buffer.  For hosts that own all device memory
+    themselves or may not call cudaMalloc where they run inference.  `out` is still the caller's
+    (here: a torch tensor allocated before the call).  Calls on one device must not overlap."""
+    x4 = _b4(_cuda(x, torch.float32))
+    n, h, w, c = x4.shape
+    oh, ow = out_dim(h, pad_h, 1, kh, stride_h), out_dim(w, pad_w, 1, kw, stride_w)
+    out = torch.empty((n, max(oh, 0), max(ow, 0), cout), dtype=torch.float32, device=x.device)
+    check(capi.load().dabnn_binconv_forward_static(_ptr(x4), _ptr(_cuda(weight, torch.int64)), weight.numel(), _ptr(out),
+                                                   n, h, w, c, cout, kh, kw, pad_h, pad_w, stride_h, stride_w,
+                                                   _eng(engine), _stream()))
+    return out if x.dim() == 4 else out[0]
+
+
 def bconv_block(x_bits, weight, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, a=None, b=None, shortcut=None,
                 want_f32=True, want_bits=False, engine="auto"):
     """Fused BinConv -> Affine -> Add -> sign bits (see dabnn_bconv_block).  Returns (f32, bits)."""

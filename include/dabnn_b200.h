@@ -116,6 +116,24 @@ int dabnn_binconv_forward(const float* in, const uint64_t* weight, size_t weight
                           int stride_h, int stride_w, void* workspace, size_t workspace_bytes,
                           int engine, dabnn_stream_t s);
 
+/* No counterpart in the reference.  dabnn_binconv_forward for callers that can neither pass a
+ * workspace nor let the library allocate one: hosts that give all device memory to their own
+ * allocator at start-up, or that call from a context where cudaMalloc is off limits (a latency-bound
+ * serving loop, another runtime's plugin callback).  The intermediate bit tensor is kept in a fixed
+ * array of DABNN_BINCONV_STATIC_BYTES (16 MiB) that is part of the library's device image; every
+ * GPU that loads the library holds those 16 MiB until the process exits.  Shapes that need more
+ * scratch than that (dabnn_binconv_workspace_bytes) are refused with DABNN_ERR_SHAPE.  The call
+ * makes no cudaMalloc / cudaFree and uses no allocating library routine.
+ *  - The first call made with a given device current looks up the array's device address
+ *    (cudaGetSymbolAddress) and caches it; make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Nothing in it needs clearing between calls (each
+ *    call overwrites what it reads), but two calls whose kernels can overlap on the GPU - different
+ *    streams, or different host threads - race on it: serialise them. */
+#define DABNN_BINCONV_STATIC_BYTES (16u << 20)
+int dabnn_binconv_forward_static(const float* in, const uint64_t* weight, size_t weight_words, float* out,
+                                 int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
+                                 int pad_w, int stride_h, int stride_w, int engine, dabnn_stream_t s);
+
 /* Fused residual block of a binarised network, the sequence the reference runs as four layers
  * (BinConv.cpp:144 -> Affine.cpp:10 -> Add.cpp:7 -> next layer's bitpack.h:277):
  *   cnt = bconv(in_bits, weight);  y = a[c]*cnt + b[c];  if (shortcut) y = y + shortcut;
