@@ -11,9 +11,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "lib" / "libdabnn_b200.so"
 
-ENGINE_AUTO, ENGINE_POPC, ENGINE_B1, ENGINE_IMMA = 0, 1, 2, 3
+ENGINE_AUTO, ENGINE_POPC, ENGINE_B1, ENGINE_IMMA, ENGINE_TCGEN05 = 0, 1, 2, 3, 4
 BINCONV_STATIC_BYTES = 16 << 20   # DABNN_BINCONV_STATIC_BYTES
-ENGINES = {"auto": ENGINE_AUTO, "popc": ENGINE_POPC, "b1": ENGINE_B1, "imma": ENGINE_IMMA}
+ENGINES = {"auto": ENGINE_AUTO, "popc": ENGINE_POPC, "b1": ENGINE_B1, "imma": ENGINE_IMMA, "tcgen05": ENGINE_TCGEN05}
 ERROR_NAMES = {1: "ARG", 2: "SHAPE", 3: "IO", 4: "FORMAT", 5: "UNSUPPORTED", 6: "NOT_FOUND", 7: "CUDA",
                8: "OOM", 9: "STATE"}
 
@@ -63,6 +63,7 @@ _SIGNATURES = {
     "dabnn_net_set_profiling": [_p, _i],
     "dabnn_net_layer_times": [_p, C.POINTER(C.c_char_p), C.POINTER(_f), _i, C.POINTER(_i)],
     "dabnn_measure_engine_peak": [_i, C.POINTER(C.c_double)],
+    "dabnn_engine_status": [C.POINTER(_i)],
     "dabnn_last_error": [],
     "dabnn_version": [],
     "dabnn_device_count": [],

@@ -2,7 +2,7 @@
 // block and the BinConv operator.
 #include <algorithm>
 
-#include "bcontract.cuh"
+#include "bcontract_tc5.cuh"
 #include "kernels.h"
 
 namespace dabnn {
@@ -42,13 +42,40 @@ static int launch_engine(const XOp& xop, const WOp& wop, const EpilogueParams& e
                   : launch_one<ENGINE, 4, 2, false>(xop, wop, ep, M, N, kwords, stream);
 }
 
+// tcgen05 engine: persistent 128-thread CTAs, two per SM (each holds up to 256 TMEM columns)
+template <class XOp, class WOp>
+static int launch_tc5(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
+                      cudaStream_t stream) {
+    auto kern = bcontract_tc5_kernel<XOp, WOp>;
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    DABNN_CUDA_OK(cudaGetDevice(&dev));
+    if (configured_device != dev) {
+        DABNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc5Smem::TOTAL));
+        configured_device = dev;
+    }
+    const int tiles_m = (M + 127) / 128, tiles_n = (N + TC5_MAX_N - 1) / TC5_MAX_N;
+    const int per_n = std::max(1, 2 * sm_count() / tiles_n);
+    dim3 grid(std::min(tiles_m, per_n), tiles_n);
+    kern<<<grid, 128, Tc5Smem::TOTAL, stream>>>(xop, wop, ep, M, N, kwords, tiles_m);
+    return check_launch("bcontract_tc5_kernel");
+}
+
+static bool tc5_eligible(const EpilogueParams& ep, int N) {
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    return N % 16 == 0 && (!ep.out || (ep.ld_out % 4 == 0 && al16(ep.out))) &&
+           (!ep.shortcut || (ep.ld_sc % 4 == 0 && al16(ep.shortcut))) && (!ep.bits || N % 64 == 0);
+}
+
 template <class XOp, class WOp>
 int launch_bcontract(int engine, const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N,
                      int kwords, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return DABNN_OK;
     DABNN_REQUIRE(kwords < (1 << 17), DABNN_ERR_SHAPE, "contraction: K must be below 2^23 bits");
-    if (engine == DABNN_ENGINE_AUTO) engine = DABNN_ENGINE_IMMA;
+    if (engine == DABNN_ENGINE_AUTO) engine = DABNN_ENGINE_TCGEN05;
+    if (engine == DABNN_ENGINE_TCGEN05 && !tc5_eligible(ep, N)) engine = DABNN_ENGINE_IMMA;
     switch (engine) {
+        case DABNN_ENGINE_TCGEN05: return launch_tc5(xop, wop, ep, M, N, kwords, stream);
         case DABNN_ENGINE_POPC: return launch_engine<ENG_POPC>(xop, wop, ep, M, N, kwords, stream);
         case DABNN_ENGINE_B1: return launch_engine<ENG_B1>(xop, wop, ep, M, N, kwords, stream);
         case DABNN_ENGINE_IMMA: return launch_engine<ENG_IMMA>(xop, wop, ep, M, N, kwords, stream);
@@ -182,4 +209,11 @@ extern "C" int dabnn_binconv_forward(const float* in, const uint64_t* weight, si
     RowMajorOperand wop{weight, row_words, cout, row_words};
     EpilogueParams ep{out, cout, 0, nullptr, nullptr, nullptr, 0, nullptr, 0};
     return launch_bcontract(engine, xop, wop, ep, n * oh * ow, cout, row_words, static_cast<cudaStream_t>(s));
+}
+
+extern "C" int dabnn_engine_status(int* status) {
+    DABNN_REQUIRE(status, DABNN_ERR_ARG, "null output");
+    DABNN_CUDA_OK(cudaDeviceSynchronize());
+    DABNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_tc5_status, sizeof(int)));
+    return DABNN_OK;
 }

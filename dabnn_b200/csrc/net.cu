@@ -734,7 +734,7 @@ extern "C" int dabnn_net_configure(dabnn_net* net, int max_batch, int engine) {
     DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
     DABNN_REQUIRE(!net->impl.loaded, DABNN_ERR_STATE, "configure must precede read");
     DABNN_REQUIRE(max_batch >= 1, DABNN_ERR_ARG, "max_batch must be >= 1");
-    DABNN_REQUIRE(engine >= DABNN_ENGINE_AUTO && engine <= DABNN_ENGINE_IMMA, DABNN_ERR_ARG, "unknown engine");
+    DABNN_REQUIRE(engine >= DABNN_ENGINE_AUTO && engine <= DABNN_ENGINE_TCGEN05, DABNN_ERR_ARG, "unknown engine");
     net->impl.max_batch = max_batch; net->impl.engine = engine;
     return DABNN_OK;
 }

@@ -229,3 +229,10 @@ def measure_engine_peak(engine):
     v = C.c_double()
     check(capi.load().dabnn_measure_engine_peak(_eng(engine), C.byref(v)))
     return v.value
+
+
+def engine_status():
+    """0, or the code of the first bounded wait that gave up inside a tcgen05 kernel (synchronises)."""
+    v = C.c_int()
+    check(capi.load().dabnn_engine_status(C.byref(v)))
+    return v.value

@@ -43,10 +43,12 @@ enum {
 
 /* Which contraction engine computes the XOR-popcount sums.  All give identical integers. */
 enum {
-    DABNN_ENGINE_AUTO = 0,  /* the fastest measured on B200 (int8 tensor-core path) */
+    DABNN_ENGINE_AUTO = 0,  /* the fastest eligible one: TCGEN05, else IMMA */
     DABNN_ENGINE_POPC = 1,  /* CUDA cores: xor + popc */
     DABNN_ENGINE_B1 = 2,    /* mma.sync m16n8k256 b1 AND-popc, xor recovered from row/column popcounts */
-    DABNN_ENGINE_IMMA = 3   /* mma.sync m16n8k32 u8 on bits expanded to {0,1} bytes in registers */
+    DABNN_ENGINE_IMMA = 3,  /* mma.sync m16n8k32 u8 on bits expanded to {0,1} bytes in registers */
+    DABNN_ENGINE_TCGEN05 = 4 /* tcgen05.mma kind::i8 (TMEM accumulators) on bits expanded to bytes in shared
+                                memory; needs N % 16 == 0 and 16-byte aligned rows, otherwise IMMA is used */
 };
 
 typedef void* dabnn_stream_t; /* cudaStream_t */
@@ -217,6 +219,12 @@ int dabnn_net_layer_times(dabnn_net* net, const char** names, float* ms, int cap
  * `engine` as above (POPC / B1 / IMMA).  Used as the roofline denominator of the contraction.
  * ------------------------------------------------------------------------------------------- */
 int dabnn_measure_engine_peak(int engine, double* bitops_per_second);
+
+/* Diagnostic: synchronises the device and returns, through *status, 0 or the code of the first
+ * bounded wait that gave up inside a TCGEN05-engine kernel since the library was loaded (1 = an
+ * operand buffer was never released by the tensor core, 2 = an accumulator never completed).
+ * Such a kernel stops issuing work, frees its tensor memory and returns instead of hanging. */
+int dabnn_engine_status(int* status);
 
 #ifdef __cplusplus
 }
