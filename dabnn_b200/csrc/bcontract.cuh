@@ -49,6 +49,7 @@ struct RowMajorOperand {
     struct Dec { int word; };
     __device__ bool pairable() const { return (ld & 1) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
     __device__ Dec decode(int word) const { return Dec{word}; }
+    __device__ void advance(Dec& d, int words) const { d.word += words; }
     __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row * ld, 0, 0, row < rows}; }
     __device__ const uint64_t* addr(const RowCtx& r, const Dec& d) const { return r.valid ? p + r.base + d.word : nullptr; }
 };
@@ -60,6 +61,7 @@ struct ColMajorOperand {
     struct Dec { long long off; };
     __device__ bool pairable() const { return false; }
     __device__ Dec decode(int word) const { return Dec{(long long)word * ld}; }
+    __device__ void advance(Dec& d, int words) const { d.off += (long long)words * ld; }
     __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row, 0, 0, row < rows}; }
     __device__ const uint64_t* addr(const RowCtx& r, const Dec& d) const { return r.valid ? p + d.off + r.base : nullptr; }
 };
@@ -73,6 +75,14 @@ struct ConvOperand {
     __device__ Dec decode(int word) const {
         const int tap = word / Cw, ky = tap / kw;
         return Dec{ky, tap - ky * kw, word - tap * Cw};
+    }
+    // step the decode of word q to word q + words without a division (words is small)
+    __device__ void advance(Dec& d, int words) const {
+        d.cw += words;
+        while (d.cw >= Cw) {
+            d.cw -= Cw;
+            if (++d.kx == kw) { d.kx = 0; ++d.ky; }
+        }
     }
     __device__ RowCtx make_row(int row) const {
         RowCtx r;

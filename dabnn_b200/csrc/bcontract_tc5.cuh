@@ -6,23 +6,28 @@
 // legacy b1 mma.sync is emulated, so the int8 kind is the fastest exact route: 8x the operand bytes
 // of 1-bit, but those bytes exist only in shared memory - HBM and L2 still carry packed bits.
 //
-// A CTA works on 128-pixel x (up to) 128-channel tiles with three kinds of warps that only meet
-// at mbarriers:
-//   * 4 producer warps, thread r = pixel row r: read the 64-bit words of the row (implicit im2col,
-//     tap by tap, zero word outside the image), expand every 32 bits to 32 bytes with shift+mask
-//     pairs ((w >> s) & 0x01010101 - the resulting bit -> K-slot permutation is the same for
-//     both operands, and a contraction is blind to it) and store them in the K-major SWIZZLE_NONE
-//     canonical layout of UMMA shared-memory descriptors (8 rows x 16 B core matrices).  Threads
-//     r < Ntile expand weight row r the same way.  K advances in chunks of 128 bits through a
-//     3-deep ring of chunk buffers.  The row popcount is accumulated on the way.
+// A CTA (one per SM, persistent over pixel tiles) works on 128-pixel x (up to) 128-channel tiles
+// with three kinds of warps that only meet at mbarriers:
+//   * 8 producer warps; thread (r, h) owns 64-bit word h of every 128-bit K chunk of operand row r:
+//     it reads the word (implicit im2col: tap by tap, zero word outside the image; the tap decode
+//     is stepped, not divided), expands every 32 bits to 32 bytes with shift+mask pairs
+//     ((w >> s) & 0x01010101 - the resulting bit -> K-slot permutation is the same for both
+//     operands, and a contraction is blind to it) and stores them in the K-major SWIZZLE_NONE
+//     canonical layout of UMMA shared-memory descriptors (8 rows x 16 B core matrices).  The same
+//     thread expands word h of weight row r when r < Ntile.  Chunks go through a 4-deep ring of
+//     32 KB buffers; loads run two chunks ahead of the expansion.  Row popcounts are accumulated
+//     on the way and handed to the epilogue through a small ring.
 //   * 1 MMA warp: one lane issues, per chunk, four tcgen05.mma (M = 128, N = Ntile, K = 32 bytes)
-//     from shared-memory descriptors into one of two TMEM accumulators and commits them to the
+//     from shared-memory descriptors into one of four TMEM accumulators and commits them to the
 //     ring's "empty" barrier, and to the accumulator's "full" barrier after the last chunk.
-//   * 4 epilogue warps, thread r = pixel row r: tcgen05.ld the row's accumulator 32 columns at a
-//     time, turn AND counts into XOR counts, apply the affine, add the shortcut, store fp32 and
-//     the row's sign bits (a thread holds whole 32-channel half words, no shuffles), then release
-//     the accumulator.
-// CTAs are persistent over pixel tiles; two fit on an SM (2 x 256 TMEM columns, 2 x ~104 KB).
+//   * 8 epilogue warps working on blocks of 128 pixels x 64 channels through two fp32 staging
+//     tiles in shared memory.  The shortcut (or the previous output, when accumulating) of the
+//     next block is copied into the idle tile with cp.async while the current block is handled,
+//     so its HBM latency is hidden behind a whole block of work.  Drain: thread (r, half)
+//     tcgen05.ld's 32 accumulator columns of row r, turns AND counts into XOR counts, applies the
+//     affine, adds the staged shortcut and writes the fp32 result back in place.  Write-out: the
+//     256 threads re-read the tile with consecutive lanes on consecutive channels, so the fp32
+//     stores are fully coalesced, and OR the sign bits of 64 channels together by shuffles.
 //
 // Every wait on an mbarrier is bounded: after a fixed number of polls the CTA records an error
 // code in a device-side status word, raises a CTA-wide abort flag that every role checks, frees
@@ -37,9 +42,12 @@ constexpr int TC5_CHUNK_BYTES = TC5_CHUNK_WORDS * 64;    // operand bytes per ro
 constexpr int TC5_SBO = (TC5_CHUNK_BYTES / 16) * 128;    // byte stride between 8-row groups
 constexpr int TC5_LBO = 128;                             // byte stride between 16-byte K units
 constexpr int TC5_MAX_N = 128;
-constexpr int TC5_STAGES = 3;
-constexpr int TC5_DECTAB = 640;                          // words of K with a precomputed tap decode
-constexpr int TC5_THREADS = 288;                         // 4 producer + 4 epilogue + 1 MMA warp
+constexpr int TC5_STAGES = 4;
+constexpr int TC5_ACCS = 4;                              // TMEM accumulators (4 x 128 columns = all of TMEM)
+constexpr int TC5_POPRING = 12;                          // tiles of row popcounts in flight (> stages + accumulators)
+constexpr int TC5_PRODUCERS = 256, TC5_EPILOGUE = 256;
+constexpr int TC5_THREADS = TC5_PRODUCERS + TC5_EPILOGUE + 32;
+constexpr int TC5_MMA_WARP = (TC5_PRODUCERS + TC5_EPILOGUE) / 32;
 constexpr uint32_t TC5_SPIN_LIMIT = 1u << 22;
 
 __device__ int g_tc5_status;  // 0 = ok; otherwise the code of the first wait that gave up
@@ -74,7 +82,9 @@ struct Tc5Smem {
     static constexpr int A_BYTES = 128 * TC5_CHUNK_BYTES;            // 16 KB
     static constexpr int B_BYTES = TC5_MAX_N * TC5_CHUNK_BYTES;      // 16 KB
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int TOTAL = TC5_STAGES * STAGE_BYTES + 1024 /*alignment slack*/;
+    static constexpr int SPITCH = 64 + 4;                            // staging tile pitch in floats (conflict-free 16-byte row accesses)
+    static constexpr int STILE_BYTES = 128 * SPITCH * 4;             // 34 KB: 128 pixels x 64 channels of fp32
+    static constexpr int TOTAL = TC5_STAGES * STAGE_BYTES + 2 * STILE_BYTES + 1024 /*alignment slack*/;
 };
 
 // 32 bits -> 32 bytes {0,1}: output word s holds bits s, s+8, s+16, s+24.  Two 16-byte stores.
@@ -86,56 +96,56 @@ __device__ __forceinline__ void expand32(unsigned char* dst_unit0, uint32_t w) {
     *reinterpret_cast<uint4*>(dst_unit0) = lo;
     *reinterpret_cast<uint4*>(dst_unit0 + TC5_LBO) = hi;
 }
-// one chunk (two 64-bit words) of one operand row: eight 16-byte units at a 128-byte stride
-__device__ __forceinline__ void expand_row(unsigned char* row_base, uint64_t w0, uint64_t w1) {
-    expand32(row_base + 0 * TC5_LBO, (uint32_t)w0);
-    expand32(row_base + 2 * TC5_LBO, (uint32_t)(w0 >> 32));
-    expand32(row_base + 4 * TC5_LBO, (uint32_t)w1);
-    expand32(row_base + 6 * TC5_LBO, (uint32_t)(w1 >> 32));
+// one 64-bit word of one operand row: four 16-byte units at a 128-byte stride
+__device__ __forceinline__ void expand_word(unsigned char* dst, uint64_t w) {
+    expand32(dst, (uint32_t)w);
+    expand32(dst + 2 * TC5_LBO, (uint32_t)(w >> 32));
 }
 
 template <class XOp, class WOp>
-__global__ void __launch_bounds__(TC5_THREADS, 2)
+__global__ void __launch_bounds__(TC5_THREADS, 1)
     bcontract_tc5_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
                          const int kwords, const int ntiles_m) {
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t bar_full[TC5_STAGES], bar_empty[TC5_STAGES], bar_acc_full[2], bar_acc_empty[2];
+    __shared__ __align__(8) uint64_t bar_full[TC5_STAGES], bar_empty[TC5_STAGES], bar_acc_full[TC5_ACCS], bar_acc_empty[TC5_ACCS];
     __shared__ uint32_t tmem_base_s;
-    __shared__ int s_abort;
-    __shared__ int popw[TC5_MAX_N], popx[4][128];   // popx: ring over tiles, producers run at most 3 tiles ahead of the epilogue
-    __shared__ float chan_a[TC5_MAX_N], chan_b[TC5_MAX_N];
-    __shared__ typename XOp::Dec dectab[TC5_DECTAB];
+    __shared__ int s_abort, epi_abort;
+    __shared__ int popw[TC5_MAX_N], popx[TC5_POPRING][2][128];
+    __shared__ __align__(16) float chan_a[TC5_MAX_N];   // read as float4 by the write-out
+    __shared__ __align__(16) float chan_b[TC5_MAX_N];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.y * TC5_MAX_N;
     const int n_this = min(TC5_MAX_N, N - n0);               // multiple of 16 (host-checked)
     unsigned char* stage0 = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     const int nchunks = (kwords + TC5_CHUNK_WORDS - 1) / TC5_CHUNK_WORDS;
-    const int tmem_cols = n_this <= 16 ? 32 : (n_this <= 32 ? 64 : (n_this <= 64 ? 128 : 256));  // 2 accumulators, power of 2
+    int tmem_cols = 32;
+    while (tmem_cols < TC5_ACCS * n_this) tmem_cols <<= 1;
     const volatile int* abort_flag = &s_abort;
 
     // ---- set-up (all threads) ----
-    if (warp == 8) {
+    if (warp == TC5_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(tmem_cols));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     if (tid == 0) {
-        for (int i = 0; i < TC5_STAGES; i++) { mbar_init(&bar_full[i], 128); mbar_init(&bar_empty[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], 128); }
+        for (int i = 0; i < TC5_STAGES; i++) { mbar_init(&bar_full[i], TC5_PRODUCERS); mbar_init(&bar_empty[i], 1); }
+        for (int i = 0; i < TC5_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], TC5_EPILOGUE); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
+        epi_abort = 0;
     }
-    const bool use_tab = kwords <= TC5_DECTAB;
-    if (use_tab)
-        for (int q = tid; q < kwords; q += TC5_THREADS) dectab[q] = xop.decode(q);
-    const RowCtx wrow = wop.make_row(n0 + (tid & 127));   // weight row owned by producer thread tid (if tid < n_this)
     if (tid < TC5_MAX_N) {
         int pc = 0;
-        if (tid < n_this)
+        if (tid < n_this) {
+            const RowCtx wr = wop.make_row(n0 + tid);
+            typename WOp::Dec d = wop.decode(0);
             for (int q = 0; q < kwords; q++) {
-                const uint64_t* p = wop.addr(wrow, wop.decode(q));
+                const uint64_t* p = wop.addr(wr, d);
                 pc += p ? __popcll(__ldg(p)) : 0;
+                wop.advance(d, 1);
             }
+        }
         popw[tid] = pc;
         const bool have = ep.a && tid < n_this;
         chan_a[tid] = have ? __ldg(ep.a + n0 + tid) : 1.f;
@@ -146,53 +156,56 @@ __global__ void __launch_bounds__(TC5_THREADS, 2)
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
 
-    if (warp < 4) {
-        // =========================== producers: thread = operand row ===========================
-        auto xdecode = [&](int q) { return use_tab ? dectab[q] : xop.decode(q); };
-        auto load_words = [&](const RowCtx& xr, int chunk, uint64_t& a0, uint64_t& a1, uint64_t& b0, uint64_t& b1) {
-            const int q = chunk * TC5_CHUNK_WORDS;
-            a0 = a1 = b0 = b1 = 0;
-            if (q < kwords) {
-                const uint64_t* p = xop.addr(xr, xdecode(q));
-                if (p) a0 = __ldg(p);
-                if (tid < n_this) { const uint64_t* w = wop.addr(wrow, wop.decode(q)); if (w) b0 = __ldg(w); }
-            }
-            if (q + 1 < kwords) {
-                const uint64_t* p = xop.addr(xr, xdecode(q + 1));
-                if (p) a1 = __ldg(p);
-                if (tid < n_this) { const uint64_t* w = wop.addr(wrow, wop.decode(q + 1)); if (w) b1 = __ldg(w); }
-            }
-        };
-        const int roff = (tid >> 3) * TC5_SBO + (tid & 7) * 16;
+    if (tid < TC5_PRODUCERS) {
+        // =========================== producers: thread = (operand row, word of the chunk) ===========================
+        const int r = tid & 127, h = tid >> 7;
+        const bool has_w = r < n_this;
+        const RowCtx wrow = wop.make_row(n0 + r);
+        const int roff = (r >> 3) * TC5_SBO + (r & 7) * 16 + h * 4 * TC5_LBO;
         uint32_t g = 0;   // chunks produced by this CTA
         bool ok = true;
         int i = 0;
         for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
-            const RowCtx xr = xop.make_row(tile * 128 + tid);
-            uint64_t a0, a1, b0, b1;
-            load_words(xr, 0, a0, a1, b0, b1);
+            const RowCtx xr = xop.make_row(tile * 128 + r);
+            typename XOp::Dec xd = xop.decode(h);   // decode state of the word being *loaded*
+            typename WOp::Dec wd = wop.decode(h);
+            int qload = h;                           // index of the word being loaded
+            auto load_next = [&](uint64_t& a, uint64_t& b) {
+                a = 0; b = 0;
+                if (qload < kwords) {
+                    const uint64_t* p = xop.addr(xr, xd);
+                    if (p) a = __ldg(p);
+                    if (has_w) { const uint64_t* w = wop.addr(wrow, wd); if (w) b = __ldg(w); }
+                }
+                qload += TC5_CHUNK_WORDS;
+                xop.advance(xd, TC5_CHUNK_WORDS);
+                wop.advance(wd, TC5_CHUNK_WORDS);
+            };
+            uint64_t a0, b0, a1, b1;   // words of chunk c and chunk c+1; chunk c+2 is loaded inside the loop
+            load_next(a0, b0);
+            load_next(a1, b1);
             int px = 0;
             for (int c = 0; c < nchunks; c++, g++) {
                 const uint32_t s = g % TC5_STAGES, use = g / TC5_STAGES;
-                uint64_t na0 = 0, na1 = 0, nb0 = 0, nb1 = 0;
-                if (c + 1 < nchunks) load_words(xr, c + 1, na0, na1, nb0, nb1);   // in flight during the expansion
+                uint64_t a2, b2;
+                load_next(a2, b2);
                 if (use >= 1 && !mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag)) {
                     atomicCAS(&g_tc5_status, 0, 1);
                     s_abort = 1;
                     ok = false;
                     break;
                 }
-                unsigned char* st = stage0 + s * Tc5Smem::STAGE_BYTES;
-                expand_row(st + roff, a0, a1);
-                if (tid < n_this) expand_row(st + Tc5Smem::A_BYTES + roff, b0, b1);
-                px += __popcll(a0) + __popcll(a1);
-                if (c == nchunks - 1) popx[i & 3][tid] = px;
+                unsigned char* st = stage0 + s * Tc5Smem::STAGE_BYTES + roff;
+                expand_word(st, a0);
+                if (has_w) expand_word(st + Tc5Smem::A_BYTES, b0);
+                px += __popcll(a0);
+                if (c == nchunks - 1) popx[i % TC5_POPRING][h][r] = px;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(&bar_full[s]);
-                a0 = na0; a1 = na1; b0 = nb0; b1 = nb1;
+                a0 = a1; b0 = b1; a1 = a2; b1 = b2;
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == TC5_MMA_WARP) {
         // =========================== MMA issue: one lane ===========================
         if (lane == 0) {
             // instruction descriptor: D = s32, A = u8, B = u8, both K-major, N = n_this, M = 128
@@ -201,7 +214,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 2)
             bool ok = true;
             int i = 0;
             for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
-                const int accbuf = i & 1, accuse = i >> 1;
+                const int accbuf = i % TC5_ACCS, accuse = i / TC5_ACCS;
                 if (accuse >= 1 && !mbar_wait(&bar_acc_empty[accbuf], (accuse - 1) & 1, abort_flag)) {
                     atomicCAS(&g_tc5_status, 0, 3);
                     s_abort = 1;
@@ -233,43 +246,76 @@ __global__ void __launch_bounds__(TC5_THREADS, 2)
             }
         }
     } else {
-        // =========================== epilogue: thread = pixel row ===========================
-        const int r = tid - 128;                 // row in the tile; TMEM lane quarter = warp % 4
+        // =========================== epilogue ===========================
+        // The channels of a tile are handled in blocks of 64.  Per block k (a counter over the
+        // whole kernel): [barrier] -> prefetch block k+1's shortcut into the other staging tile
+        // with cp.async -> drain: thread (r, h2) reads 32 accumulator columns of row r, converts,
+        // applies the affine, adds the staged shortcut and writes the result back in place ->
+        // [barrier] -> write-out: coalesced fp32 stores and sign-bit words from the staging tile.
+        const int et = tid - TC5_PRODUCERS;
+        const int r = et & 127, h2 = et >> 7;          // drain role: TMEM lane quarter = warp % 4 = r / 32
+        float* sbuf0 = reinterpret_cast<float*>(stage0 + TC5_STAGES * Tc5Smem::STAGE_BYTES);
         const float* addsrc = ep.shortcut ? ep.shortcut : (ep.accumulate ? ep.out : nullptr);
         const long long ld_add = ep.shortcut ? ep.ld_sc : ep.ld_out;
-        int i = 0;
-        for (int tile = blockIdx.x; tile < ntiles_m; tile += gridDim.x, i++) {
-            const int accbuf = i & 1, accuse = i >> 1;
-            if (!mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag)) {
-                atomicCAS(&g_tc5_status, 0, 2);
-                s_abort = 1;
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = tile * 128 + r;
-            const bool row_ok = row < M;
-            const int px = popx[i & 3][r];
-            const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * n_this;
-            for (int c0 = 0; c0 < n_this; c0 += 32) {
-                const int ncol = min(32, n_this - c0);   // 16 or 32
-                float4 add4[8];
-                if (addsrc && row_ok) {
-                    const float4* ap = reinterpret_cast<const float4*>(addsrc + (long long)row * ld_add + n0 + c0);
+        const int nblk = (n_this + 63) >> 6;           // 64-channel blocks per tile
+        int my_tiles = 0;
+        for (int t = blockIdx.x; t < ntiles_m; t += gridDim.x) my_tiles++;
+        const int total_blocks = my_tiles * nblk;
+
+        // issue the shortcut copies of block kb into staging tile kb & 1 (one commit group per call)
+        auto prefetch = [&](int kb) {
+            if (addsrc && kb < total_blocks) {
+                const int tile = blockIdx.x + (kb / nblk) * gridDim.x, cb = (kb % nblk) * 64;
+                const int width = min(64, n_this - cb);
+                const uint32_t sbase = smem_u32(sbuf0 + (kb & 1) * Tc5Smem::SPITCH * 128);
 #pragma unroll
-                    for (int q = 0; q < 8; q++) add4[q] = q * 4 < ncol ? __ldg(ap + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int j = 0; j < 8; j++) {
+                    const int it = et + j * TC5_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
+                    const int row = tile * 128 + rr;
+                    if (row < M && c4 < width)
+                        cp_async16(sbase + (rr * Tc5Smem::SPITCH + c4) * 4, addsrc + (long long)row * ld_add + n0 + cb + c4, 16);
                 }
+            }
+            cp_async_commit();
+        };
+        prefetch(0);
+        bool okw = true;
+        for (int kb = 0; kb < total_blocks; kb++) {
+            const int i = kb / nblk, blk = kb % nblk;
+            const int tile = blockIdx.x + i * gridDim.x, cb = blk * 64;
+            const int width = min(64, n_this - cb);
+            const int accbuf = i % TC5_ACCS, accuse = i / TC5_ACCS;
+            float* sb = sbuf0 + (kb & 1) * Tc5Smem::SPITCH * 128;
+            cp_async_wait<0>();                                               // my copies of block kb have landed
+            asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // everybody's have; write-out of kb-1 is over
+            prefetch(kb + 1);
+            // ---- drain ----
+            const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
+            if (blk == 0 && okw) {
+                okw = mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag);
+                if (!okw) {
+                    atomicCAS(&g_tc5_status, 0, 2);
+                    s_abort = 1;
+                    epi_abort = 1;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (okw && ncol > 0) {
+                const int px = popx[i % TC5_POPRING][0][r] + popx[i % TC5_POPRING][1][r];
+                const int c0 = cb + h2 * 32;
+                const uint32_t t_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * n_this + c0;
                 uint32_t v[32];
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
                                "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                             : "r"(t_row + c0));
+                             : "r"(t_addr));
                 if (ncol > 16)
                     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                                  : "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
                                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                                 : "r"(t_row + c0 + 16));
+                                 : "r"(t_addr + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                uint32_t signs = 0;
+                float* srow = sb + r * Tc5Smem::SPITCH + h2 * 32;
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
                     if (q * 4 >= ncol) break;
@@ -277,31 +323,52 @@ __global__ void __launch_bounds__(TC5_THREADS, 2)
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
                         const int cl = c0 + q * 4 + e;
-                        const int cnt = px + popw[cl] - 2 * (int)v[q * 4 + e];
-                        float f = small_int_to_float(cnt);
+                        float f = small_int_to_float(px + popw[cl] - 2 * (int)v[q * 4 + e]);
                         if (ep.a) f = __fadd_rn(__fmul_rn(chan_a[cl], f), chan_b[cl]);
                         o[e] = f;
                     }
-                    if (addsrc && row_ok) {
-                        o[0] = __fadd_rn(add4[q].x, o[0]); o[1] = __fadd_rn(add4[q].y, o[1]);
-                        o[2] = __fadd_rn(add4[q].z, o[2]); o[3] = __fadd_rn(add4[q].w, o[3]);
+                    if (addsrc) {
+                        const float4 ad = *reinterpret_cast<const float4*>(srow + q * 4);
+                        o[0] = __fadd_rn(ad.x, o[0]); o[1] = __fadd_rn(ad.y, o[1]);
+                        o[2] = __fadd_rn(ad.z, o[2]); o[3] = __fadd_rn(ad.w, o[3]);
                     }
-                    if (ep.out && row_ok)
-                        *reinterpret_cast<float4*>(ep.out + (long long)row * ep.ld_out + n0 + c0 + q * 4) = make_float4(o[0], o[1], o[2], o[3]);
-                    signs |= ((o[0] > 0.f ? 1u : 0u) | (o[1] > 0.f ? 2u : 0u) | (o[2] > 0.f ? 4u : 0u) | (o[3] > 0.f ? 8u : 0u)) << (q * 4);
+                    *reinterpret_cast<float4*>(srow + q * 4) = make_float4(o[0], o[1], o[2], o[3]);
                 }
-                if (ep.bits && row_ok)   // n0 and c0 are multiples of 32: this is one aligned half word
-                    reinterpret_cast<uint32_t*>(ep.bits + (long long)row * ep.ld_bits)[(n0 + c0) >> 5] = signs;
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&bar_acc_empty[accbuf]);   // the accumulator may be overwritten by the tile after next
+            if (blk == nblk - 1 && okw) {   // the whole accumulator has been read
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&bar_acc_empty[accbuf]);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
+            if (epi_abort) break;
+            // ---- write-out: item = (row, 4 channels); 16 consecutive lanes walk along a row ----
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int it = et + j * TC5_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
+                const int row = tile * 128 + rr;
+                const bool live = row < M && c4 < width;
+                const float4 o = *reinterpret_cast<const float4*>(sb + rr * Tc5Smem::SPITCH + c4);
+                if (ep.out && live) __stcs(reinterpret_cast<float4*>(ep.out + (long long)row * ep.ld_out + n0 + cb + c4), o);
+                if (ep.bits) {   // the 16 lanes of a row hold the 64 channels of one word (channel tiles are 64-multiples here)
+                    const unsigned nib = (o.x > 0.f ? 1u : 0u) | (o.y > 0.f ? 2u : 0u) | (o.z > 0.f ? 4u : 0u) | (o.w > 0.f ? 8u : 0u);
+                    const int sub = lane & 15;
+                    unsigned lo = sub < 8 ? nib << (4 * sub) : 0u, hi = sub >= 8 ? nib << (4 * (sub - 8)) : 0u;
+#pragma unroll
+                    for (int off = 1; off < 16; off <<= 1) {
+                        lo |= __shfl_xor_sync(0xffffffffu, lo, off);
+                        hi |= __shfl_xor_sync(0xffffffffu, hi, off);
+                    }
+                    if (sub == 0 && row < M) ep.bits[(long long)row * ep.ld_bits + ((n0 + cb) >> 6)] = ((unsigned long long)hi << 32) | lo;
+                }
+            }
         }
+        cp_async_wait<0>();   // nothing of this thread's is in flight when the CTA winds down
     }
 
     // ---- drain: everybody is past its last use of the tensor memory ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 8) {
+    if (warp == TC5_MMA_WARP) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols));
     }

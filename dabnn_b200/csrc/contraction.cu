@@ -42,7 +42,7 @@ static int launch_engine(const XOp& xop, const WOp& wop, const EpilogueParams& e
                   : launch_one<ENGINE, 4, 2, false>(xop, wop, ep, M, N, kwords, stream);
 }
 
-// tcgen05 engine: persistent warp-specialised CTAs, two per SM (each holds up to 256 TMEM columns)
+// tcgen05 engine: persistent warp-specialised CTAs, one per SM (it owns all of the SM's tensor memory)
 template <class XOp, class WOp>
 static int launch_tc5(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
                       cudaStream_t stream) {
@@ -55,7 +55,7 @@ static int launch_tc5(const XOp& xop, const WOp& wop, const EpilogueParams& ep, 
         configured_device = dev;
     }
     const int tiles_m = (M + 127) / 128, tiles_n = (N + TC5_MAX_N - 1) / TC5_MAX_N;
-    const int per_n = std::max(1, 2 * sm_count() / tiles_n);
+    const int per_n = std::max(1, sm_count() / tiles_n);
     dim3 grid(std::min(tiles_m, per_n), tiles_n);
     kern<<<grid, TC5_THREADS, Tc5Smem::TOTAL, stream>>>(xop, wop, ep, M, N, kwords, tiles_m);
     return check_launch("bcontract_tc5_kernel");
