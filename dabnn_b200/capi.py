@@ -63,6 +63,7 @@ _SIGNATURES = {
     "dabnn_net_set_profiling": [_p, _i],
     "dabnn_net_layer_times": [_p, C.POINTER(C.c_char_p), C.POINTER(_f), _i, C.POINTER(_i)],
     "dabnn_measure_engine_peak": [_i, C.POINTER(C.c_double)],
+    "dabnn_measure_tf32_peak": [C.POINTER(C.c_double)],
     "dabnn_engine_status": [C.POINTER(_i)],
     "dabnn_last_error": [],
     "dabnn_version": [],

@@ -215,5 +215,6 @@ extern "C" int dabnn_engine_status(int* status) {
     DABNN_REQUIRE(status, DABNN_ERR_ARG, "null output");
     DABNN_CUDA_OK(cudaDeviceSynchronize());
     DABNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_tc5_status, sizeof(int)));
+    if (*status == 0) return fconv_tc5_status(status);   // the float convolution keeps its own word (codes 11-14)
     return DABNN_OK;
 }

@@ -1,0 +1,292 @@
+// Float convolution on the 5th-generation tensor cores: tcgen05.mma kind::tf32, three products per
+// fp32 product (x = hi + lo with hi, lo representable in tf32; hi*hi + hi*lo + lo*hi keeps the error
+// below 2^-22 relative), fp32 accumulators in TMEM.
+//
+// A CTA (one per SM, persistent over tiles of 128 output pixels) owns one block of up to 64 output
+// channels.  Its weights are split into hi / lo once and stay in shared memory for the life of the
+// CTA in the K-major canonical layout of UMMA descriptors (8 rows x 16 B core matrices).  Three
+// kinds of warps meet only at mbarriers:
+//   * 8 producer warps; thread (r, h) gathers 8 consecutive k of pixel row r per 16-float K chunk
+//     (implicit im2col through a k -> (offset, ky, kx) table; validity of a tap comes from two
+//     per-row bit masks, so there is no division and no compare in the loop), splits them and
+//     stores hi and lo into a ring of 16 KB stages.  The gather runs one chunk ahead.
+//   * 1 MMA warp: one lane issues, per 8-float slice, lo*hi, hi*lo and hi*hi (M = 128, N = channel
+//     block, K = 8) into one of four TMEM accumulators.
+//   * 8 epilogue warps: thread (r, half) reads 32 accumulator columns of row r, adds the bias,
+//     applies the affine (product and sum rounded separately) and the relu and parks the row in a
+//     shared staging tile, from which all 256 threads write coalesced 16-byte stores.
+// Every mbarrier wait is bounded (see bcontract_tc5.cuh): on a time-out the CTA records a code in
+// the device status word, raises its abort flag, frees its TMEM and returns.
+#pragma once
+#include "bcontract_tc5.cuh"
+
+namespace dabnn {
+
+constexpr int FT_N = 64;                        // channel block
+constexpr int FT_CHUNK = 16;                    // floats of K per ring stage (two MMA slices of 8)
+constexpr int FT_MAXK = 256;                    // padded K the resident weights may have
+constexpr int FT_ACCS = 4;
+constexpr int FT_PRODUCERS = 256, FT_EPILOGUE = 256;
+constexpr int FT_THREADS = FT_PRODUCERS + FT_EPILOGUE + 32;
+constexpr int FT_MMA_WARP = (FT_PRODUCERS + FT_EPILOGUE) / 32;
+constexpr int FT_HALF_BYTES = 128 * FT_CHUNK * 4;        // hi (or lo) part of a stage: 8 KB
+constexpr int FT_STAGE_BYTES = 2 * FT_HALF_BYTES;
+constexpr int FT_A_SBO = (FT_CHUNK / 4) * 128;           // 8-row group stride inside a stage
+constexpr int FT_SPITCH = FT_N + 4;                      // staging tile pitch in floats
+constexpr int FT_STILE_BYTES = 128 * FT_SPITCH * 4;
+constexpr int FT_MAX_STAGES = 8;
+
+// hi / lo parts of the resident weights of a channel block: K-major canonical layout over the whole padded K
+__host__ __device__ inline int ft_weight_bytes(int kpad) { return 2 * (FT_N / 8) * (kpad / 4) * 128; }
+__host__ __device__ inline int ft_smem_bytes(int kpad, int stages) {
+    return 1024 + ft_weight_bytes(kpad) + stages * FT_STAGE_BYTES + FT_STILE_BYTES;
+}
+
+__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t saddr, int lbo, int sbo) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
+           ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t ad, uint64_t bd, uint32_t idesc, uint32_t accum) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+                 ::"r"(d_tmem), "l"(ad), "l"(bd), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+    hi = to_tf32(x);
+    lo = to_tf32(x - __uint_as_float(hi));
+}
+
+__global__ void __launch_bounds__(FT_THREADS, 1)
+    fconv_tc5_kernel(const FconvParams p, const int M, const int K, const int kpad, const int ntiles_m, const int stages) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t bar_full[FT_MAX_STAGES], bar_empty[FT_MAX_STAGES], bar_acc_full[FT_ACCS], bar_acc_empty[FT_ACCS];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_abort, epi_abort;
+    __shared__ int tab_off[FT_MAXK];        // k -> float offset of (ky, kx, ci) from the window's first pixel
+    __shared__ uint32_t tab_yx[FT_MAXK];    // k -> ky | kx << 8; k >= K -> bit 31 (never valid)
+    __shared__ __align__(16) float chan_bias[FT_N], chan_a[FT_N], chan_b[FT_N];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.y * FT_N;
+    const int n_this = min(FT_N, p.cout - n0);                 // multiple of 16 (host-checked)
+    unsigned char* wbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    const int w_sbo = (kpad / 4) * 128, w_half = (FT_N / 8) * w_sbo;
+    unsigned char* stage0 = wbase + 2 * w_half;
+    float* stile = reinterpret_cast<float*>(stage0 + stages * FT_STAGE_BYTES);
+    const int nchunks = (kpad + FT_CHUNK - 1) / FT_CHUNK;
+    const volatile int* abort_flag = &s_abort;
+    constexpr int TMEM_COLS = FT_ACCS * FT_N;                  // 256
+
+    // ---- set-up (all threads) ----
+    if (warp == FT_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid == 0) {
+        for (int i = 0; i < stages; i++) { mbar_init(&bar_full[i], FT_PRODUCERS); mbar_init(&bar_empty[i], 1); }
+        for (int i = 0; i < FT_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], FT_EPILOGUE); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::);
+        s_abort = 0;
+        epi_abort = 0;
+    }
+    for (int k = tid; k < FT_MAXK; k += FT_THREADS) {
+        if (k < K) {
+            const int tap = k / p.cin, ky = tap / p.kw, kx = tap - ky * p.kw;
+            tab_off[k] = (ky * p.dil_h * p.w + kx * p.dil_w) * p.cin + (k - tap * p.cin);
+            tab_yx[k] = (uint32_t)ky | ((uint32_t)kx << 8);
+        } else {
+            tab_off[k] = 0;
+            tab_yx[k] = 0x80000000u;
+        }
+    }
+    if (tid < FT_N) {
+        const bool in = tid < n_this;
+        chan_bias[tid] = (in && p.bias) ? __ldg(p.bias + n0 + tid) : 0.f;
+        chan_a[tid] = (in && p.a) ? __ldg(p.a + n0 + tid) : 1.f;
+        chan_b[tid] = (in && p.a) ? __ldg(p.b + n0 + tid) : 0.f;
+    }
+    // resident weights: element (n, k) -> (n / 8) * w_sbo + (k / 4) * 128 + (n % 8) * 16 + (k % 4) * 4
+    for (int idx = tid; idx < FT_N * kpad; idx += FT_THREADS) {
+        const int n = idx / kpad, k = idx - n * kpad;
+        const float v = (n < n_this && k < K) ? __ldg(p.wgt + (size_t)(n0 + n) * K + k) : 0.f;
+        uint32_t hi, lo;
+        split_tf32(v, hi, lo);
+        const int off = (n >> 3) * w_sbo + (k >> 2) * 128 + (n & 7) * 16 + (k & 3) * 4;
+        *reinterpret_cast<uint32_t*>(wbase + off) = hi;
+        *reinterpret_cast<uint32_t*>(wbase + w_half + off) = lo;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (tid < FT_PRODUCERS) {
+        // =========================== producers: thread = (pixel row, 8-float half of the chunk) ===========================
+        const int r = tid & 127, h = tid >> 7;
+        const int roff = (r >> 3) * FT_A_SBO + (r & 7) * 16 + h * 2 * 128;
+        const int ohw = p.oh * p.ow;
+        uint32_t g = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x) {
+            const int pm = tile * 128 + r;
+            long long base = 0;
+            uint32_t my = 0, mx = 0;   // bit ky / kx set <=> that tap row / column lies inside the image for this pixel
+            if (pm < M) {
+                const int img = pm / ohw, rem = pm - img * ohw, oy = rem / p.ow, ox = rem - oy * p.ow;
+                const int iy0 = oy * p.stride_h - p.pad_h, ix0 = ox * p.stride_w - p.pad_w;
+                base = (((long long)img * p.h + iy0) * p.w + ix0) * p.cin;
+                for (int ky = 0; ky < p.kh; ky++) my |= ((unsigned)(iy0 + ky * p.dil_h) < (unsigned)p.h ? 1u : 0u) << ky;
+                for (int kx = 0; kx < p.kw; kx++) mx |= ((unsigned)(ix0 + kx * p.dil_w) < (unsigned)p.w ? 1u : 0u) << kx;
+            }
+            const float* src = p.in + base;
+            auto gather = [&](int c, float (&v)[8]) {
+                const int k0 = c * FT_CHUNK + h * 8;
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const uint32_t yx = tab_yx[k0 + q];
+                    const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
+                    v[q] = valid ? __ldg(src + tab_off[k0 + q]) : 0.f;
+                }
+            };
+            float cur[8], nxt[8];
+            gather(0, cur);
+            for (int c = 0; c < nchunks; c++, g++) {
+                const uint32_t s = g % stages, use = g / stages;
+                if (c + 1 < nchunks) gather(c + 1, nxt);
+                if (use >= 1 && !mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag)) {
+                    atomicCAS(&g_tc5_status, 0, 11);
+                    s_abort = 1;
+                    ok = false;
+                    break;
+                }
+                uint32_t hi[8], lo[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) split_tf32(cur[q], hi[q], lo[q]);
+                unsigned char* st = stage0 + s * FT_STAGE_BYTES + roff;
+                *reinterpret_cast<uint4*>(st) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(st + 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                *reinterpret_cast<uint4*>(st + FT_HALF_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4*>(st + FT_HALF_BYTES + 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&bar_full[s]);
+#pragma unroll
+                for (int q = 0; q < 8; q++) cur[q] = nxt[q];
+            }
+        }
+    } else if (warp == FT_MMA_WARP) {
+        // =========================== MMA issue: one lane ===========================
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = tf32, both K-major, N = n_this, M = 128
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_this >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            const uint32_t w_hi = smem_u32(wbase), w_lo = w_hi + w_half;
+            uint32_t g = 0;
+            bool ok = true;
+            int i = 0;
+            for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
+                const int accbuf = i % FT_ACCS, accuse = i / FT_ACCS;
+                if (accuse >= 1 && !mbar_wait(&bar_acc_empty[accbuf], (accuse - 1) & 1, abort_flag)) {
+                    atomicCAS(&g_tc5_status, 0, 13);
+                    s_abort = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + accbuf * FT_N;
+                for (int c = 0; c < nchunks; c++, g++) {
+                    const uint32_t s = g % stages, use = g / stages;
+                    if (!mbar_wait(&bar_full[s], use & 1, abort_flag)) {
+                        atomicCAS(&g_tc5_status, 0, 14);
+                        s_abort = 1;
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_hi = smem_u32(stage0 + s * FT_STAGE_BYTES), a_lo = a_hi + FT_HALF_BYTES;
+                    const int slices = min(FT_CHUNK / 8, (kpad - c * FT_CHUNK) / 8);
+                    for (int j = 0; j < slices; j++) {   // one 8-float slice = two 16-byte units
+                        const uint32_t ao = j * 2 * 128, wo = (c * (FT_CHUNK / 4) + j * 2) * 128;
+                        const uint64_t ah = umma_desc_kmajor(a_hi + ao, 128, FT_A_SBO), al = umma_desc_kmajor(a_lo + ao, 128, FT_A_SBO);
+                        const uint64_t bh = umma_desc_kmajor(w_hi + wo, 128, w_sbo), bl = umma_desc_kmajor(w_lo + wo, 128, w_sbo);
+                        mma_tf32_ss(d_tmem, al, bh, idesc, (c > 0 || j > 0) ? 1u : 0u);   // small terms first
+                        mma_tf32_ss(d_tmem, ah, bl, idesc, 1u);
+                        mma_tf32_ss(d_tmem, ah, bh, idesc, 1u);
+                    }
+                    umma_commit(&bar_empty[s]);
+                    if (c == nchunks - 1) umma_commit(&bar_acc_full[accbuf]);
+                }
+            }
+        }
+    } else {
+        // =========================== epilogue ===========================
+        const int et = tid - FT_PRODUCERS;
+        const int r = et & 127, h2 = et >> 7;          // drain role: TMEM lane quarter = warp % 4 = r / 32
+        const int ncol = max(0, min(32, n_this - h2 * 32));   // 0, 16 or 32 columns for this thread
+        int i = 0;
+        for (int tile = blockIdx.x; tile < ntiles_m; tile += gridDim.x, i++) {
+            const int accbuf = i % FT_ACCS, accuse = i / FT_ACCS;
+            const bool okw = mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag);
+            if (!okw) {
+                atomicCAS(&g_tc5_status, 0, 12);
+                s_abort = 1;
+                epi_abort = 1;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (okw && ncol > 0) {
+                const uint32_t t_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * FT_N + h2 * 32;
+                uint32_t v[32];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                               "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                             : "r"(t_addr));
+                if (ncol > 16)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                                 : "r"(t_addr + 16));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float* srow = stile + r * FT_SPITCH + h2 * 32;
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    if (q * 4 >= ncol) break;
+                    float o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int cl = h2 * 32 + q * 4 + e;
+                        float f = __uint_as_float(v[q * 4 + e]);
+                        if (p.bias) f = __fadd_rn(f, chan_bias[cl]);
+                        if (p.a) f = __fadd_rn(__fmul_rn(chan_a[cl], f), chan_b[cl]);
+                        if (p.relu) f = relu_ref(f);
+                        o[e] = f;
+                    }
+                    *reinterpret_cast<float4*>(srow + q * 4) = make_float4(o[0], o[1], o[2], o[3]);
+                }
+            }
+            if (okw) {   // the accumulator has been read: the MMA warp may reuse it
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&bar_acc_empty[accbuf]);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the tile is staged (or abort decided)
+            if (epi_abort) break;
+            // ---- write-out: item = (row, 4 channels); 16 consecutive lanes walk along a row ----
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int it = et + j * FT_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
+                const int row = tile * 128 + rr;
+                if (row < M && c4 < n_this)
+                    __stcs(reinterpret_cast<float4*>(p.out + (size_t)row * p.cout + n0 + c4),
+                           *reinterpret_cast<const float4*>(stile + rr * FT_SPITCH + c4));
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the staging tile may be overwritten
+        }
+    }
+
+    // ---- drain: everybody is past its last use of the tensor memory ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == FT_MMA_WARP) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+}
+
+}  // namespace dabnn

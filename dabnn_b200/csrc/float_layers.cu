@@ -4,6 +4,7 @@
 // sign bits derived from them - are bit-identical to the reference's x86 build.
 #include <cfloat>
 
+#include <algorithm>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -399,6 +400,41 @@ __global__ void __launch_bounds__(FNT, 2) fconv_kernel(const FconvParams p) {
     }
 }
 
+}  // namespace dabnn
+
+#include "fconv_tc5.cuh"
+
+namespace dabnn {
+
+// The tcgen05 kernel takes a convolution whose padded K fits the resident weight block, whose taps
+// fit the 32-bit validity masks and whose channel blocks are MMA-sized; everything else runs on the
+// mma.sync kernel above.  Returns the number of ring stages that fit, or 0 when not eligible.
+static int fconv_tc5_stages(const FconvParams& p, int kpad) {
+    if (kpad > FT_MAXK || p.kh > 32 || p.kw > 32 || (p.cout % 16) != 0) return 0;
+    if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (reinterpret_cast<uintptr_t>(p.in) & 3) != 0) return 0;
+    if ((long long)(p.kh * p.dil_h) * p.w * p.cin >= (1ll << 31)) return 0;
+    static thread_local int budget_device = -1, budget = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev != budget_device) {
+        int optin = 0;
+        cudaFuncAttributes fa;
+        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
+        if (cudaFuncGetAttributes(&fa, fconv_tc5_kernel) != cudaSuccess) return 0;
+        budget = optin - (int)fa.sharedSizeBytes;
+        if (cudaFuncSetAttribute(fconv_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess) return 0;
+        budget_device = dev;
+    }
+    const int stages = (budget - ft_smem_bytes(kpad, 0)) / FT_STAGE_BYTES;
+    return stages < 2 ? 0 : (stages > FT_MAX_STAGES ? FT_MAX_STAGES : stages);
+}
+
+// status word of the tcgen05 float convolution (this translation unit has its own copy of the word)
+int fconv_tc5_status(int* status) {
+    DABNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_tc5_status, sizeof(int)));
+    return DABNN_OK;
+}
+
 int fconv_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b, int relu,
                float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w,
                int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream) {
@@ -414,6 +450,15 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     dim3 grid((n * oh * ow + FTM - 1) / FTM, (cout + FTN - 1) / FTN);
     const FconvParams prm{in, weight, bias, a, b, out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w,
                           stride_h, stride_w, dil_h, dil_w, oh, ow};
+    const int M = n * oh * ow, K = kh * kw * cin, kpad = (K + 7) / 8 * 8;
+    const int stages = fconv_tc5_stages(prm, kpad);
+    if (stages > 0) {
+        const int ntiles_m = (M + 127) / 128, ny = (cout + FT_N - 1) / FT_N;
+        const int per_n = std::max(1, sm_count() / ny);
+        dim3 tgrid(std::min(ntiles_m, per_n), ny);
+        fconv_tc5_kernel<<<tgrid, FT_THREADS, ft_smem_bytes(kpad, stages), stream>>>(prm, M, K, kpad, ntiles_m, stages);
+        return check_launch("fconv_tc5_kernel");
+    }
     fconv_kernel<<<grid, FNT, 0, stream>>>(prm);
     return check_launch("fconv_kernel");
 }

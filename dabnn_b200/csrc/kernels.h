@@ -20,6 +20,7 @@ int elementwise_chain(const float* x, const float* a, const float* b, const floa
 
 // Float convolution with an optional fused per-channel affine and relu applied to the result
 // (conv (+bias) -> a*v+b -> max(v,0)); used for the stem and the downsample shortcuts.
+int fconv_tc5_status(int* status);
 int fconv_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b,
                int relu, float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
                int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream);

@@ -1,7 +1,7 @@
 // Register-resident peak rate of one contraction instruction: the roofline denominator for the
 // binary contraction.  NVIDIA publishes no 1-bit figure for B200, so it is measured: every warp of
 // a full-occupancy grid issues the instruction back to back on eight independent accumulators.
-#include "bcontract.cuh"
+#include "bcontract_tc5.cuh"
 
 namespace dabnn {
 
@@ -34,13 +34,101 @@ __global__ void __launch_bounds__(256) engine_peak_kernel(const uint32_t* __rest
     if (s == 0x7fffffff) out[0] = s;  // keeps the loop alive without a store on the hot path
 }
 
+// tcgen05.mma issued back to back by one thread per SM on fixed shared-memory operands
+// (M = 128, N = 128, 32 bytes of K per instruction), alternating between two TMEM accumulators.
+// KIND 0: kind::i8 (u8 x u8 -> s32), KIND 1: kind::tf32 (-> f32).  A commit + bounded wait closes
+// every batch of 64 instructions so that the issue queue cannot run ahead of the timing.
+template <int KIND>
+__global__ void __launch_bounds__(128, 1) tcgen05_peak_kernel(int batches, int* status) {
+    __shared__ __align__(1024) unsigned char ops[2 * 128 * 32];   // A then B, K-major canonical layout, one 32-byte K slice
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    for (int i = tid; i < (int)sizeof(ops) / 4; i += 128) reinterpret_cast<uint32_t*>(ops)[i] = KIND == 0 ? 0x01000101u : 0x3f800000u;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(256));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::);
+        s_abort = 0;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    if (tid == 0) {
+        // one 32-byte K slice: two 16-byte units 128 B apart, 8-row groups 256 B apart
+        auto desc = [](uint32_t saddr) {
+            return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(256 >> 4) << 32) | ((uint64_t)1 << 46);
+        };
+        const uint64_t ad = desc(smem_u32(ops)), bd = desc(smem_u32(ops) + 128 * 32);
+        const uint32_t idesc = KIND == 0 ? ((2u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24))
+                                         : ((1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24));
+        for (int b = 0; b < batches; b++) {
+            for (int j = 0; j < 64; j++) {
+                const uint32_t d_tmem = tmem_base + (j & 1) * 128, accum = (b | (j >> 1)) ? 1u : 0u;
+                if (KIND == 0)
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+                                 ::"r"(d_tmem), "l"(ad), "l"(bd), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+                else
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+                                 ::"r"(d_tmem), "l"(ad), "l"(bd), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+            }
+            umma_commit(&bar);
+            if (!mbar_wait(&bar, b & 1, &s_abort)) { atomicCAS(status, 0, 1); break; }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256));
+}
+
 }  // namespace dabnn
 
 using namespace dabnn;
 
+// seconds per launch of the tcgen05 issue loop (best of three after a warm-up), or < 0 on failure
+static double time_tcgen05_peak(int kind, int batches) {
+    int* status = nullptr;
+    if (cudaMalloc(&status, sizeof(int)) != cudaSuccess) return -1.0;
+    cudaMemset(status, 0, sizeof(int));
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    float best = 1e30f;
+    for (int rep = 0; rep < 4; rep++) {
+        cudaEventRecord(e0);
+        if (kind == 0) tcgen05_peak_kernel<0><<<sm_count(), 128>>>(batches, status);
+        else tcgen05_peak_kernel<1><<<sm_count(), 128>>>(batches, status);
+        cudaEventRecord(e1);
+        cudaEventSynchronize(e1);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep > 0 && ms < best) best = ms;
+    }
+    int h = 0;
+    cudaMemcpy(&h, status, sizeof(int), cudaMemcpyDeviceToHost);
+    const cudaError_t err = cudaGetLastError();
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(status);
+    return (err != cudaSuccess || h != 0) ? -1.0 : best * 1e-3;
+}
+
 extern "C" int dabnn_measure_engine_peak(int engine, double* bitops_per_second) {
     DABNN_REQUIRE(bitops_per_second, DABNN_ERR_ARG, "null output");
-    DABNN_REQUIRE(engine >= DABNN_ENGINE_POPC && engine <= DABNN_ENGINE_IMMA, DABNN_ERR_ARG, "engine must be POPC, B1 or IMMA");
+    DABNN_REQUIRE(engine >= DABNN_ENGINE_POPC && engine <= DABNN_ENGINE_TCGEN05, DABNN_ERR_ARG, "engine must be POPC, B1, IMMA or TCGEN05");
+    if (engine == DABNN_ENGINE_TCGEN05) {
+        const int batches = 400;
+        const double sec = time_tcgen05_peak(0, batches);
+        if (sec <= 0.0) return fail(DABNN_ERR_CUDA, "tcgen05 peak kernel failed");
+        *bitops_per_second = 2.0 * 128 * 128 * 32 * 64.0 * batches * sm_count() / sec;
+        return DABNN_OK;
+    }
     uint32_t host[2048];
     for (int i = 0; i < 2048; i++) host[i] = (uint32_t)i * 2654435761u;
     uint32_t* in = nullptr;
@@ -70,5 +158,14 @@ extern "C" int dabnn_measure_engine_peak(int engine, double* bitops_per_second) 
     cudaFree(in); cudaFree(out);
     if (err != cudaSuccess) return fail(DABNN_ERR_CUDA, cudaGetErrorString(err));
     *bitops_per_second = ops * 8.0 * iters * 256.0 * grid / (best * 1e-3);
+    return DABNN_OK;
+}
+
+extern "C" int dabnn_measure_tf32_peak(double* flops_per_second) {
+    DABNN_REQUIRE(flops_per_second, DABNN_ERR_ARG, "null output");
+    const int batches = 400;
+    const double sec = time_tcgen05_peak(1, batches);
+    if (sec <= 0.0) return fail(DABNN_ERR_CUDA, "tcgen05 peak kernel failed");
+    *flops_per_second = 2.0 * 128 * 128 * 8 * 64.0 * batches * sm_count() / sec;
     return DABNN_OK;
 }

@@ -231,6 +231,13 @@ def measure_engine_peak(engine):
     return v.value
 
 
+def measure_tf32_peak():
+    """Issue-bound rate of tcgen05.mma kind::tf32 in FLOP/s (the float convolution's denominator)."""
+    v = C.c_double()
+    check(capi.load().dabnn_measure_tf32_peak(C.byref(v)))
+    return v.value
+
+
 def engine_status():
     """0, or the code of the first bounded wait that gave up inside a tcgen05 kernel (synchronises)."""
     v = C.c_int()

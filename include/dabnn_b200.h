@@ -216,9 +216,16 @@ int dabnn_net_layer_times(dabnn_net* net, const char** names, float* ms, int cap
 /* ---------------------------------------------------------------------------------------------
  * Measurement helper: register-resident peak rate (bit-op/s, one op = one xor or one accumulate
  * per bit pair, i.e. 2*m*n*k per MMA) of one contraction instruction on the current device.
- * `engine` as above (POPC / B1 / IMMA).  Used as the roofline denominator of the contraction.
+ * `engine` as above (POPC / B1 / IMMA / TCGEN05; for TCGEN05 one thread per SM issues 128x128x32
+ * kind::i8 instructions on fixed shared-memory operands).  Used as the roofline denominator of the
+ * contraction.
  * ------------------------------------------------------------------------------------------- */
 int dabnn_measure_engine_peak(int engine, double* bitops_per_second);
+
+/* The same for the float convolution: FLOP/s of tcgen05.mma kind::tf32 (128x128x8 per
+ * instruction, one issuing thread per SM).  The float convolution spends three such products per
+ * fp32 product (hi*hi + hi*lo + lo*hi), so its fp32-equivalent ceiling is a third of this. */
+int dabnn_measure_tf32_peak(double* flops_per_second);
 
 /* Diagnostic: synchronises the device and returns, through *status, 0 or the code of the first
  * bounded wait that gave up inside a TCGEN05-engine kernel since the library was loaded (1 = an

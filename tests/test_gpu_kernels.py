@@ -302,7 +302,11 @@ def test_float_layers_random(ops, port, shape):
 
 
 @pytest.mark.parametrize("h,cin,cout,ks,stride,pad,bias", [(32, 3, 64, 7, 2, 3, False), (8, 64, 128, 1, 1, 0, False),
-                                                           (1, 512, 1000, 1, 1, 0, True), (9, 5, 7, 3, 1, 1, True)])
+                                                           (1, 512, 1000, 1, 1, 0, True), (9, 5, 7, 3, 1, 1, True),
+                                                           # tensor-memory path: more tiles than SMs, ragged channel blocks,
+                                                           # padded K of 152 / 144 / 256, a partial last pixel tile
+                                                           (224, 3, 64, 7, 2, 3, True), (14, 256, 48, 1, 1, 0, True),
+                                                           (20, 16, 144, 3, 1, 1, False), (13, 28, 16, 3, 2, 1, True)])
 def test_fconv_vs_oracle(ops, port, h, cin, cout, ks, stride, pad, bias):
     rng = np.random.default_rng(h + cin)
     x = rng.normal(0, 1, (2, h, h, cin)).astype(np.float32)
@@ -319,5 +323,6 @@ def test_no_bounded_wait_gave_up(ops):
 
 
 def test_engine_peaks_are_measurable(ops):
-    peaks = {e: ops.measure_engine_peak(e) for e in ["popc", "b1", "imma"]}
+    peaks = {e: ops.measure_engine_peak(e) for e in ["popc", "b1", "imma", "tcgen05"]}
+    peaks["tf32"] = ops.measure_tf32_peak()
     assert all(v > 1e13 for v in peaks.values()), peaks
