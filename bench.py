@@ -32,7 +32,12 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 IMAGE_HW, CLASSES = 224, 1000
-BITOPS_PER_IMAGE = 3.353e9   # 16 binary 3x3 convolutions, 2*M*N*K each (K = true bits)
+
+
+def measured_traffic():
+    """DRAM bytes per image of each layer class from the committed ncu captures (profiles/traffic.json), or {}."""
+    p = ROOT / "profiles" / "traffic.json"
+    return json.loads(p.read_text()) if p.exists() else {}
 
 
 def measured_peaks():
@@ -94,6 +99,7 @@ def algorithmic_bytes(spec, batch):
     shapes = {spec.input_name: spec.input_shape[1:]}
     t = {x.name: x for x in spec.tensors}
     out = {}
+    flops = {}   # multiply-adds * 2 per class (binary: per bit pair)
 
     def add(cls, n):
         out[cls] = out.get(cls, 0) + n
@@ -106,6 +112,8 @@ def algorithmic_bytes(spec, batch):
             oh = (h + 2 * f["pads"][0] - kh) // f["strides"][0] + 1
             ow = (w + 2 * f["pads"][1] - kw) // f["strides"][1] + 1
             shapes[f["output"]] = (oh, ow, o)
+            cls = "Float Conv" if l.type == "FpConv2D" else "Bin Conv block"
+            flops[cls] = flops.get(cls, 0) + 2.0 * batch * oh * ow * o * kh * kw * c
             if l.type == "FpConv2D":
                 add("Float Conv", batch * (h * w * c + oh * ow * o) * 4 + t[f["weight"]].data.size * 4)
             else:   # fused block: packed input, fp32 shortcut in, fp32 + packed out
@@ -120,7 +128,7 @@ def algorithmic_bytes(spec, batch):
             shapes[f["output"]] = shapes[f["input1"]]
         else:
             shapes[f["output"]] = shapes[f["input"]]
-    return out
+    return out, flops
 
 
 def run_ours(args):
@@ -222,28 +230,34 @@ def run_ours(args):
         hbm_gbs, peak_src = measured_peaks()
         total_ms = sum(classes.values())
         top = max(classes, key=classes.get)
-        alg = algorithmic_bytes(spec, B)
+        alg, flops = algorithmic_bytes(spec, B)
         layers = {k: {"ms": round(v, 4), "share": round(v / total_ms, 4),
                       "GBps": round(alg[k] / (v * 1e-3) / 1e9, 1) if k in alg else None} for k, v in classes.items()}
-        peaks = {e: ops.measure_engine_peak(e) / 1e12 for e in ("imma", "b1", "popc")}
-        eng = "imma" if args.engine == "auto" else args.engine
+        peaks = {e: ops.measure_engine_peak(e) / 1e12 for e in ("tcgen05", "imma", "b1", "popc")}
+        tf32_peak = ops.measure_tf32_peak() / 1e12
+        eng = "tcgen05" if args.engine == "auto" else args.engine
+        traffic = measured_traffic()
         conv_ms = classes.get("Bin Conv block", 0.0)
-        conv_tops = BITOPS_PER_IMAGE * B / (conv_ms * 1e-3) / 1e12 if conv_ms else None
-        if top == "Bin Conv block":
-            roof = {"bound": "tensor", "kernel": f"bcontract_kernel<{eng}> (16 fused binary conv launches)",
-                    "achieved": round(conv_tops, 1), "peak": round(peaks[eng], 1), "unit": "Tbit-op/s",
-                    "frac": round(conv_tops / peaks[eng], 4),
-                    "peak_source": "mma.sync register-resident peak of the engine's instruction, measured in this run",
-                    "traffic": None}
+        conv_tops = flops["Bin Conv block"] / (conv_ms * 1e-3) / 1e12 if conv_ms else None
+        if top == "Float Conv":
+            # three tf32 products are issued per fp32 product; both sides of the fraction count issued products
+            tf = 3.0 * flops[top] / (classes[top] * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": "fconv_tc5_kernel (float convolutions, 3xTF32 on tcgen05 kind::tf32)",
+                    "achieved": round(tf, 1), "peak": round(tf32_peak, 1), "unit": "TFLOP/s", "frac": round(tf / tf32_peak, 4),
+                    "peak_source": "tcgen05.mma kind::tf32 issue loop (128x128x8), measured in this run; "
+                                   "achieved counts the 3 tf32 products issued per fp32 product",
+                    "traffic": traffic.get(top, {}).get("bytes_per_image", 0) * B or None}
         else:
             gbps = alg[top] / (classes[top] * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": top, "achieved": round(gbps, 1), "peak": hbm_gbs, "unit": "GB/s",
-                    "frac": round(gbps / hbm_gbs, 4), "peak_source": peak_src, "traffic": None}
+            names = {"Bin Conv block": f"bcontract_tc5_kernel / bcontract_kernel<{eng}> (16 fused binary conv blocks)"}
+            roof = {"bound": "hbm", "kernel": names.get(top, top), "achieved": round(gbps, 1), "peak": hbm_gbs, "unit": "GB/s",
+                    "frac": round(gbps / hbm_gbs, 4), "peak_source": peak_src,
+                    "traffic": traffic.get(top, {}).get("bytes_per_image", 0) * B or None}
         result = {
             "metric": "Bi-Real-18-shape images/s", "value": round(world * B * args.steps / (ms_dev * 1e-3), 1),
             "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_dev / args.steps, 4), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "b1 x b1 -> s32 (int8 mma.sync on expanded bits) + fp32",
+            "vs_baseline": None, "dtype": "b1 x b1 -> s32 (tcgen05 kind::i8 on bits expanded in shared memory) + fp32 (3xTF32)",
             "data": "synthetic",
             "config": {"workload": f"Bi-Real-Net-18-shaped BNN, 224x224x3 fp32 N(0,1) inputs, random-init, batch {B} per GPU, "
                                    "independent replicas",
@@ -255,7 +269,8 @@ def run_ours(args):
             "gpu_launches": stats["kernels_per_run"] * args.steps,
             "clocks": clocks, "roofline": roof,
             "bconv_total": {"Tbit_op_per_s": round(conv_tops, 1) if conv_tops else None,
-                            "engine_peaks_Tbit_op_per_s": {k: round(v, 1) for k, v in peaks.items()}},
+                            "engine_peaks_Tbit_op_per_s": {k: round(v, 1) for k, v in peaks.items()},
+                            "tf32_peak_TFLOP_per_s": round(tf32_peak, 1)},
             "layers": layers, "device_bytes": stats["device_bytes"], "replica_check": gathered_ok,
         }
     return result, world, rank
@@ -287,7 +302,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1024, help="images per GPU per step")
-    ap.add_argument("--engine", default="auto", choices=["auto", "imma", "b1", "popc"])
+    ap.add_argument("--engine", default="auto", choices=["auto", "tcgen05", "imma", "b1", "popc"])
     ap.add_argument("--cpu-images", type=int, default=4, help="images per host process in the CPU baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

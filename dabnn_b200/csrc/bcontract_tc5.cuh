@@ -78,6 +78,12 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t ad, uint64_t bd, uint32_t idesc, uint32_t accum) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
+                 ::"r"(d_tmem), "l"(ad), "l"(bd), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+
 struct Tc5Smem {
     static constexpr int A_BYTES = 128 * TC5_CHUNK_BYTES;            // 16 KB
     static constexpr int B_BYTES = TC5_MAX_N * TC5_CHUNK_BYTES;      // 16 KB
@@ -129,8 +135,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     if (tid == 0) {
-        for (int i = 0; i < TC5_STAGES; i++) { mbar_init(&bar_full[i], TC5_PRODUCERS); mbar_init(&bar_empty[i], 1); }
-        for (int i = 0; i < TC5_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], TC5_EPILOGUE); }
+        for (int i = 0; i < TC5_STAGES; i++) { mbar_init(&bar_full[i], TC5_PRODUCERS / 32); mbar_init(&bar_empty[i], 1); }
+        for (int i = 0; i < TC5_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], TC5_EPILOGUE / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
         epi_abort = 0;
@@ -189,7 +195,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 const uint32_t s = g % TC5_STAGES, use = g / TC5_STAGES;
                 uint64_t a2, b2;
                 load_next(a2, b2);
-                if (use >= 1 && !mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag)) {
+                if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                     atomicCAS(&g_tc5_status, 0, 1);
                     s_abort = 1;
                     ok = false;
@@ -201,7 +207,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 px += __popcll(a0);
                 if (c == nchunks - 1) popx[i % TC5_POPRING][h][r] = px;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&bar_full[s]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_full[s]);   // one arrival per warp: arrivals on one mbarrier are serialised
                 a0 = a1; b0 = b1; a1 = a2; b1 = b2;
             }
         }
@@ -210,7 +217,12 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         if (lane == 0) {
             // instruction descriptor: D = s32, A = u8, B = u8, both K-major, N = n_this, M = 128
             const uint32_t idesc = (2u << 4) | ((uint32_t)(n_this >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t g = 0;
+            // The issuing thread is a single instruction stream, so its own latency bounds the MMA rate: the
+            // descriptors are built once and advanced by adding byte offsets >> 4 to their address field
+            // (shared-memory addresses stay below 2^18, so the 14-bit field cannot carry).
+            const uint64_t d_a = umma_desc(smem_u32(stage0)), d_b = d_a + (Tc5Smem::A_BYTES >> 4);
+            const bool last_is_half = (kwords % TC5_CHUNK_WORDS) != 0;   // the last chunk holds one 64-bit word
+            uint32_t s = 0, par = 0;
             bool ok = true;
             int i = 0;
             for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
@@ -222,27 +234,28 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + accbuf * n_this;
-                for (int c = 0; c < nchunks; c++, g++) {
-                    const uint32_t s = g % TC5_STAGES, use = g / TC5_STAGES;
-                    if (!mbar_wait(&bar_full[s], use & 1, abort_flag)) {
+                uint32_t accum = 0;
+                for (int c = 0; c < nchunks; c++) {
+                    if (!mbar_wait(&bar_full[s], par, abort_flag)) {
                         atomicCAS(&g_tc5_status, 0, 4);
                         s_abort = 1;
                         ok = false;
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(stage0 + s * Tc5Smem::STAGE_BYTES), b_addr = a_addr + Tc5Smem::A_BYTES;
-                    const int words = min(TC5_CHUNK_WORDS, kwords - c * TC5_CHUNK_WORDS);
-                    for (int j = 0; j < words * 2; j++) {   // one MMA per 32 bytes of K = two 16-byte units
-                        const uint64_t ad = umma_desc(a_addr + j * 2 * TC5_LBO), bd = umma_desc(b_addr + j * 2 * TC5_LBO);
-                        const uint32_t accum = (c > 0 || j > 0) ? 1u : 0u;
-                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                                     "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
-                                     ::"r"(d_tmem), "l"(ad), "l"(bd), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+                    const uint64_t ad = d_a + (uint64_t)(s * (Tc5Smem::STAGE_BYTES >> 4)), bd = d_b + (uint64_t)(s * (Tc5Smem::STAGE_BYTES >> 4));
+                    // one MMA per 32 bytes of K = two 16-byte units = 256 bytes of descriptor address
+                    mma_i8_ss(d_tmem, ad, bd, idesc, accum);
+                    mma_i8_ss(d_tmem, ad + 16, bd + 16, idesc, 1u);
+                    accum = 1u;
+                    if (!(last_is_half && c == nchunks - 1)) {
+                        mma_i8_ss(d_tmem, ad + 32, bd + 32, idesc, 1u);
+                        mma_i8_ss(d_tmem, ad + 48, bd + 48, idesc, 1u);
                     }
                     umma_commit(&bar_empty[s]);
-                    if (c == nchunks - 1) umma_commit(&bar_acc_full[accbuf]);
+                    if (++s == TC5_STAGES) { s = 0; par ^= 1u; }
                 }
+                if (ok) umma_commit(&bar_acc_full[accbuf]);
             }
         }
     } else {
@@ -292,7 +305,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             // ---- drain ----
             const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
             if (blk == 0 && okw) {
-                okw = mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag);
+                okw = __all_sync(0xffffffffu, mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
                 if (!okw) {
                     atomicCAS(&g_tc5_status, 0, 2);
                     s_abort = 1;
@@ -337,7 +350,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             }
             if (blk == nblk - 1 && okw) {   // the whole accumulator has been read
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(&bar_acc_empty[accbuf]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_acc_empty[accbuf]);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
             if (epi_abort) break;

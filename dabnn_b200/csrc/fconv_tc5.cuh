@@ -2,21 +2,30 @@
 // fp32 product (x = hi + lo with hi, lo representable in tf32; hi*hi + hi*lo + lo*hi keeps the error
 // below 2^-22 relative), fp32 accumulators in TMEM.
 //
-// A CTA (one per SM, persistent over tiles of 128 output pixels) owns one block of up to 64 output
-// channels.  Its weights are split into hi / lo once and stay in shared memory for the life of the
-// CTA in the K-major canonical layout of UMMA descriptors (8 rows x 16 B core matrices).  Three
-// kinds of warps meet only at mbarriers:
-//   * 8 producer warps; thread (r, h) gathers 8 consecutive k of pixel row r per 16-float K chunk
-//     (implicit im2col through a k -> (offset, ky, kx) table; validity of a tap comes from two
-//     per-row bit masks, so there is no division and no compare in the loop), splits them and
-//     stores hi and lo into a ring of 16 KB stages.  The gather runs one chunk ahead.
+// A CTA (one per SM, persistent over pixel tiles) owns one block of up to 64 output channels.  Its
+// weights are split into hi / lo once and stay in shared memory for the life of the CTA in the
+// K-major canonical layout of UMMA descriptors (8 rows x 16 B core matrices).  Three kinds of warps
+// meet only at mbarriers:
+//   * 8 producer warps build the pixel operand (implicit im2col), split it and store hi and lo
+//     into a ring of 16 KB stages; thread (r, h) owns 8 consecutive k of pixel row r per 16-float
+//     K chunk.  Two ways to get at the pixels:
+//       ROWS   - a tile is (a 128-pixel segment of) one output row.  The kh input rows under it
+//                are copied once, coalesced, with cp.async into a double-buffered patch in shared
+//                memory (next tile's patch while this tile is expanded), out-of-image parts
+//                zero-filled, so that the k loop is a table look-up and one shared-memory load
+//                per element with no predicate, and every input byte crosses L2 -> SM once per
+//                tile instead of once per tap;
+//       DIRECT - a tile is 128 consecutive output pixels and elements come straight from global
+//                memory through a k -> (offset, ky, kx) table and two per-row validity masks
+//                (1x1 convolutions, where nothing is reused, and windows too large to stage).
 //   * 1 MMA warp: one lane issues, per 8-float slice, lo*hi, hi*lo and hi*hi (M = 128, N = channel
 //     block, K = 8) into one of four TMEM accumulators.
 //   * 8 epilogue warps: thread (r, half) reads 32 accumulator columns of row r, adds the bias,
 //     applies the affine (product and sum rounded separately) and the relu and parks the row in a
 //     shared staging tile, from which all 256 threads write coalesced 16-byte stores.
 // Every mbarrier wait is bounded (see bcontract_tc5.cuh): on a time-out the CTA records a code in
-// the device status word, raises its abort flag, frees its TMEM and returns.
+// the device status word, raises its abort flag, frees its TMEM and returns.  Named barriers are
+// only reached by code paths that every thread of the role takes the same number of times.
 #pragma once
 #include "bcontract_tc5.cuh"
 
@@ -35,11 +44,18 @@ constexpr int FT_A_SBO = (FT_CHUNK / 4) * 128;           // 8-row group stride i
 constexpr int FT_SPITCH = FT_N + 4;                      // staging tile pitch in floats
 constexpr int FT_STILE_BYTES = 128 * FT_SPITCH * 4;
 constexpr int FT_MAX_STAGES = 8;
+constexpr int FT_DIRECT = 0, FT_ROWS = 1;
+constexpr int FT_MAX_PATCH_BYTES = 72 * 1024;            // both patch buffers together
 
 // hi / lo parts of the resident weights of a channel block: K-major canonical layout over the whole padded K
 __host__ __device__ inline int ft_weight_bytes(int kpad) { return 2 * (FT_N / 8) * (kpad / 4) * 128; }
-__host__ __device__ inline int ft_smem_bytes(int kpad, int stages) {
-    return 1024 + ft_weight_bytes(kpad) + stages * FT_STAGE_BYTES + FT_STILE_BYTES;
+// floats per staged input row: the widest segment's window span, up to 3 floats of alignment shift, rounded to 16 bytes
+__host__ __device__ inline int ft_patch_pitch(int ow, int stride_w, int kw, int dil_w, int cin) {
+    const int seg = ow < 128 ? ow : 128;
+    return (((seg - 1) * stride_w + (kw - 1) * dil_w + 1) * cin + 3 + 3) / 4 * 4 + 4;
+}
+__host__ __device__ inline int ft_smem_bytes(int kpad, int stages, int patch_bytes) {
+    return 1024 + ft_weight_bytes(kpad) + patch_bytes + stages * FT_STAGE_BYTES + FT_STILE_BYTES;
 }
 
 __device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t saddr, int lbo, int sbo) {
@@ -55,15 +71,40 @@ __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) 
     hi = to_tf32(x);
     lo = to_tf32(x - __uint_as_float(hi));
 }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
+}
+// barrier over the 256 producers that also ORs a flag: every thread gets the same answer
+__device__ __forceinline__ bool producers_sync_or(bool mine) {
+    uint32_t res;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.or.pred p, 2, %2, q;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(res) : "r"((uint32_t)mine), "n"(FT_PRODUCERS) : "memory");
+    return res != 0;
+}
 
+// pixel rows of tile t: first flattened output pixel and how many of the 128 operand rows are real
+template <int MODE>
+__device__ __forceinline__ void ft_tile_rows(int t, int M, int ow, int nseg, long long& rowbase, int& len) {
+    if (MODE == FT_ROWS) {
+        const int line = t / nseg, seg = t - line * nseg;
+        rowbase = (long long)line * ow + seg * 128;
+        len = min(128, ow - seg * 128);
+    } else {
+        rowbase = (long long)t * 128;
+        len = (int)min(128ll, (long long)M - rowbase);
+    }
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(FT_THREADS, 1)
-    fconv_tc5_kernel(const FconvParams p, const int M, const int K, const int kpad, const int ntiles_m, const int stages) {
+    fconv_tc5_kernel(const FconvParams p, const int M, const int K, const int kpad, const int ntiles, const int stages,
+                     const int nseg, const int pitch, const int vec16) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bar_full[FT_MAX_STAGES], bar_empty[FT_MAX_STAGES], bar_acc_full[FT_ACCS], bar_acc_empty[FT_ACCS];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_abort, epi_abort;
-    __shared__ int tab_off[FT_MAXK];        // k -> float offset of (ky, kx, ci) from the window's first pixel
-    __shared__ uint32_t tab_yx[FT_MAXK];    // k -> ky | kx << 8; k >= K -> bit 31 (never valid)
+    __shared__ __align__(16) int tab_off[FT_MAXK];   // k -> float offset of (ky, kx, ci): in the patch (ROWS) or the image (DIRECT)
+    __shared__ uint32_t tab_yx[FT_MAXK];             // DIRECT: k -> ky | kx << 8; k >= K -> bit 31 (never valid)
     __shared__ __align__(16) float chan_bias[FT_N], chan_a[FT_N], chan_b[FT_N];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -71,7 +112,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     const int n_this = min(FT_N, p.cout - n0);                 // multiple of 16 (host-checked)
     unsigned char* wbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     const int w_sbo = (kpad / 4) * 128, w_half = (FT_N / 8) * w_sbo;
-    unsigned char* stage0 = wbase + 2 * w_half;
+    float* patch0 = reinterpret_cast<float*>(wbase + 2 * w_half);
+    const int patch_floats = MODE == FT_ROWS ? p.kh * pitch : 0;        // one buffer
+    unsigned char* stage0 = reinterpret_cast<unsigned char*>(patch0 + 2 * patch_floats);
     float* stile = reinterpret_cast<float*>(stage0 + stages * FT_STAGE_BYTES);
     const int nchunks = (kpad + FT_CHUNK - 1) / FT_CHUNK;
     const volatile int* abort_flag = &s_abort;
@@ -83,16 +126,16 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     if (tid == 0) {
-        for (int i = 0; i < stages; i++) { mbar_init(&bar_full[i], FT_PRODUCERS); mbar_init(&bar_empty[i], 1); }
-        for (int i = 0; i < FT_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], FT_EPILOGUE); }
+        for (int i = 0; i < stages; i++) { mbar_init(&bar_full[i], FT_PRODUCERS / 32); mbar_init(&bar_empty[i], 1); }
+        for (int i = 0; i < FT_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], FT_EPILOGUE / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
         epi_abort = 0;
     }
     for (int k = tid; k < FT_MAXK; k += FT_THREADS) {
         if (k < K) {
-            const int tap = k / p.cin, ky = tap / p.kw, kx = tap - ky * p.kw;
-            tab_off[k] = (ky * p.dil_h * p.w + kx * p.dil_w) * p.cin + (k - tap * p.cin);
+            const int tap = k / p.cin, ky = tap / p.kw, kx = tap - ky * p.kw, ci = k - tap * p.cin;
+            tab_off[k] = MODE == FT_ROWS ? ky * pitch + kx * p.dil_w * p.cin + ci : (ky * p.dil_h * p.w + kx * p.dil_w) * p.cin + ci;
             tab_yx[k] = (uint32_t)ky | ((uint32_t)kx << 8);
         } else {
             tab_off[k] = 0;
@@ -125,53 +168,116 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         // =========================== producers: thread = (pixel row, 8-float half of the chunk) ===========================
         const int r = tid & 127, h = tid >> 7;
         const int roff = (r >> 3) * FT_A_SBO + (r & 7) * 16 + h * 2 * 128;
-        const int ohw = p.oh * p.ow;
-        uint32_t g = 0;
+        uint32_t s = 0, use = 0;   // ring stage to fill next and how often the ring has wrapped
         bool ok = true;
-        for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x) {
-            const int pm = tile * 128 + r;
-            long long base = 0;
-            uint32_t my = 0, mx = 0;   // bit ky / kx set <=> that tap row / column lies inside the image for this pixel
-            if (pm < M) {
-                const int img = pm / ohw, rem = pm - img * ohw, oy = rem / p.ow, ox = rem - oy * p.ow;
-                const int iy0 = oy * p.stride_h - p.pad_h, ix0 = ox * p.stride_w - p.pad_w;
-                base = (((long long)img * p.h + iy0) * p.w + ix0) * p.cin;
-                for (int ky = 0; ky < p.kh; ky++) my |= ((unsigned)(iy0 + ky * p.dil_h) < (unsigned)p.h ? 1u : 0u) << ky;
-                for (int kx = 0; kx < p.kw; kx++) mx |= ((unsigned)(ix0 + kx * p.dil_w) < (unsigned)p.w ? 1u : 0u) << kx;
+        // split 8 values and publish them as this thread's share of the next ring stage
+        auto emit = [&](const float (&v)[8]) -> bool {
+            if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
+                atomicCAS(&g_tc5_status, 0, 11);
+                s_abort = 1;
+                return false;
             }
-            const float* src = p.in + base;
-            auto gather = [&](int c, float (&v)[8]) {
-                const int k0 = c * FT_CHUNK + h * 8;
+            uint32_t hi[8], lo[8];
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    const uint32_t yx = tab_yx[k0 + q];
-                    const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
-                    v[q] = valid ? __ldg(src + tab_off[k0 + q]) : 0.f;
+            for (int q = 0; q < 8; q++) split_tf32(v[q], hi[q], lo[q]);
+            unsigned char* st = stage0 + s * FT_STAGE_BYTES + roff;
+            *reinterpret_cast<uint4*>(st) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(st + 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+            *reinterpret_cast<uint4*>(st + FT_HALF_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<uint4*>(st + FT_HALF_BYTES + 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_full[s]);   // one arrival per warp: arrivals on one mbarrier are serialised
+            if (++s == (uint32_t)stages) { s = 0; use++; }
+            return true;
+        };
+        if (MODE == FT_ROWS) {
+            const int row_floats = p.w * p.cin;
+            // copy the kh input rows under tile t into patch buffer b; patch position s of a row is image float
+            // s - shift + gx0, with shift chosen so that 16-byte groups of the patch are 16-byte groups of the image
+            auto stage_patch = [&](int t, int b) {
+                if (t < ntiles) {
+                    const int line = t / nseg, seg = t - line * nseg, img = line / p.oh, oy = line - img * p.oh;
+                    const int iy0 = oy * p.stride_h - p.pad_h;
+                    const int gx0 = (seg * 128 * p.stride_w - p.pad_w) * p.cin;
+                    const float* img_rows = p.in + (long long)img * p.h * row_floats;
+                    float* buf = patch0 + b * patch_floats;
+                    if (vec16) {
+                        const int shift = gx0 & 3, groups = pitch >> 2;
+                        for (int idx = tid; idx < p.kh * groups; idx += FT_PRODUCERS) {
+                            const int ky = idx / groups, j = idx - ky * groups;
+                            const int iy = iy0 + ky * p.dil_h, gidx = 4 * j - shift + gx0;
+                            float* dst = buf + ky * pitch + 4 * j;
+                            if ((unsigned)iy < (unsigned)p.h && gidx >= 0 && gidx + 4 <= row_floats)
+                                cp_async16(smem_u32(dst), img_rows + (long long)iy * row_floats + gidx, 16);
+                            else
+                                *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    } else {
+                        for (int idx = tid; idx < p.kh * pitch; idx += FT_PRODUCERS) {
+                            const int ky = idx / pitch, s = idx - ky * pitch;
+                            const int iy = iy0 + ky * p.dil_h, gidx = s + gx0;
+                            if ((unsigned)iy < (unsigned)p.h && gidx >= 0 && gidx < row_floats)
+                                cp_async4(smem_u32(buf + idx), img_rows + (long long)iy * row_floats + gidx);
+                            else
+                                buf[idx] = 0.f;
+                        }
+                    }
                 }
+                cp_async_commit();
             };
-            float cur[8], nxt[8];
-            gather(0, cur);
-            for (int c = 0; c < nchunks; c++, g++) {
-                const uint32_t s = g % stages, use = g / stages;
-                if (c + 1 < nchunks) gather(c + 1, nxt);
-                if (use >= 1 && !mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag)) {
-                    atomicCAS(&g_tc5_status, 0, 11);
-                    s_abort = 1;
-                    ok = false;
-                    break;
+            stage_patch(blockIdx.x, 0);
+            int i = 0;
+            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, i++) {
+                cp_async_wait<0>();                                   // my copies of this tile's patch have landed
+                if (producers_sync_or(!ok || *abort_flag)) break;      // everybody's have, and the other buffer is idle
+                stage_patch(tile + gridDim.x, (i + 1) & 1);
+                const int seg = tile % nseg, len = min(128, p.ow - seg * 128);
+                const int shift = vec16 ? ((seg * 128 * p.stride_w - p.pad_w) * p.cin) & 3 : 0;
+                const float* pb = patch0 + (i & 1) * patch_floats + shift + min(r, len - 1) * p.stride_w * p.cin;
+                for (int c = 0; c < nchunks && ok; c++) {
+                    const int k0 = c * FT_CHUNK + h * 8;
+                    const int4 o0 = *reinterpret_cast<const int4*>(tab_off + k0), o1 = *reinterpret_cast<const int4*>(tab_off + k0 + 4);
+                    float v[8];
+                    v[0] = k0 + 0 < K ? pb[o0.x] : 0.f; v[1] = k0 + 1 < K ? pb[o0.y] : 0.f;
+                    v[2] = k0 + 2 < K ? pb[o0.z] : 0.f; v[3] = k0 + 3 < K ? pb[o0.w] : 0.f;
+                    v[4] = k0 + 4 < K ? pb[o1.x] : 0.f; v[5] = k0 + 5 < K ? pb[o1.y] : 0.f;
+                    v[6] = k0 + 6 < K ? pb[o1.z] : 0.f; v[7] = k0 + 7 < K ? pb[o1.w] : 0.f;
+                    ok = emit(v);
                 }
-                uint32_t hi[8], lo[8];
+            }
+            cp_async_wait<0>();   // nothing of this thread's is in flight when the CTA winds down
+        } else {
+            const int ohw = p.oh * p.ow;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int pm = tile * 128 + r;
+                long long base = 0;
+                uint32_t my = 0, mx = 0;   // bit ky / kx set <=> that tap row / column lies inside the image for this pixel
+                if (pm < M) {
+                    const int img = pm / ohw, rem = pm - img * ohw, oy = rem / p.ow, ox = rem - oy * p.ow;
+                    const int iy0 = oy * p.stride_h - p.pad_h, ix0 = ox * p.stride_w - p.pad_w;
+                    base = (((long long)img * p.h + iy0) * p.w + ix0) * p.cin;
+                    for (int ky = 0; ky < p.kh; ky++) my |= ((unsigned)(iy0 + ky * p.dil_h) < (unsigned)p.h ? 1u : 0u) << ky;
+                    for (int kx = 0; kx < p.kw; kx++) mx |= ((unsigned)(ix0 + kx * p.dil_w) < (unsigned)p.w ? 1u : 0u) << kx;
+                }
+                const float* src = p.in + base;
+                auto gather = [&](int c, float (&v)[8]) {
+                    const int k0 = c * FT_CHUNK + h * 8;
 #pragma unroll
-                for (int q = 0; q < 8; q++) split_tf32(cur[q], hi[q], lo[q]);
-                unsigned char* st = stage0 + s * FT_STAGE_BYTES + roff;
-                *reinterpret_cast<uint4*>(st) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(st + 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                *reinterpret_cast<uint4*>(st + FT_HALF_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                *reinterpret_cast<uint4*>(st + FT_HALF_BYTES + 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&bar_full[s]);
+                    for (int q = 0; q < 8; q++) {
+                        const uint32_t yx = tab_yx[k0 + q];
+                        const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
+                        v[q] = valid ? __ldg(src + tab_off[k0 + q]) : 0.f;
+                    }
+                };
+                float cur[8], nxt[8];
+                gather(0, cur);
+                for (int c = 0; c < nchunks && ok; c++) {
+                    if (c + 1 < nchunks) gather(c + 1, nxt);   // loads run one chunk ahead of the expansion
+                    ok = emit(cur);
 #pragma unroll
-                for (int q = 0; q < 8; q++) cur[q] = nxt[q];
+                    for (int q = 0; q < 8; q++) cur[q] = nxt[q];
+                }
             }
         }
     } else if (warp == FT_MMA_WARP) {
@@ -179,11 +285,16 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         if (lane == 0) {
             // instruction descriptor: D = f32, A = B = tf32, both K-major, N = n_this, M = 128
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_this >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            const uint32_t w_hi = smem_u32(wbase), w_lo = w_hi + w_half;
-            uint32_t g = 0;
+            // The issuing thread is a single instruction stream, so its own latency bounds the MMA rate: descriptors
+            // are built once and advanced by adding byte offsets >> 4 to their address field (shared-memory addresses
+            // stay below 2^18, so the 14-bit field cannot carry), and the ring position is a counter, not a division.
+            const uint64_t d_a = umma_desc_kmajor(smem_u32(stage0), 128, FT_A_SBO);
+            const uint64_t d_wh = umma_desc_kmajor(smem_u32(wbase), 128, w_sbo), d_wl = umma_desc_kmajor(smem_u32(wbase) + w_half, 128, w_sbo);
+            const bool last_is_half = (kpad % FT_CHUNK) != 0;   // the last chunk holds one 8-float slice
+            uint32_t s = 0, par = 0;
             bool ok = true;
             int i = 0;
-            for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, i++) {
                 const int accbuf = i % FT_ACCS, accuse = i / FT_ACCS;
                 if (accuse >= 1 && !mbar_wait(&bar_acc_empty[accbuf], (accuse - 1) & 1, abort_flag)) {
                     atomicCAS(&g_tc5_status, 0, 13);
@@ -192,28 +303,33 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + accbuf * FT_N;
-                for (int c = 0; c < nchunks; c++, g++) {
-                    const uint32_t s = g % stages, use = g / stages;
-                    if (!mbar_wait(&bar_full[s], use & 1, abort_flag)) {
+                uint64_t bh = d_wh, bl = d_wl;
+                uint32_t accum = 0;
+                for (int c = 0; c < nchunks; c++) {
+                    if (!mbar_wait(&bar_full[s], par, abort_flag)) {
                         atomicCAS(&g_tc5_status, 0, 14);
                         s_abort = 1;
                         ok = false;
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_hi = smem_u32(stage0 + s * FT_STAGE_BYTES), a_lo = a_hi + FT_HALF_BYTES;
-                    const int slices = min(FT_CHUNK / 8, (kpad - c * FT_CHUNK) / 8);
-                    for (int j = 0; j < slices; j++) {   // one 8-float slice = two 16-byte units
-                        const uint32_t ao = j * 2 * 128, wo = (c * (FT_CHUNK / 4) + j * 2) * 128;
-                        const uint64_t ah = umma_desc_kmajor(a_hi + ao, 128, FT_A_SBO), al = umma_desc_kmajor(a_lo + ao, 128, FT_A_SBO);
-                        const uint64_t bh = umma_desc_kmajor(w_hi + wo, 128, w_sbo), bl = umma_desc_kmajor(w_lo + wo, 128, w_sbo);
-                        mma_tf32_ss(d_tmem, al, bh, idesc, (c > 0 || j > 0) ? 1u : 0u);   // small terms first
-                        mma_tf32_ss(d_tmem, ah, bl, idesc, 1u);
-                        mma_tf32_ss(d_tmem, ah, bh, idesc, 1u);
+                    const uint64_t ah = d_a + (uint64_t)(s * (FT_STAGE_BYTES >> 4)), al = ah + (FT_HALF_BYTES >> 4);
+                    // one 8-float slice = two 16-byte units = 256 bytes of descriptor address; small terms first
+                    mma_tf32_ss(d_tmem, al, bh, idesc, accum);
+                    mma_tf32_ss(d_tmem, ah, bl, idesc, 1u);
+                    mma_tf32_ss(d_tmem, ah, bh, idesc, 1u);
+                    accum = 1u;
+                    if (!(last_is_half && c == nchunks - 1)) {
+                        mma_tf32_ss(d_tmem, al + 16, bh + 16, idesc, 1u);
+                        mma_tf32_ss(d_tmem, ah + 16, bl + 16, idesc, 1u);
+                        mma_tf32_ss(d_tmem, ah + 16, bh + 16, idesc, 1u);
                     }
+                    bh += 2 * 16;
+                    bl += 2 * 16;
                     umma_commit(&bar_empty[s]);
-                    if (c == nchunks - 1) umma_commit(&bar_acc_full[accbuf]);
+                    if (++s == (uint32_t)stages) { s = 0; par ^= 1u; }
                 }
+                if (ok) umma_commit(&bar_acc_full[accbuf]);
             }
         }
     } else {
@@ -222,9 +338,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         const int r = et & 127, h2 = et >> 7;          // drain role: TMEM lane quarter = warp % 4 = r / 32
         const int ncol = max(0, min(32, n_this - h2 * 32));   // 0, 16 or 32 columns for this thread
         int i = 0;
-        for (int tile = blockIdx.x; tile < ntiles_m; tile += gridDim.x, i++) {
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, i++) {
             const int accbuf = i % FT_ACCS, accuse = i / FT_ACCS;
-            const bool okw = mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag);
+            long long rowbase;
+            int len;
+            ft_tile_rows<MODE>(tile, M, p.ow, nseg, rowbase, len);
+            const bool okw = __all_sync(0xffffffffu, mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
             if (!okw) {
                 atomicCAS(&g_tc5_status, 0, 12);
                 s_abort = 1;
@@ -263,7 +382,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             if (okw) {   // the accumulator has been read: the MMA warp may reuse it
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(&bar_acc_empty[accbuf]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_acc_empty[accbuf]);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the tile is staged (or abort decided)
             if (epi_abort) break;
@@ -271,9 +391,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const int it = et + j * FT_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
-                const int row = tile * 128 + rr;
-                if (row < M && c4 < n_this)
-                    __stcs(reinterpret_cast<float4*>(p.out + (size_t)row * p.cout + n0 + c4),
+                if (rr < len && c4 < n_this)
+                    __stcs(reinterpret_cast<float4*>(p.out + (size_t)(rowbase + rr) * p.cout + n0 + c4),
                            *reinterpret_cast<const float4*>(stile + rr * FT_SPITCH + c4));
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the staging tile may be overwritten

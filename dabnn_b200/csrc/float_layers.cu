@@ -408,25 +408,52 @@ namespace dabnn {
 
 // The tcgen05 kernel takes a convolution whose padded K fits the resident weight block, whose taps
 // fit the 32-bit validity masks and whose channel blocks are MMA-sized; everything else runs on the
-// mma.sync kernel above.  Returns the number of ring stages that fit, or 0 when not eligible.
-static int fconv_tc5_stages(const FconvParams& p, int kpad) {
-    if (kpad > FT_MAXK || p.kh > 32 || p.kw > 32 || (p.cout % 16) != 0) return 0;
-    if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (reinterpret_cast<uintptr_t>(p.in) & 3) != 0) return 0;
-    if ((long long)(p.kh * p.dil_h) * p.w * p.cin >= (1ll << 31)) return 0;
+// mma.sync kernel above.  Windows larger than 1x1 go through the staged-rows variant when both
+// patch buffers fit beside at least three ring stages.
+struct FconvTc5Plan {
+    int mode = -1, stages = 0, pitch = 0, patch_bytes = 0, vec16 = 0;   // mode < 0: not eligible
+};
+
+static FconvTc5Plan fconv_tc5_plan(const FconvParams& p, int kpad) {
+    FconvTc5Plan plan;
+    if (kpad > FT_MAXK || p.kh > 32 || p.kw > 32 || (p.cout % 16) != 0) return plan;
+    if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (reinterpret_cast<uintptr_t>(p.in) & 3) != 0) return plan;
+    if ((long long)(p.kh * p.dil_h) * p.w * p.cin >= (1ll << 31)) return plan;
     static thread_local int budget_device = -1, budget = 0;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return plan;
     if (dev != budget_device) {
         int optin = 0;
-        cudaFuncAttributes fa;
-        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
-        if (cudaFuncGetAttributes(&fa, fconv_tc5_kernel) != cudaSuccess) return 0;
-        budget = optin - (int)fa.sharedSizeBytes;
-        if (cudaFuncSetAttribute(fconv_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess) return 0;
+        cudaFuncAttributes fa0, fa1;
+        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return plan;
+        if (cudaFuncGetAttributes(&fa0, fconv_tc5_kernel<FT_DIRECT>) != cudaSuccess) return plan;
+        if (cudaFuncGetAttributes(&fa1, fconv_tc5_kernel<FT_ROWS>) != cudaSuccess) return plan;
+        budget = optin - (int)std::max(fa0.sharedSizeBytes, fa1.sharedSizeBytes);
+        if (cudaFuncSetAttribute(fconv_tc5_kernel<FT_DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess) return plan;
+        if (cudaFuncSetAttribute(fconv_tc5_kernel<FT_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess) return plan;
         budget_device = dev;
     }
-    const int stages = (budget - ft_smem_bytes(kpad, 0)) / FT_STAGE_BYTES;
-    return stages < 2 ? 0 : (stages > FT_MAX_STAGES ? FT_MAX_STAGES : stages);
+    auto stages_for = [&](int patch_bytes) {
+        const int st = (budget - ft_smem_bytes(kpad, 0, patch_bytes)) / FT_STAGE_BYTES;
+        return st > FT_MAX_STAGES ? FT_MAX_STAGES : st;
+    };
+    if (p.kh * p.kw > 1) {
+        const int pitch = ft_patch_pitch(p.ow, p.stride_w, p.kw, p.dil_w, p.cin);
+        const int patch_bytes = 2 * p.kh * pitch * 4;
+        if (patch_bytes <= FT_MAX_PATCH_BYTES && stages_for(patch_bytes) >= 3) {
+            plan.mode = FT_ROWS;
+            plan.stages = stages_for(patch_bytes);
+            plan.pitch = pitch;
+            plan.patch_bytes = patch_bytes;
+            plan.vec16 = ((p.w * p.cin) % 4 == 0 && (reinterpret_cast<uintptr_t>(p.in) & 15) == 0) ? 1 : 0;
+            return plan;
+        }
+    }
+    if (stages_for(0) >= 2) {
+        plan.mode = FT_DIRECT;
+        plan.stages = stages_for(0);
+    }
+    return plan;
 }
 
 // status word of the tcgen05 float convolution (this translation unit has its own copy of the word)
@@ -451,12 +478,16 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     const FconvParams prm{in, weight, bias, a, b, out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w,
                           stride_h, stride_w, dil_h, dil_w, oh, ow};
     const int M = n * oh * ow, K = kh * kw * cin, kpad = (K + 7) / 8 * 8;
-    const int stages = fconv_tc5_stages(prm, kpad);
-    if (stages > 0) {
-        const int ntiles_m = (M + 127) / 128, ny = (cout + FT_N - 1) / FT_N;
-        const int per_n = std::max(1, sm_count() / ny);
-        dim3 tgrid(std::min(ntiles_m, per_n), ny);
-        fconv_tc5_kernel<<<tgrid, FT_THREADS, ft_smem_bytes(kpad, stages), stream>>>(prm, M, K, kpad, ntiles_m, stages);
+    const FconvTc5Plan plan = fconv_tc5_plan(prm, kpad);
+    if (plan.mode >= 0) {
+        const int nseg = (ow + 127) / 128, ny = (cout + FT_N - 1) / FT_N;
+        const int ntiles = plan.mode == FT_ROWS ? n * oh * nseg : (M + 127) / 128;
+        dim3 tgrid(std::min(ntiles, std::max(1, sm_count() / ny)), ny);
+        const int smem = ft_smem_bytes(kpad, plan.stages, plan.patch_bytes);
+        if (plan.mode == FT_ROWS)
+            fconv_tc5_kernel<FT_ROWS><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, plan.pitch, plan.vec16);
+        else
+            fconv_tc5_kernel<FT_DIRECT><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, 0, 0);
         return check_launch("fconv_tc5_kernel");
     }
     fconv_kernel<<<grid, FNT, 0, stream>>>(prm);

@@ -306,7 +306,11 @@ def test_float_layers_random(ops, port, shape):
                                                            # tensor-memory path: more tiles than SMs, ragged channel blocks,
                                                            # padded K of 152 / 144 / 256, a partial last pixel tile
                                                            (224, 3, 64, 7, 2, 3, True), (14, 256, 48, 1, 1, 0, True),
-                                                           (20, 16, 144, 3, 1, 1, False), (13, 28, 16, 3, 2, 1, True)])
+                                                           (20, 16, 144, 3, 1, 1, False), (13, 28, 16, 3, 2, 1, True),
+                                                           # staged rows: two segments per output row, with 16-byte copies at
+                                                           # a non-zero alignment shift and with 4-byte copies
+                                                           (136, 3, 16, 3, 1, 1, True), (150, 3, 16, 3, 1, 1, False),
+                                                           (132, 4, 32, 5, 1, 2, True)])
 def test_fconv_vs_oracle(ops, port, h, cin, cout, ks, stride, pad, bias):
     rng = np.random.default_rng(h + cin)
     x = rng.normal(0, 1, (2, h, h, cin)).astype(np.float32)
