@@ -48,7 +48,7 @@ constexpr int TC5_POPRING = 12;                          // tiles of row popcoun
 constexpr int TC5_PRODUCERS = 256, TC5_EPILOGUE = 256;
 constexpr int TC5_THREADS = TC5_PRODUCERS + TC5_EPILOGUE + 32;
 constexpr int TC5_MMA_WARP = (TC5_PRODUCERS + TC5_EPILOGUE) / 32;
-constexpr uint32_t TC5_SPIN_LIMIT = 1u << 22;
+constexpr uint32_t TC5_SPIN_LIMIT = 1u << 22;   // polls before a wait gives up (at least 0.1 s)
 
 __device__ int g_tc5_status;  // 0 = ok; otherwise the code of the first wait that gave up
 
@@ -63,6 +63,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait; gives up (returns false) when the barrier does not flip or the CTA is aborting.
+// SLEEP_NS > 0 makes a waiting thread yield its issue slots between polls: the warps of a role that is
+// ahead of the others would otherwise spend most of the SM's issue bandwidth on polling.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
     const uint32_t addr = smem_u32(bar);
     for (uint32_t it = 0; it < TC5_SPIN_LIMIT; it++) {
@@ -70,6 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
                      : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((it & 1023) == 1023 && *abort_flag) return false;
     }
     return false;
@@ -195,7 +199,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 const uint32_t s = g % TC5_STAGES, use = g / TC5_STAGES;
                 uint64_t a2, b2;
                 load_next(a2, b2);
-                if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
+                if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<64>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                     atomicCAS(&g_tc5_status, 0, 1);
                     s_abort = 1;
                     ok = false;
@@ -305,7 +309,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             // ---- drain ----
             const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
             if (blk == 0 && okw) {
-                okw = __all_sync(0xffffffffu, mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
+                okw = __all_sync(0xffffffffu, mbar_wait<256>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
                 if (!okw) {
                     atomicCAS(&g_tc5_status, 0, 2);
                     s_abort = 1;

@@ -32,13 +32,13 @@
 namespace dabnn {
 
 constexpr int FT_N = 64;                        // channel block
-constexpr int FT_CHUNK = 16;                    // floats of K per ring stage (two MMA slices of 8)
+constexpr int FT_CHUNK = 32;                    // floats of K per ring stage (four MMA slices of 8)
 constexpr int FT_MAXK = 256;                    // padded K the resident weights may have
 constexpr int FT_ACCS = 4;
 constexpr int FT_PRODUCERS = 256, FT_EPILOGUE = 256;
 constexpr int FT_THREADS = FT_PRODUCERS + FT_EPILOGUE + 32;
 constexpr int FT_MMA_WARP = (FT_PRODUCERS + FT_EPILOGUE) / 32;
-constexpr int FT_HALF_BYTES = 128 * FT_CHUNK * 4;        // hi (or lo) part of a stage: 8 KB
+constexpr int FT_HALF_BYTES = 128 * FT_CHUNK * 4;        // hi (or lo) part of a stage: 16 KB
 constexpr int FT_STAGE_BYTES = 2 * FT_HALF_BYTES;
 constexpr int FT_A_SBO = (FT_CHUNK / 4) * 128;           // 8-row group stride inside a stage
 constexpr int FT_SPITCH = FT_N + 4;                      // staging tile pitch in floats
@@ -67,9 +67,11 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t ad, uint64
                  "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}\n"
                  ::"r"(d_tmem), "l"(ad), "l"(bd), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
 }
+// x = hi + lo exactly, hi with its low 13 mantissa bits clear.  The tensor core reads 19 bits of each 32-bit
+// container, so lo loses at most 2^-10 of itself, i.e. 2^-20 of x: two instructions instead of two roundings.
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-    hi = to_tf32(x);
-    lo = to_tf32(x - __uint_as_float(hi));
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
 }
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
@@ -118,7 +120,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     float* stile = reinterpret_cast<float*>(stage0 + stages * FT_STAGE_BYTES);
     const int nchunks = (kpad + FT_CHUNK - 1) / FT_CHUNK;
     const volatile int* abort_flag = &s_abort;
-    constexpr int TMEM_COLS = FT_ACCS * FT_N;                  // 256
+    constexpr int ACC_COLS = 2 * FT_N;                         // hi*hi + lo*hi in the first 64 columns, hi*lo in the others
+    constexpr int TMEM_COLS = FT_ACCS * ACC_COLS;              // 512: all of the tensor memory
 
     // ---- set-up (all threads) ----
     if (warp == FT_MMA_WARP) {
@@ -137,9 +140,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             const int tap = k / p.cin, ky = tap / p.kw, kx = tap - ky * p.kw, ci = k - tap * p.cin;
             tab_off[k] = MODE == FT_ROWS ? ky * pitch + kx * p.dil_w * p.cin + ci : (ky * p.dil_h * p.w + kx * p.dil_w) * p.cin + ci;
             tab_yx[k] = (uint32_t)ky | ((uint32_t)kx << 8);
-        } else {
+        } else {   // padded k: the weights there are zero, so any finite pixel value will do - take the window's first
             tab_off[k] = 0;
-            tab_yx[k] = 0x80000000u;
+            tab_yx[k] = MODE == FT_ROWS ? 0u : 0x80000000u;
         }
     }
     if (tid < FT_N) {
@@ -167,24 +170,25 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     if (tid < FT_PRODUCERS) {
         // =========================== producers: thread = (pixel row, 8-float half of the chunk) ===========================
         const int r = tid & 127, h = tid >> 7;
-        const int roff = (r >> 3) * FT_A_SBO + (r & 7) * 16 + h * 2 * 128;
+        const int roff = (r >> 3) * FT_A_SBO + (r & 7) * 16 + h * 4 * 128;
         uint32_t s = 0, use = 0;   // ring stage to fill next and how often the ring has wrapped
         bool ok = true;
-        // split 8 values and publish them as this thread's share of the next ring stage
-        auto emit = [&](const float (&v)[8]) -> bool {
-            if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
+        // split 16 values and publish them as this thread's share (four 16-byte units) of the next ring stage
+        auto emit = [&](const float (&v)[16]) -> bool {
+            if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<64>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                 atomicCAS(&g_tc5_status, 0, 11);
                 s_abort = 1;
                 return false;
             }
-            uint32_t hi[8], lo[8];
-#pragma unroll
-            for (int q = 0; q < 8; q++) split_tf32(v[q], hi[q], lo[q]);
             unsigned char* st = stage0 + s * FT_STAGE_BYTES + roff;
-            *reinterpret_cast<uint4*>(st) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4*>(st + 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-            *reinterpret_cast<uint4*>(st + FT_HALF_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            *reinterpret_cast<uint4*>(st + FT_HALF_BYTES + 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                uint32_t hi[4], lo[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) split_tf32(v[u * 4 + q], hi[q], lo[q]);
+                *reinterpret_cast<uint4*>(st + u * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(st + FT_HALF_BYTES + u * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_full[s]);   // one arrival per warp: arrivals on one mbarrier are serialised
@@ -236,13 +240,13 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 const int shift = vec16 ? ((seg * 128 * p.stride_w - p.pad_w) * p.cin) & 3 : 0;
                 const float* pb = patch0 + (i & 1) * patch_floats + shift + min(r, len - 1) * p.stride_w * p.cin;
                 for (int c = 0; c < nchunks && ok; c++) {
-                    const int k0 = c * FT_CHUNK + h * 8;
-                    const int4 o0 = *reinterpret_cast<const int4*>(tab_off + k0), o1 = *reinterpret_cast<const int4*>(tab_off + k0 + 4);
-                    float v[8];
-                    v[0] = k0 + 0 < K ? pb[o0.x] : 0.f; v[1] = k0 + 1 < K ? pb[o0.y] : 0.f;
-                    v[2] = k0 + 2 < K ? pb[o0.z] : 0.f; v[3] = k0 + 3 < K ? pb[o0.w] : 0.f;
-                    v[4] = k0 + 4 < K ? pb[o1.x] : 0.f; v[5] = k0 + 5 < K ? pb[o1.y] : 0.f;
-                    v[6] = k0 + 6 < K ? pb[o1.z] : 0.f; v[7] = k0 + 7 < K ? pb[o1.w] : 0.f;
+                    const int k0 = c * FT_CHUNK + h * 16;
+                    float v[16];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int4 o = *reinterpret_cast<const int4*>(tab_off + k0 + u * 4);
+                        v[u * 4 + 0] = pb[o.x]; v[u * 4 + 1] = pb[o.y]; v[u * 4 + 2] = pb[o.z]; v[u * 4 + 3] = pb[o.w];
+                    }
                     ok = emit(v);
                 }
             }
@@ -261,22 +265,32 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     for (int kx = 0; kx < p.kw; kx++) mx |= ((unsigned)(ix0 + kx * p.dil_w) < (unsigned)p.w ? 1u : 0u) << kx;
                 }
                 const float* src = p.in + base;
-                auto gather = [&](int c, float (&v)[8]) {
-                    const int k0 = c * FT_CHUNK + h * 8;
+                auto gather = [&](int c, float (&v)[16]) {
+                    const int k0 = c * FT_CHUNK + h * 16;
+                    if (vec16) {   // channels are a multiple of 4 and 16-byte aligned: a unit is four channels of one tap
 #pragma unroll
-                    for (int q = 0; q < 8; q++) {
-                        const uint32_t yx = tab_yx[k0 + q];
-                        const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
-                        v[q] = valid ? __ldg(src + tab_off[k0 + q]) : 0.f;
+                        for (int u = 0; u < 4; u++) {
+                            const uint32_t yx = tab_yx[k0 + u * 4];
+                            const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
+                            const float4 t = valid ? __ldg(reinterpret_cast<const float4*>(src + tab_off[k0 + u * 4])) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            v[u * 4 + 0] = t.x; v[u * 4 + 1] = t.y; v[u * 4 + 2] = t.z; v[u * 4 + 3] = t.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 16; q++) {
+                            const uint32_t yx = tab_yx[k0 + q];
+                            const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
+                            v[q] = valid ? __ldg(src + tab_off[k0 + q]) : 0.f;
+                        }
                     }
                 };
-                float cur[8], nxt[8];
+                float cur[16], nxt[16];
                 gather(0, cur);
                 for (int c = 0; c < nchunks && ok; c++) {
                     if (c + 1 < nchunks) gather(c + 1, nxt);   // loads run one chunk ahead of the expansion
                     ok = emit(cur);
 #pragma unroll
-                    for (int q = 0; q < 8; q++) cur[q] = nxt[q];
+                    for (int q = 0; q < 16; q++) cur[q] = nxt[q];
                 }
             }
         }
@@ -284,13 +298,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         // =========================== MMA issue: one lane ===========================
         if (lane == 0) {
             // instruction descriptor: D = f32, A = B = tf32, both K-major, N = n_this, M = 128
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_this >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            const uint32_t idesc_m = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 4) << 24);
+            const uint32_t idesc = idesc_m | ((uint32_t)(n_this >> 3) << 17);
+            // The lo rows of the weights follow the hi rows at the same 8-row stride, so with a full channel block one
+            // N = 128 instruction computes hi*[hi; lo] - two instructions (10 KB of operand reads) per slice, not three (18 KB).
+            const bool stacked = n_this == FT_N;
+            const uint32_t idesc2 = idesc_m | ((uint32_t)((2 * FT_N) >> 3) << 17);
             // The issuing thread is a single instruction stream, so its own latency bounds the MMA rate: descriptors
             // are built once and advanced by adding byte offsets >> 4 to their address field (shared-memory addresses
             // stay below 2^18, so the 14-bit field cannot carry), and the ring position is a counter, not a division.
             const uint64_t d_a = umma_desc_kmajor(smem_u32(stage0), 128, FT_A_SBO);
             const uint64_t d_wh = umma_desc_kmajor(smem_u32(wbase), 128, w_sbo), d_wl = umma_desc_kmajor(smem_u32(wbase) + w_half, 128, w_sbo);
-            const bool last_is_half = (kpad % FT_CHUNK) != 0;   // the last chunk holds one 8-float slice
             uint32_t s = 0, par = 0;
             bool ok = true;
             int i = 0;
@@ -302,7 +320,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_tmem = tmem_base + accbuf * FT_N;
+                const uint32_t d_tmem = tmem_base + accbuf * ACC_COLS;
                 uint64_t bh = d_wh, bl = d_wl;
                 uint32_t accum = 0;
                 for (int c = 0; c < nchunks; c++) {
@@ -315,17 +333,22 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ah = d_a + (uint64_t)(s * (FT_STAGE_BYTES >> 4)), al = ah + (FT_HALF_BYTES >> 4);
                     // one 8-float slice = two 16-byte units = 256 bytes of descriptor address; small terms first
-                    mma_tf32_ss(d_tmem, al, bh, idesc, accum);
-                    mma_tf32_ss(d_tmem, ah, bl, idesc, 1u);
-                    mma_tf32_ss(d_tmem, ah, bh, idesc, 1u);
-                    accum = 1u;
-                    if (!(last_is_half && c == nchunks - 1)) {
-                        mma_tf32_ss(d_tmem, al + 16, bh + 16, idesc, 1u);
-                        mma_tf32_ss(d_tmem, ah + 16, bl + 16, idesc, 1u);
-                        mma_tf32_ss(d_tmem, ah + 16, bh + 16, idesc, 1u);
+                    const int slices = min(FT_CHUNK / 8, (kpad - c * FT_CHUNK) / 8);
+#pragma unroll
+                    for (int j = 0; j < FT_CHUNK / 8; j++) {
+                        if (j < slices) {
+                            if (stacked) {
+                                mma_tf32_ss(d_tmem, ah + j * 16, bh + j * 16, idesc2, accum);
+                            } else {
+                                mma_tf32_ss(d_tmem, ah + j * 16, bh + j * 16, idesc, accum);
+                                mma_tf32_ss(d_tmem + FT_N, ah + j * 16, bl + j * 16, idesc, accum);
+                            }
+                            mma_tf32_ss(d_tmem, al + j * 16, bh + j * 16, idesc, 1u);
+                            accum = 1u;
+                        }
                     }
-                    bh += 2 * 16;
-                    bl += 2 * 16;
+                    bh += (FT_CHUNK / 4) * 8;
+                    bl += (FT_CHUNK / 4) * 8;
                     umma_commit(&bar_empty[s]);
                     if (++s == (uint32_t)stages) { s = 0; par ^= 1u; }
                 }
@@ -343,7 +366,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             long long rowbase;
             int len;
             ft_tile_rows<MODE>(tile, M, p.ow, nseg, rowbase, len);
-            const bool okw = __all_sync(0xffffffffu, mbar_wait(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
+            const bool okw = __all_sync(0xffffffffu, mbar_wait<256>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
             if (!okw) {
                 atomicCAS(&g_tc5_status, 0, 12);
                 s_abort = 1;
@@ -351,8 +374,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (okw && ncol > 0) {
-                const uint32_t t_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * FT_N + h2 * 32;
-                uint32_t v[32];
+                const uint32_t t_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * ACC_COLS + h2 * 32;
+                uint32_t v[32], x[32];
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
                                "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
@@ -362,6 +385,15 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                                  : "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
                                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                                  : "r"(t_addr + 16));
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]), "=r"(x[8]),
+                               "=r"(x[9]), "=r"(x[10]), "=r"(x[11]), "=r"(x[12]), "=r"(x[13]), "=r"(x[14]), "=r"(x[15])
+                             : "r"(t_addr + FT_N));
+                if (ncol > 16)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(x[16]), "=r"(x[17]), "=r"(x[18]), "=r"(x[19]), "=r"(x[20]), "=r"(x[21]), "=r"(x[22]), "=r"(x[23]),
+                                   "=r"(x[24]), "=r"(x[25]), "=r"(x[26]), "=r"(x[27]), "=r"(x[28]), "=r"(x[29]), "=r"(x[30]), "=r"(x[31])
+                                 : "r"(t_addr + FT_N + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 float* srow = stile + r * FT_SPITCH + h2 * 32;
 #pragma unroll
@@ -371,7 +403,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
                         const int cl = h2 * 32 + q * 4 + e;
-                        float f = __uint_as_float(v[q * 4 + e]);
+                        float f = __uint_as_float(v[q * 4 + e]) + __uint_as_float(x[q * 4 + e]);   // + the hi*lo part
                         if (p.bias) f = __fadd_rn(f, chan_bias[cl]);
                         if (p.a) f = __fadd_rn(__fmul_rn(chan_a[cl], f), chan_b[cl]);
                         if (p.relu) f = relu_ref(f);

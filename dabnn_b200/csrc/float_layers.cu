@@ -409,7 +409,7 @@ namespace dabnn {
 // The tcgen05 kernel takes a convolution whose padded K fits the resident weight block, whose taps
 // fit the 32-bit validity masks and whose channel blocks are MMA-sized; everything else runs on the
 // mma.sync kernel above.  Windows larger than 1x1 go through the staged-rows variant when both
-// patch buffers fit beside at least three ring stages.
+// patch buffers fit beside at least two ring stages.
 struct FconvTc5Plan {
     int mode = -1, stages = 0, pitch = 0, patch_bytes = 0, vec16 = 0;   // mode < 0: not eligible
 };
@@ -440,7 +440,7 @@ static FconvTc5Plan fconv_tc5_plan(const FconvParams& p, int kpad) {
     if (p.kh * p.kw > 1) {
         const int pitch = ft_patch_pitch(p.ow, p.stride_w, p.kw, p.dil_w, p.cin);
         const int patch_bytes = 2 * p.kh * pitch * 4;
-        if (patch_bytes <= FT_MAX_PATCH_BYTES && stages_for(patch_bytes) >= 3) {
+        if (patch_bytes <= FT_MAX_PATCH_BYTES && stages_for(patch_bytes) >= 2) {
             plan.mode = FT_ROWS;
             plan.stages = stages_for(patch_bytes);
             plan.pitch = pitch;
@@ -452,6 +452,7 @@ static FconvTc5Plan fconv_tc5_plan(const FconvParams& p, int kpad) {
     if (stages_for(0) >= 2) {
         plan.mode = FT_DIRECT;
         plan.stages = stages_for(0);
+        plan.vec16 = (p.cin % 4 == 0 && (reinterpret_cast<uintptr_t>(p.in) & 15) == 0) ? 1 : 0;
     }
     return plan;
 }
@@ -487,7 +488,7 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
         if (plan.mode == FT_ROWS)
             fconv_tc5_kernel<FT_ROWS><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, plan.pitch, plan.vec16);
         else
-            fconv_tc5_kernel<FT_DIRECT><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, 0, 0);
+            fconv_tc5_kernel<FT_DIRECT><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, 0, plan.vec16);
         return check_launch("fconv_tc5_kernel");
     }
     fconv_kernel<<<grid, FNT, 0, stream>>>(prm);
