@@ -112,6 +112,9 @@ struct EpilogueParams {
     long long ld_sc;
     uint64_t* bits;        // sign bits of the final value, [rows][ld_bits words], or nullptr
     long long ld_bits;
+    // TCGEN05 engine only (not an epilogue matter, but it travels with the launch): the weights already expanded
+    // to bytes in the engine's shared-memory stage layout (tc5_expand_weights), or nullptr to expand them per tile
+    const unsigned char* w_expanded;
 };
 
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, int src_bytes) {

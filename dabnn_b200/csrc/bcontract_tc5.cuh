@@ -112,6 +112,24 @@ __device__ __forceinline__ void expand_word(unsigned char* dst, uint64_t w) {
     expand32(dst + 2 * TC5_LBO, (uint32_t)(w >> 32));
 }
 
+// Weights expanded once instead of once per pixel tile: for every 128-channel block and every K chunk one
+// 16 KB image of the stage's weight half, exactly as the producers would write it, so that a stage's weights
+// become one bulk copy (global -> shared, completion on the stage's "full" mbarrier) issued by one thread.
+__host__ __device__ inline size_t tc5_expanded_bytes(int N, int kwords) {
+    return (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * ((kwords + TC5_CHUNK_WORDS - 1) / TC5_CHUNK_WORDS) * Tc5Smem::B_BYTES;
+}
+template <class WOp>
+__global__ void __launch_bounds__(256) tc5_expand_weights_kernel(const WOp wop, const int N, const int kwords, unsigned char* dst) {
+    const int c = blockIdx.x, nt = blockIdx.y, r = threadIdx.x & 127, h = threadIdx.x >> 7;
+    const int q = c * TC5_CHUNK_WORDS + h, n = nt * TC5_MAX_N + r;
+    uint64_t w = 0;
+    if (n < N && q < kwords) {
+        const uint64_t* p = wop.addr(wop.make_row(n), wop.decode(q));
+        if (p) w = __ldg(p);
+    }
+    expand_word(dst + ((size_t)nt * gridDim.x + c) * Tc5Smem::B_BYTES + (r >> 3) * TC5_SBO + (r & 7) * 16 + h * 4 * TC5_LBO, w);
+}
+
 template <class XOp, class WOp>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
     bcontract_tc5_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
@@ -132,6 +150,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
     int tmem_cols = 32;
     while (tmem_cols < TC5_ACCS * n_this) tmem_cols <<= 1;
     const volatile int* abort_flag = &s_abort;
+    const bool pre = ep.w_expanded != nullptr;   // stage weights arrive by bulk copy
 
     // ---- set-up (all threads) ----
     if (warp == TC5_MMA_WARP) {
@@ -139,7 +158,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     if (tid == 0) {
-        for (int i = 0; i < TC5_STAGES; i++) { mbar_init(&bar_full[i], TC5_PRODUCERS / 32); mbar_init(&bar_empty[i], 1); }
+        for (int i = 0; i < TC5_STAGES; i++) { mbar_init(&bar_full[i], TC5_PRODUCERS / 32 + (pre ? 1 : 0)); mbar_init(&bar_empty[i], 1); }
         for (int i = 0; i < TC5_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], TC5_EPILOGUE / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
@@ -169,7 +188,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
     if (tid < TC5_PRODUCERS) {
         // =========================== producers: thread = (operand row, word of the chunk) ===========================
         const int r = tid & 127, h = tid >> 7;
-        const bool has_w = r < n_this;
+        const bool has_w = r < n_this && !pre;
+        const unsigned char* wsrc = pre ? ep.w_expanded + (size_t)blockIdx.y * nchunks * Tc5Smem::B_BYTES : nullptr;
         const RowCtx wrow = wop.make_row(n0 + r);
         const int roff = (r >> 3) * TC5_SBO + (r & 7) * 16 + h * 4 * TC5_LBO;
         uint32_t g = 0;   // chunks produced by this CTA
@@ -204,6 +224,13 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                     s_abort = 1;
                     ok = false;
                     break;
+                }
+                if (pre && tid == 0) {   // this stage's weights: one bulk copy that completes on the stage's "full" barrier
+                    const uint32_t bytes = (uint32_t)n_this * TC5_CHUNK_BYTES, bar = smem_u32(&bar_full[s]);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(smem_u32(stage0 + s * Tc5Smem::STAGE_BYTES + Tc5Smem::A_BYTES)), "l"(wsrc + (size_t)c * Tc5Smem::B_BYTES),
+                                   "r"(bytes), "r"(bar) : "memory");
                 }
                 unsigned char* st = stage0 + s * Tc5Smem::STAGE_BYTES + roff;
                 expand_word(st, a0);

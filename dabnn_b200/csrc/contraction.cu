@@ -112,10 +112,24 @@ static int check_conv_args(const void* in, const void* weight, size_t weight_wor
     return DABNN_OK;
 }
 
+size_t bconv_expanded_weight_bytes(int cout, int kwords) { return tc5_expanded_bytes(cout, kwords); }
+
+int bconv_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int kwords, unsigned char* dst,
+                         cudaStream_t stream) {
+    DABNN_REQUIRE(weight && dst && cout > 0 && kwords > 0, DABNN_ERR_ARG, "expand_weights: bad arguments");
+    DABNN_REQUIRE(weight_words % (size_t)cout == 0 && weight_words / cout >= (size_t)kwords, DABNN_ERR_SHAPE,
+                  "expand_weights: filter rows shorter than kwords");
+    DABNN_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, DABNN_ERR_ARG, "expand_weights: dst must be 16-byte aligned");
+    RowMajorOperand wop{weight, (long long)(weight_words / cout), cout, kwords};
+    dim3 grid((kwords + TC5_CHUNK_WORDS - 1) / TC5_CHUNK_WORDS, (cout + TC5_MAX_N - 1) / TC5_MAX_N);
+    tc5_expand_weights_kernel<<<grid, 256, 0, stream>>>(wop, cout, kwords, dst);
+    return check_launch("tc5_expand_weights_kernel");
+}
+
 int bconv_block_impl(const uint64_t* in_bits, const uint64_t* weight, size_t weight_words, const float* a,
                      const float* b, const float* shortcut, float* out_f32, uint64_t* out_bits, int n, int h,
                      int w, int cw, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
-                     int stride_w, int engine, cudaStream_t stream) {
+                     int stride_w, int engine, cudaStream_t stream, const unsigned char* w_expanded) {
     int rc = check_conv_args(in_bits, weight, weight_words, n, h, w, cw, cout, kh, kw, pad_h, pad_w, stride_h,
                              stride_w);
     if (rc) return rc;
@@ -124,7 +138,7 @@ int bconv_block_impl(const uint64_t* in_bits, const uint64_t* weight, size_t wei
     DABNN_REQUIRE(!out_bits || cout % 64 == 0, DABNN_ERR_SHAPE, "bconv_block: bit output needs cout % 64 == 0");
     const ConvOperand xop = make_conv_operand(in_bits, n, h, w, cw, kh, kw, pad_h, pad_w, stride_h, stride_w);
     RowMajorOperand wop{weight, (long long)(weight_words / cout), cout, xop.kwords};
-    EpilogueParams ep{out_f32, cout, 0, a, b, shortcut, cout, out_bits, cout / 64};
+    EpilogueParams ep{out_f32, cout, 0, a, b, shortcut, cout, out_bits, cout / 64, w_expanded};
     return launch_bcontract(engine, xop, wop, ep, xop.rows, cout, xop.kwords, stream);
 }
 

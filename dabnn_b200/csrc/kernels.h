@@ -7,11 +7,16 @@
 
 namespace dabnn {
 
+// Weights of a binary convolution expanded once to the TCGEN05 engine's stage layout (bytes {0,1}, 8x the packed
+// size): size of the buffer, and the kernel that fills it.  bconv_block_impl takes the buffer as w_expanded.
+size_t bconv_expanded_weight_bytes(int cout, int kwords);
+int bconv_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int kwords, unsigned char* dst,
+                         cudaStream_t stream);
 // bconv + optional affine + optional shortcut + optional sign-bit output (see dabnn_bconv_block).
 int bconv_block_impl(const uint64_t* in_bits, const uint64_t* weight, size_t weight_words, const float* a,
                      const float* b, const float* shortcut, float* out_f32, uint64_t* out_bits, int n, int h,
                      int w, int cw, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
-                     int stride_w, int engine, cudaStream_t stream);
+                     int stride_w, int engine, cudaStream_t stream, const unsigned char* w_expanded = nullptr);
 
 // Elementwise chain on an fp32 NHWC tensor, in one pass:  v = x;  if (a) v = a[c]*v + b[c];
 // if (add) v += add;  if (relu) v = max(v, 0);  optional fp32 store and optional sign-bit store.

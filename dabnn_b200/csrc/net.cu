@@ -58,6 +58,7 @@ struct Op {
     int kh = 0, kw = 0, pad_h = 0, pad_w = 0, stride_h = 1, stride_w = 1;
     int relu = 0;
     bool write_f32 = true, write_bits = false;
+    const unsigned char* w_expanded = nullptr;   // BConvBlock: the weights in the TCGEN05 engine's stage layout
 };
 
 struct Layer {
@@ -87,6 +88,8 @@ struct NetImpl {
     unsigned char* arena = nullptr;
     size_t arena_bytes = 0, weights_bytes = 0, arena_bytes_extra = 0;
     unsigned char* weights = nullptr;
+    unsigned char* expanded = nullptr;   // all binary convolution weights expanded to bytes, once, at load time
+    size_t expanded_bytes = 0;
     const float* cur_input = nullptr;  // device pointer of the images the plan is currently reading
     int cur_batch = 0;
     int input_blob = -1;
@@ -112,6 +115,7 @@ struct NetImpl {
         if (copy_stream) cudaStreamDestroy(copy_stream);
         if (arena) cudaFree(arena);
         if (weights) cudaFree(weights);
+        if (expanded) cudaFree(expanded);
         if (stream) cudaStreamDestroy(stream);
     }
 
@@ -587,6 +591,31 @@ int NetImpl::build() {
         }
         arena_bytes_extra = 2 * sb;
     }
+    if (engine == DABNN_ENGINE_AUTO || engine == DABNN_ENGINE_TCGEN05) {
+        // the weights never change: expand them to the tensor-core engine's byte layout once, not once per pixel tile
+        std::vector<size_t> offs;
+        for (const Op& o : plan) {
+            if (o.kind != OpKind::BConvBlock) continue;
+            offs.push_back(expanded_bytes);
+            expanded_bytes += bconv_expanded_weight_bytes(blobs[o.out].c, o.kh * o.kw * (blobs[o.in].c / 64));
+        }
+        if (expanded_bytes) {
+            if (cudaMalloc(&expanded, expanded_bytes) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(DABNN_ERR_OOM, "cannot allocate the expanded binary weights");
+            }
+            size_t k = 0;
+            for (Op& o : plan) {
+                if (o.kind != OpKind::BConvBlock) continue;
+                unsigned char* dst = expanded + offs[k++];
+                const int rc = bconv_expand_weights(static_cast<const uint64_t*>(o.w->dev), o.w->count, blobs[o.out].c,
+                                                    o.kh * o.kw * (blobs[o.in].c / 64), dst, stream);
+                if (rc) return rc;
+                o.w_expanded = dst;
+            }
+            DABNN_CUDA_OK(cudaStreamSynchronize(stream));
+        }
+    }
     if (profiling) {
         events.resize(plan.size() + 1);
         for (auto& e : events) DABNN_CUDA_OK(cudaEventCreate(&e));
@@ -658,7 +687,7 @@ int NetImpl::run_plan(int batch) {
                                       o.b ? static_cast<const float*>(o.b->dev) : nullptr,
                                       o.in2 >= 0 ? f32(o.in2) : nullptr, f32(o.out),
                                       o.write_bits ? bits(o.out) : nullptr, batch, ib.h, ib.w, ib.c / 64, ob.c, o.kh,
-                                      o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, eng, stream);
+                                      o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, eng, stream, o.w_expanded);
                 break;
             }
             case OpKind::BinConvIm2col: {
@@ -804,7 +833,7 @@ extern "C" int dabnn_net_stats(dabnn_net* net, int* kernels_per_run, size_t* are
     int k = 0;
     for (const auto& o : net->impl.plan) k += o.kind == OpKind::BinConvIm2col ? 2 : 1;
     if (kernels_per_run) *kernels_per_run = k;
-    if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes + net->impl.arena_bytes_extra;
+    if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes + net->impl.arena_bytes_extra + net->impl.expanded_bytes;
     return DABNN_OK;
 }
 extern "C" int dabnn_net_set_profiling(dabnn_net* net, int on) {
