@@ -31,7 +31,7 @@
 
 namespace dabnn {
 
-constexpr int FT_N = 64;                        // channel block
+constexpr int FT_N = 64;                        // channel block (32 when the weights of 64 channels do not fit)
 constexpr int FT_CHUNK = 32;                    // floats of K per ring stage (four MMA slices of 8)
 constexpr int FT_MAXK = 256;                    // padded K the resident weights may have
 constexpr int FT_ACCS = 4;
@@ -48,14 +48,14 @@ constexpr int FT_DIRECT = 0, FT_ROWS = 1;
 constexpr int FT_MAX_PATCH_BYTES = 72 * 1024;            // both patch buffers together
 
 // hi / lo parts of the resident weights of a channel block: K-major canonical layout over the whole padded K
-__host__ __device__ inline int ft_weight_bytes(int kpad) { return 2 * (FT_N / 8) * (kpad / 4) * 128; }
+__host__ __device__ inline int ft_weight_bytes(int kpad, int n_blk) { return 2 * (n_blk / 8) * (kpad / 4) * 128; }
 // floats per staged input row: the widest segment's window span, up to 3 floats of alignment shift, rounded to 16 bytes
 __host__ __device__ inline int ft_patch_pitch(int ow, int stride_w, int kw, int dil_w, int cin) {
     const int seg = ow < 128 ? ow : 128;
     return (((seg - 1) * stride_w + (kw - 1) * dil_w + 1) * cin + 3 + 3) / 4 * 4 + 4;
 }
-__host__ __device__ inline int ft_smem_bytes(int kpad, int stages, int patch_bytes) {
-    return 1024 + ft_weight_bytes(kpad) + patch_bytes + stages * FT_STAGE_BYTES + FT_STILE_BYTES;
+__host__ __device__ inline int ft_smem_bytes(int kpad, int n_blk, int stages, int patch_bytes) {
+    return 1024 + ft_weight_bytes(kpad, n_blk) + patch_bytes + stages * FT_STAGE_BYTES + FT_STILE_BYTES;
 }
 
 __device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t saddr, int lbo, int sbo) {
@@ -100,7 +100,7 @@ __device__ __forceinline__ void ft_tile_rows(int t, int M, int ow, int nseg, lon
 template <int MODE>
 __global__ void __launch_bounds__(FT_THREADS, 1)
     fconv_tc5_kernel(const FconvParams p, const int M, const int K, const int kpad, const int ntiles, const int stages,
-                     const int nseg, const int pitch, const int vec16) {
+                     const int nseg, const int pitch, const int vec16, const int n_blk) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bar_full[FT_MAX_STAGES], bar_empty[FT_MAX_STAGES], bar_acc_full[FT_ACCS], bar_acc_empty[FT_ACCS];
     __shared__ uint32_t tmem_base_s;
@@ -110,10 +110,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     __shared__ __align__(16) float chan_bias[FT_N], chan_a[FT_N], chan_b[FT_N];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.y * FT_N;
-    const int n_this = min(FT_N, p.cout - n0);                 // multiple of 16 (host-checked)
+    const int n0 = blockIdx.y * n_blk;
+    const int n_this = min(n_blk, p.cout - n0);                 // multiple of 16 (host-checked)
     unsigned char* wbase = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-    const int w_sbo = (kpad / 4) * 128, w_half = (FT_N / 8) * w_sbo;
+    const int w_sbo = (kpad / 4) * 128, w_half = (n_blk / 8) * w_sbo;
     float* patch0 = reinterpret_cast<float*>(wbase + 2 * w_half);
     const int patch_floats = MODE == FT_ROWS ? p.kh * pitch : 0;        // one buffer
     unsigned char* stage0 = reinterpret_cast<unsigned char*>(patch0 + 2 * patch_floats);
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         chan_b[tid] = (in && p.a) ? __ldg(p.b + n0 + tid) : 0.f;
     }
     // resident weights: element (n, k) -> (n / 8) * w_sbo + (k / 4) * 128 + (n % 8) * 16 + (k % 4) * 4
-    for (int idx = tid; idx < FT_N * kpad; idx += FT_THREADS) {
+    for (int idx = tid; idx < n_blk * kpad; idx += FT_THREADS) {
         const int n = idx / kpad, k = idx - n * kpad;
         const float v = (n < n_this && k < K) ? __ldg(p.wgt + (size_t)(n0 + n) * K + k) : 0.f;
         uint32_t hi, lo;

@@ -411,7 +411,7 @@ namespace dabnn {
 // mma.sync kernel above.  Windows larger than 1x1 go through the staged-rows variant when both
 // patch buffers fit beside at least two ring stages.
 struct FconvTc5Plan {
-    int mode = -1, stages = 0, pitch = 0, patch_bytes = 0, vec16 = 0;   // mode < 0: not eligible
+    int mode = -1, stages = 0, pitch = 0, patch_bytes = 0, vec16 = 0, n_blk = FT_N;   // mode < 0: not eligible
 };
 
 static FconvTc5Plan fconv_tc5_plan(const FconvParams& p, int kpad) {
@@ -434,9 +434,10 @@ static FconvTc5Plan fconv_tc5_plan(const FconvParams& p, int kpad) {
         budget_device = dev;
     }
     auto stages_for = [&](int patch_bytes) {
-        const int st = (budget - ft_smem_bytes(kpad, 0, patch_bytes)) / FT_STAGE_BYTES;
+        const int st = (budget - ft_smem_bytes(kpad, plan.n_blk, 0, patch_bytes)) / FT_STAGE_BYTES;
         return st > FT_MAX_STAGES ? FT_MAX_STAGES : st;
     };
+    if (stages_for(0) < 2) plan.n_blk = FT_N / 2;   // long K: the weights of 64 channels would leave no room for the ring
     if (p.kh * p.kw > 1) {
         const int pitch = ft_patch_pitch(p.ow, p.stride_w, p.kw, p.dil_w, p.cin);
         const int patch_bytes = 2 * p.kh * pitch * 4;
@@ -481,14 +482,14 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     const int M = n * oh * ow, K = kh * kw * cin, kpad = (K + 7) / 8 * 8;
     const FconvTc5Plan plan = fconv_tc5_plan(prm, kpad);
     if (plan.mode >= 0) {
-        const int nseg = (ow + 127) / 128, ny = (cout + FT_N - 1) / FT_N;
+        const int nseg = (ow + 127) / 128, ny = (cout + plan.n_blk - 1) / plan.n_blk;
         const int ntiles = plan.mode == FT_ROWS ? n * oh * nseg : (M + 127) / 128;
         dim3 tgrid(std::min(ntiles, std::max(1, sm_count() / ny)), ny);
-        const int smem = ft_smem_bytes(kpad, plan.stages, plan.patch_bytes);
+        const int smem = ft_smem_bytes(kpad, plan.n_blk, plan.stages, plan.patch_bytes);
         if (plan.mode == FT_ROWS)
-            fconv_tc5_kernel<FT_ROWS><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, plan.pitch, plan.vec16);
+            fconv_tc5_kernel<FT_ROWS><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, plan.pitch, plan.vec16, plan.n_blk);
         else
-            fconv_tc5_kernel<FT_DIRECT><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, 0, plan.vec16);
+            fconv_tc5_kernel<FT_DIRECT><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, 0, plan.vec16, plan.n_blk);
         return check_launch("fconv_tc5_kernel");
     }
     fconv_kernel<<<grid, FNT, 0, stream>>>(prm);

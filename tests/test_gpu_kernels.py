@@ -310,7 +310,9 @@ def test_float_layers_random(ops, port, shape):
                                                            # staged rows: two segments per output row, with 16-byte copies at
                                                            # a non-zero alignment shift and with 4-byte copies
                                                            (136, 3, 16, 3, 1, 1, True), (150, 3, 16, 3, 1, 1, False),
-                                                           (132, 4, 32, 5, 1, 2, True)])
+                                                           (132, 4, 32, 5, 1, 2, True),
+                                                           # K = 256: 32-channel weight blocks
+                                                           (7, 256, 96, 1, 1, 0, True)])
 def test_fconv_vs_oracle(ops, port, h, cin, cout, ks, stride, pad, bias):
     rng = np.random.default_rng(h + cin)
     x = rng.normal(0, 1, (2, h, h, cin)).astype(np.float32)
