@@ -60,6 +60,9 @@ _SIGNATURES = {
     "dabnn_net_output_name": [_p, _i],
     "dabnn_net_stream": [_p],
     "dabnn_net_stats": [_p, C.POINTER(_i), C.POINTER(_z)],
+    "dabnn_net_set_host_chunk": [_p, _i],
+    "dabnn_net_submit": [_p, _p, _i, C.c_char_p, _p, C.c_size_t, C.POINTER(_i)],
+    "dabnn_net_wait": [_p, _i],
     "dabnn_net_set_profiling": [_p, _i],
     "dabnn_net_layer_times": [_p, C.POINTER(C.c_char_p), C.POINTER(_f), _i, C.POINTER(_i)],
     "dabnn_measure_engine_peak": [_i, C.POINTER(C.c_double)],

@@ -63,18 +63,22 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait; gives up (returns false) when the barrier does not flip or the CTA is aborting.
-// SLEEP_NS > 0 makes a waiting thread yield its issue slots between polls: the warps of a role that is
-// ahead of the others would otherwise spend most of the SM's issue bandwidth on polling.
-template <int SLEEP_NS = 0>
+// HINT_NS > 0 passes a suspend-time hint: the hardware parks the thread until the phase completes or the
+// time runs out, so a role that is ahead of the others does not fill the issue slots with polling.
+template <int HINT_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < TC5_SPIN_LIMIT; it++) {
+    constexpr uint32_t LIMIT = HINT_NS > 0 ? (TC5_SPIN_LIMIT >> 6) : TC5_SPIN_LIMIT;
+    for (uint32_t it = 0; it < LIMIT; it++) {
         uint32_t done;
-        asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (HINT_NS > 0)
+            asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
+                         : "=r"(done) : "r"(addr), "r"(parity), "r"((uint32_t)HINT_NS) : "memory");
+        else
+            asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
+                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
-        if ((it & 1023) == 1023 && *abort_flag) return false;
+        if ((it & (HINT_NS > 0 ? 15u : 1023u)) == (HINT_NS > 0 ? 15u : 1023u) && *abort_flag) return false;
     }
     return false;
 }
@@ -190,26 +194,24 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         const int r = tid & 127, h = tid >> 7;
         const bool has_w = r < n_this && !pre;
         const unsigned char* wsrc = pre ? ep.w_expanded + (size_t)blockIdx.y * nchunks * Tc5Smem::B_BYTES : nullptr;
-        const RowCtx wrow = wop.make_row(n0 + r);
         const int roff = (r >> 3) * TC5_SBO + (r & 7) * 16 + h * 4 * TC5_LBO;
         uint32_t g = 0;   // chunks produced by this CTA
         bool ok = true;
         int i = 0;
         for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
-            const RowCtx xr = xop.make_row(tile * 128 + r);
-            typename XOp::Dec xd = xop.decode(h);   // decode state of the word being *loaded*
-            typename WOp::Dec wd = wop.decode(h);
-            int qload = h;                           // index of the word being loaded
+            typename XOp::Walk xw = xop.walker(tile * 128 + r, h);   // position of the word being *loaded*
+            typename WOp::Walk ww = wop.walker(n0 + r, h);
+            int qload = h;                                           // index of the word being loaded
             auto load_next = [&](uint64_t& a, uint64_t& b) {
                 a = 0; b = 0;
                 if (qload < kwords) {
-                    const uint64_t* p = xop.addr(xr, xd);
+                    const uint64_t* p = xop.cur(xw);
                     if (p) a = __ldg(p);
-                    if (has_w) { const uint64_t* w = wop.addr(wrow, wd); if (w) b = __ldg(w); }
+                    if (has_w) { const uint64_t* w = wop.cur(ww); if (w) b = __ldg(w); }
                 }
                 qload += TC5_CHUNK_WORDS;
-                xop.advance(xd, TC5_CHUNK_WORDS);
-                wop.advance(wd, TC5_CHUNK_WORDS);
+                xop.step(xw, TC5_CHUNK_WORDS);
+                if (has_w) wop.step(ww, TC5_CHUNK_WORDS);
             };
             uint64_t a0, b0, a1, b1;   // words of chunk c and chunk c+1; chunk c+2 is loaded inside the loop
             load_next(a0, b0);
@@ -219,7 +221,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 const uint32_t s = g % TC5_STAGES, use = g / TC5_STAGES;
                 uint64_t a2, b2;
                 load_next(a2, b2);
-                if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<64>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
+                if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<2000>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                     atomicCAS(&g_tc5_status, 0, 1);
                     s_abort = 1;
                     ok = false;
@@ -336,7 +338,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             // ---- drain ----
             const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
             if (blk == 0 && okw) {
-                okw = __all_sync(0xffffffffu, mbar_wait<256>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
+                okw = __all_sync(0xffffffffu, mbar_wait<2000>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
                 if (!okw) {
                     atomicCAS(&g_tc5_status, 0, 2);
                     s_abort = 1;

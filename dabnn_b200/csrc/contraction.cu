@@ -73,7 +73,7 @@ int launch_bcontract(int engine, const XOp& xop, const WOp& wop, const EpilogueP
     if (M <= 0 || N <= 0) return DABNN_OK;
     DABNN_REQUIRE(kwords < (1 << 17), DABNN_ERR_SHAPE, "contraction: K must be below 2^23 bits");
     if (engine == DABNN_ENGINE_AUTO) engine = DABNN_ENGINE_TCGEN05;
-    if (engine == DABNN_ENGINE_TCGEN05 && !tc5_eligible(ep, N)) engine = DABNN_ENGINE_IMMA;
+    if (engine == DABNN_ENGINE_TCGEN05 && (!tc5_eligible(ep, N) || !xop.walkable() || !wop.walkable())) engine = DABNN_ENGINE_IMMA;
     switch (engine) {
         case DABNN_ENGINE_TCGEN05: return launch_tc5(xop, wop, ep, M, N, kwords, stream);
         case DABNN_ENGINE_POPC: return launch_engine<ENG_POPC>(xop, wop, ep, M, N, kwords, stream);

@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         bool ok = true;
         // split 16 values and publish them as this thread's share (four 16-byte units) of the next ring stage
         auto emit = [&](const float (&v)[16]) -> bool {
-            if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<64>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
+            if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<2000>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                 atomicCAS(&g_tc5_status, 0, 11);
                 s_abort = 1;
                 return false;
@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             long long rowbase;
             int len;
             ft_tile_rows<MODE>(tile, M, p.ow, nseg, rowbase, len);
-            const bool okw = __all_sync(0xffffffffu, mbar_wait<256>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
+            const bool okw = __all_sync(0xffffffffu, mbar_wait<2000>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
             if (!okw) {
                 atomicCAS(&g_tc5_status, 0, 12);
                 s_abort = 1;

@@ -96,10 +96,15 @@ struct NetImpl {
     size_t out_offset = 0;             // first image of the sub-batch being computed (kept blobs are full-batch)
 
     // host inputs are streamed in sub-batches: copy of sub-batch k+1 overlaps the kernels of k
-    static constexpr int kHostChunk = 256;
+    int host_chunk = 256;   // images per staging buffer
+    size_t chunk_seq = 0;   // sub-batches copied so far, over all runs: sub-batch i uses staging buffer i & 1
     cudaStream_t copy_stream = nullptr;
     float* staging[2] = {nullptr, nullptr};
     cudaEvent_t copied[2] = {nullptr, nullptr}, consumed[2] = {nullptr, nullptr};
+
+    static constexpr int kTickets = 8;
+    cudaEvent_t tickets[kTickets] = {};
+    int next_ticket = 0;
 
     std::vector<cudaEvent_t> events;
     std::vector<std::string> time_names;
@@ -107,6 +112,7 @@ struct NetImpl {
 
     ~NetImpl() {
         for (auto e : events) cudaEventDestroy(e);
+        for (auto e : tickets) if (e) cudaEventDestroy(e);
         for (int i = 0; i < 2; i++) {
             if (copied[i]) cudaEventDestroy(copied[i]);
             if (consumed[i]) cudaEventDestroy(consumed[i]);
@@ -579,7 +585,7 @@ int NetImpl::build() {
         return fail(DABNN_ERR_OOM, "cannot allocate a " + std::to_string(arena_bytes) + " byte device arena");
     }
     {   // double-buffered staging for host inputs
-        const size_t sb = (size_t)std::min(max_batch, kHostChunk) * in_h * in_w * in_c * sizeof(float);
+        const size_t sb = (size_t)std::min(max_batch, host_chunk) * in_h * in_w * in_c * sizeof(float);
         DABNN_CUDA_OK(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
         for (int i = 0; i < 2; i++) {
             if (cudaMalloc(&staging[i], sb) != cudaSuccess) {
@@ -640,24 +646,27 @@ int NetImpl::run(const float* input, int batch, bool is_device) {
     }
     // host input: sub-batches through two staging buffers; the copy of sub-batch k+1 is issued
     // before the kernels of sub-batch k so that PCIe transfer and compute overlap
-    const int chunk = std::min(max_batch, kHostChunk);
+    const int chunk = std::min(max_batch, host_chunk);
     const int nchunks = (batch + chunk - 1) / chunk;
+    const size_t seq0 = chunk_seq;
+    chunk_seq += nchunks;
     auto issue_copy = [&](int k) -> int {
-        const int i0 = k * chunk, cnt = std::min(chunk, batch - i0), sb = k & 1;
-        if (k >= 2) DABNN_CUDA_OK(cudaStreamWaitEvent(copy_stream, consumed[sb], 0));
+        const int i0 = k * chunk, cnt = std::min(chunk, batch - i0), sb = (int)((seq0 + k) & 1);
+        // the buffer's last reader: sub-batch k - 2 of this run, or the matching sub-batch of the previous run
+        // (a wait on an event that was never recorded returns at once)
+        DABNN_CUDA_OK(cudaStreamWaitEvent(copy_stream, consumed[sb], 0));
         DABNN_CUDA_OK(cudaMemcpyAsync(staging[sb], input + (size_t)i0 * img_floats, (size_t)cnt * img_floats * sizeof(float),
                                       cudaMemcpyHostToDevice, copy_stream));
         DABNN_CUDA_OK(cudaEventRecord(copied[sb], copy_stream));
         return DABNN_OK;
     };
-    // the staging buffers may still be read by the previous run's kernels
-    DABNN_CUDA_OK(cudaEventRecord(consumed[0], stream));
-    DABNN_CUDA_OK(cudaStreamWaitEvent(copy_stream, consumed[0], 0));
+    // Nothing here waits for the previous run as a whole: its last sub-batches still compute while this
+    // run's first copies cross PCIe, which is what lets back-to-back submissions overlap.
     int rc = issue_copy(0);
     for (int k = 0; k < nchunks && rc == DABNN_OK; k++) {
         if (k + 1 < nchunks) rc = issue_copy(k + 1);
         if (rc) break;
-        const int i0 = k * chunk, cnt = std::min(chunk, batch - i0), sb = k & 1;
+        const int i0 = k * chunk, cnt = std::min(chunk, batch - i0), sb = (int)((seq0 + k) & 1);
         DABNN_CUDA_OK(cudaStreamWaitEvent(stream, copied[sb], 0));
         cur_input = staging[sb];
         out_offset = (size_t)i0;
@@ -767,6 +776,13 @@ extern "C" int dabnn_net_configure(dabnn_net* net, int max_batch, int engine) {
     net->impl.max_batch = max_batch; net->impl.engine = engine;
     return DABNN_OK;
 }
+extern "C" int dabnn_net_set_host_chunk(dabnn_net* net, int images) {
+    DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
+    DABNN_REQUIRE(!net->impl.loaded, DABNN_ERR_STATE, "set_host_chunk must precede read");
+    DABNN_REQUIRE(images >= 1, DABNN_ERR_ARG, "host chunk must be >= 1 image");
+    net->impl.host_chunk = images;
+    return DABNN_OK;
+}
 extern "C" int dabnn_net_read_buf(dabnn_net* net, const void* buf, size_t len) {
     DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
     DABNN_REQUIRE(!net->impl.loaded, DABNN_ERR_STATE, "a model has already been read into this net");
@@ -798,6 +814,31 @@ extern "C" int dabnn_net_run(dabnn_net* net, const float* input, int batch, int 
 extern "C" int dabnn_net_sync(dabnn_net* net) {
     DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
     DABNN_CUDA_OK(cudaStreamSynchronize(net->impl.stream));
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_submit(dabnn_net* net, const float* host_input, int batch, const char* blob, float* host_out,
+                                size_t host_floats, int* ticket) {
+    DABNN_REQUIRE(net && blob && host_out && ticket, DABNN_ERR_ARG, "null argument");
+    NetImpl& n = net->impl;
+    DABNN_REQUIRE(n.loaded, DABNN_ERR_STATE, "submit: no model has been read");
+    auto it = n.blob_of.find(blob);
+    if (it == n.blob_of.end()) return fail(DABNN_ERR_NOT_FOUND, std::string("Key ") + blob + " not found.");
+    const Blob& b = n.blobs[it->second];
+    DABNN_REQUIRE(b.keep && it->second != n.input_blob, DABNN_ERR_NOT_FOUND, "submit: the blob is not materialised");
+    DABNN_REQUIRE(batch >= 1 && host_floats >= (size_t)batch * b.per_image(), DABNN_ERR_ARG, "submit: host buffer too small");
+    int rc = n.run(host_input, batch, false);
+    if (rc) return rc;
+    DABNN_CUDA_OK(cudaMemcpyAsync(host_out, n.f32(it->second), (size_t)batch * b.per_image() * 4, cudaMemcpyDeviceToHost, n.stream));
+    const int t = n.next_ticket;
+    if (!n.tickets[t]) DABNN_CUDA_OK(cudaEventCreateWithFlags(&n.tickets[t], cudaEventDisableTiming));
+    DABNN_CUDA_OK(cudaEventRecord(n.tickets[t], n.stream));
+    n.next_ticket = (t + 1) % NetImpl::kTickets;
+    *ticket = t;
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_wait(dabnn_net* net, int ticket) {
+    DABNN_REQUIRE(net && ticket >= 0 && ticket < NetImpl::kTickets && net->impl.tickets[ticket], DABNN_ERR_ARG, "wait: unknown ticket");
+    DABNN_CUDA_OK(cudaEventSynchronize(net->impl.tickets[ticket]));
     return DABNN_OK;
 }
 extern "C" int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4], const float** device_ptr,

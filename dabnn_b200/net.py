@@ -26,6 +26,7 @@ class Net:
         check(capi.load().dabnn_net_create(C.byref(self._h)))
         self.optimize, self.run_fconv, self.strict = True, True, True
         self.max_batch, self.engine = 1, "auto"
+        self.host_chunk = 256   # images per staging buffer for host inputs (see dabnn_net_set_host_chunk)
         self._loaded = False
         self._keep = None
 
@@ -39,6 +40,7 @@ class Net:
         check(lib.dabnn_net_set_flags(self._h, int(self.optimize), int(self.run_fconv), int(self.strict)))
         eng = capi.ENGINES[self.engine] if isinstance(self.engine, str) else int(self.engine)
         check(lib.dabnn_net_configure(self._h, int(self.max_batch), eng))
+        check(lib.dabnn_net_set_host_chunk(self._h, int(self.host_chunk)))
 
     def read(self, path: str):
         self._configure()
@@ -80,6 +82,18 @@ class Net:
     def run_host_ptr(self, ptr: int, batch: int):
         """run() on a raw host pointer (e.g. pinned memory), no Python-side copies."""
         check(capi.load().dabnn_net_run(self._h, C.c_void_p(ptr), batch, 0))
+
+    def submit(self, host_ptr: int, batch: int, blob: str, out_ptr: int, out_floats: int) -> int:
+        """Enqueue run() on a (pinned) host input plus the copy of `blob` into the host buffer at
+        `out_ptr`; returns a ticket for wait().  Keep two submissions in flight to overlap the host
+        copy of one with the kernels of the other."""
+        t = C.c_int()
+        check(capi.load().dabnn_net_submit(self._h, C.c_void_p(host_ptr), batch, blob.encode(), C.c_void_p(out_ptr),
+                                           out_floats, C.byref(t)))
+        return t.value
+
+    def wait(self, ticket: int):
+        check(capi.load().dabnn_net_wait(self._h, ticket))
 
     def sync(self):
         check(capi.load().dabnn_net_sync(self._h))

@@ -185,6 +185,12 @@ int dabnn_net_set_flags(dabnn_net* net, int optimize, int run_fconv, int strict)
 /* Largest batch `run` will be called with (default 1, the reference's only case) and the engine
  * used when optimize != 0.  Must precede read. */
 int dabnn_net_configure(dabnn_net* net, int max_batch, int engine);
+/* Host inputs reach the device in sub-batches of `images` (default 256) through two staging buffers, the copy
+ * of one overlapping the kernels of the one before.  Small sub-batches shorten a single run() (more of the copy
+ * is hidden inside it); with pipelined submissions (dabnn_net_submit) the copy of the next submission hides behind
+ * the current one anyway, and a sub-batch as large as the batch keeps the kernels at their full-batch
+ * efficiency.  Costs 2 * images * H * W * C * 4 bytes of device memory.  Must precede read. */
+int dabnn_net_set_host_chunk(dabnn_net* net, int images);
 /* reference net.cpp:32 Net::read(path) / net.cpp:46 Net::read_buf(ptr): parse the .dab model,
  * upload the weights and build the execution plan (net.cpp:54 prepare).  Unlike the reference the
  * buffer may be released after the call (weights are copied to the device). */
@@ -201,6 +207,16 @@ int dabnn_net_sync(dabnn_net* net);
  * are still materialised exist: network outputs and the outputs of fused groups. */
 int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4], const float** device_ptr,
                        float* to_host, size_t host_floats);
+/* Pipelined serving (no counterpart in the reference, whose run() is synchronous): enqueue run() on a host
+ * input (pinned memory for the copies to be asynchronous) followed by the device-to-host copy of blob `blob`
+ * into `host_out` (capacity `host_floats`), and return at once with a ticket; dabnn_net_wait(ticket) blocks
+ * until that submission's output is in `host_out`.  Submissions execute in order; the host copy of
+ * submission k+1 overlaps the kernels of submission k, so keep two or more in flight (at most 8 tickets
+ * are live; a ticket is reused by the 8th later submission).  The caller keeps `host_input` and `host_out`
+ * untouched until the wait returns. */
+int dabnn_net_submit(dabnn_net* net, const float* host_input, int batch, const char* blob, float* host_out,
+                     size_t host_floats, int* ticket);
+int dabnn_net_wait(dabnn_net* net, int ticket);
 /* Name of the i-th blob that no layer consumes (network outputs); NULL when i is out of range. */
 const char* dabnn_net_output_name(dabnn_net* net, int i);
 /* The CUDA stream (cudaStream_t) the net enqueues on. */
