@@ -37,12 +37,12 @@
 
 namespace dabnn {
 
-constexpr int TC5_CHUNK_WORDS = 2;                       // 128 bits of K per chunk
+constexpr int TC5_CHUNK_WORDS = 4;                       // 256 bits of K per chunk (a thread owns two of the words)
 constexpr int TC5_CHUNK_BYTES = TC5_CHUNK_WORDS * 64;    // operand bytes per row per chunk
 constexpr int TC5_SBO = (TC5_CHUNK_BYTES / 16) * 128;    // byte stride between 8-row groups
 constexpr int TC5_LBO = 128;                             // byte stride between 16-byte K units
 constexpr int TC5_MAX_N = 128;
-constexpr int TC5_STAGES = 4;
+constexpr int TC5_STAGES = 2;
 constexpr int TC5_ACCS = 4;                              // TMEM accumulators (4 x 128 columns = all of TMEM)
 constexpr int TC5_POPRING = 12;                          // tiles of row popcounts in flight (> stages + accumulators)
 constexpr int TC5_PRODUCERS = 256, TC5_EPILOGUE = 256;
@@ -125,13 +125,16 @@ __host__ __device__ inline size_t tc5_expanded_bytes(int N, int kwords) {
 template <class WOp>
 __global__ void __launch_bounds__(256) tc5_expand_weights_kernel(const WOp wop, const int N, const int kwords, unsigned char* dst) {
     const int c = blockIdx.x, nt = blockIdx.y, r = threadIdx.x & 127, h = threadIdx.x >> 7;
-    const int q = c * TC5_CHUNK_WORDS + h, n = nt * TC5_MAX_N + r;
-    uint64_t w = 0;
-    if (n < N && q < kwords) {
-        const uint64_t* p = wop.addr(wop.make_row(n), wop.decode(q));
-        if (p) w = __ldg(p);
+    const int n = nt * TC5_MAX_N + r;
+    for (int j = 0; j < 2; j++) {
+        const int q = c * TC5_CHUNK_WORDS + 2 * h + j;
+        uint64_t w = 0;
+        if (n < N && q < kwords) {
+            const uint64_t* p = wop.addr(wop.make_row(n), wop.decode(q));
+            if (p) w = __ldg(p);
+        }
+        expand_word(dst + ((size_t)nt * gridDim.x + c) * Tc5Smem::B_BYTES + (r >> 3) * TC5_SBO + (r & 7) * 16 + (2 * h + j) * 4 * TC5_LBO, w);
     }
-    expand_word(dst + ((size_t)nt * gridDim.x + c) * Tc5Smem::B_BYTES + (r >> 3) * TC5_SBO + (r & 7) * 16 + h * 4 * TC5_LBO, w);
 }
 
 template <class XOp, class WOp>
@@ -194,33 +197,37 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         const int r = tid & 127, h = tid >> 7;
         const bool has_w = r < n_this && !pre;
         const unsigned char* wsrc = pre ? ep.w_expanded + (size_t)blockIdx.y * nchunks * Tc5Smem::B_BYTES : nullptr;
-        const int roff = (r >> 3) * TC5_SBO + (r & 7) * 16 + h * 4 * TC5_LBO;
-        uint32_t g = 0;   // chunks produced by this CTA
+        const int roff = (r >> 3) * TC5_SBO + (r & 7) * 16 + 2 * h * 4 * TC5_LBO;
+        uint32_t s = 0, use = 0;   // ring stage to fill next and how often the ring has wrapped
         bool ok = true;
         int i = 0;
         for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
-            typename XOp::Walk xw = xop.walker(tile * 128 + r, h);   // position of the word being *loaded*
-            typename WOp::Walk ww = wop.walker(n0 + r, h);
-            int qload = h;                                           // index of the word being loaded
-            auto load_next = [&](uint64_t& a, uint64_t& b) {
-                a = 0; b = 0;
-                if (qload < kwords) {
-                    const uint64_t* p = xop.cur(xw);
-                    if (p) a = __ldg(p);
-                    if (has_w) { const uint64_t* w = wop.cur(ww); if (w) b = __ldg(w); }
+            typename XOp::Walk xw = xop.walker(tile * 128 + r, 2 * h);   // position of the word being *loaded*
+            typename WOp::Walk ww = wop.walker(n0 + r, 2 * h);
+            int qload = 2 * h;                                           // index of the word being loaded
+            struct Pair { uint64_t a[2], b[2]; };
+            auto load_next = [&](Pair& v) {   // words 2h and 2h + 1 of the next chunk
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    v.a[j] = 0; v.b[j] = 0;
+                    if (qload + j < kwords) {
+                        const uint64_t* p = xop.cur(xw);
+                        if (p) v.a[j] = __ldg(p);
+                        if (has_w) { const uint64_t* w = wop.cur(ww); if (w) v.b[j] = __ldg(w); }
+                    }
+                    const int adv = j == 0 ? 1 : TC5_CHUNK_WORDS - 1;
+                    xop.step(xw, adv);
+                    if (has_w) wop.step(ww, adv);
                 }
                 qload += TC5_CHUNK_WORDS;
-                xop.step(xw, TC5_CHUNK_WORDS);
-                if (has_w) wop.step(ww, TC5_CHUNK_WORDS);
             };
-            uint64_t a0, b0, a1, b1;   // words of chunk c and chunk c+1; chunk c+2 is loaded inside the loop
-            load_next(a0, b0);
-            load_next(a1, b1);
+            Pair v0, v1;   // chunk c and chunk c+1; chunk c+2 is loaded inside the loop
+            load_next(v0);
+            load_next(v1);
             int px = 0;
-            for (int c = 0; c < nchunks; c++, g++) {
-                const uint32_t s = g % TC5_STAGES, use = g / TC5_STAGES;
-                uint64_t a2, b2;
-                load_next(a2, b2);
+            for (int c = 0; c < nchunks; c++) {
+                Pair v2;
+                load_next(v2);
                 if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<2000>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                     atomicCAS(&g_tc5_status, 0, 1);
                     s_abort = 1;
@@ -235,14 +242,19 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                                    "r"(bytes), "r"(bar) : "memory");
                 }
                 unsigned char* st = stage0 + s * Tc5Smem::STAGE_BYTES + roff;
-                expand_word(st, a0);
-                if (has_w) expand_word(st + Tc5Smem::A_BYTES, b0);
-                px += __popcll(a0);
+                expand_word(st, v0.a[0]);
+                expand_word(st + 4 * TC5_LBO, v0.a[1]);
+                if (has_w) {
+                    expand_word(st + Tc5Smem::A_BYTES, v0.b[0]);
+                    expand_word(st + Tc5Smem::A_BYTES + 4 * TC5_LBO, v0.b[1]);
+                }
+                px += __popcll(v0.a[0]) + __popcll(v0.a[1]);
                 if (c == nchunks - 1) popx[i % TC5_POPRING][h][r] = px;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_full[s]);   // one arrival per warp: arrivals on one mbarrier are serialised
-                a0 = a1; b0 = b1; a1 = a2; b1 = b2;
+                if (++s == TC5_STAGES) { s = 0; use++; }
+                v0 = v1; v1 = v2;
             }
         }
     } else if (warp == TC5_MMA_WARP) {
@@ -254,7 +266,6 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             // descriptors are built once and advanced by adding byte offsets >> 4 to their address field
             // (shared-memory addresses stay below 2^18, so the 14-bit field cannot carry).
             const uint64_t d_a = umma_desc(smem_u32(stage0)), d_b = d_a + (Tc5Smem::A_BYTES >> 4);
-            const bool last_is_half = (kwords % TC5_CHUNK_WORDS) != 0;   // the last chunk holds one 64-bit word
             uint32_t s = 0, par = 0;
             bool ok = true;
             int i = 0;
@@ -278,12 +289,13 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ad = d_a + (uint64_t)(s * (Tc5Smem::STAGE_BYTES >> 4)), bd = d_b + (uint64_t)(s * (Tc5Smem::STAGE_BYTES >> 4));
                     // one MMA per 32 bytes of K = two 16-byte units = 256 bytes of descriptor address
-                    mma_i8_ss(d_tmem, ad, bd, idesc, accum);
-                    mma_i8_ss(d_tmem, ad + 16, bd + 16, idesc, 1u);
-                    accum = 1u;
-                    if (!(last_is_half && c == nchunks - 1)) {
-                        mma_i8_ss(d_tmem, ad + 32, bd + 32, idesc, 1u);
-                        mma_i8_ss(d_tmem, ad + 48, bd + 48, idesc, 1u);
+                    const int slices = min(2 * TC5_CHUNK_WORDS, 2 * (kwords - c * TC5_CHUNK_WORDS));
+#pragma unroll
+                    for (int j = 0; j < 2 * TC5_CHUNK_WORDS; j++) {
+                        if (j < slices) {
+                            mma_i8_ss(d_tmem, ad + j * 16, bd + j * 16, idesc, accum);
+                            accum = 1u;
+                        }
                     }
                     umma_commit(&bar_empty[s]);
                     if (++s == TC5_STAGES) { s = 0; par ^= 1u; }
