@@ -52,13 +52,6 @@ struct RowMajorOperand {
     __device__ void advance(Dec& d, int words) const { d.word += words; }
     __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row * ld, 0, 0, row < rows}; }
     __device__ const uint64_t* addr(const RowCtx& r, const Dec& d) const { return r.valid ? p + r.base + d.word : nullptr; }
-    // A walker follows one operand row through K in fixed steps with as few instructions per step as the layout
-    // allows: cur() is the address of the current word (nullptr where the operand is zero), step() advances.
-    struct Walk { const uint64_t* ptr; };
-    __host__ __device__ bool walkable() const { return true; }
-    __device__ Walk walker(int row, int word) const { return Walk{row < rows ? p + (long long)row * ld + word : nullptr}; }
-    __device__ const uint64_t* cur(const Walk& w) const { return w.ptr; }
-    __device__ void step(Walk& w, int words) const { if (w.ptr) w.ptr += words; }
 };
 // the reference bgemm's `a`: element (row i, word h) at p[h*ld + i]
 struct ColMajorOperand {
@@ -71,11 +64,6 @@ struct ColMajorOperand {
     __device__ void advance(Dec& d, int words) const { d.off += (long long)words * ld; }
     __device__ RowCtx make_row(int row) const { return RowCtx{(long long)row, 0, 0, row < rows}; }
     __device__ const uint64_t* addr(const RowCtx& r, const Dec& d) const { return r.valid ? p + d.off + r.base : nullptr; }
-    struct Walk { const uint64_t* ptr; };
-    __host__ __device__ bool walkable() const { return true; }
-    __device__ Walk walker(int row, int word) const { return Walk{row < rows ? p + (long long)word * ld + row : nullptr}; }
-    __device__ const uint64_t* cur(const Walk& w) const { return w.ptr; }
-    __device__ void step(Walk& w, int words) const { if (w.ptr) w.ptr += (long long)words * ld; }
 };
 // implicit im2col over packed NHWC bits: row = output pixel, word = (ky*kw + kx)*Cw + cw
 struct ConvOperand {
@@ -110,41 +98,6 @@ struct ConvOperand {
         const int y = r.iy0 + d.ky, x = r.ix0 + d.kx;
         if (!r.valid || (unsigned)y >= (unsigned)H || (unsigned)x >= (unsigned)W) return nullptr;
         return p + (r.base + (long long)y * W + x) * Cw + d.cw;
-    }
-    // Walker: the row's window origin as one pointer, the tap as a 32-bit word offset kept by additions, and the
-    // validity of a tap row / column as two bit masks - no multiplication and no coordinate compare per step.
-    struct Walk {
-        const uint64_t* origin;   // word 0 of the (possibly out-of-image) pixel under tap (0, 0)
-        int off_tap, cw, ky, kx;  // word offset of the current tap from origin; word within the tap; the tap
-        uint32_t my, mx;          // bit ky / kx set <=> that tap row / column is inside the image for this pixel
-    };
-    __host__ __device__ bool walkable() const { return kh <= 32 && kw <= 32; }
-    __device__ Walk walker(int row, int word) const {
-        Walk w;
-        w.my = 0; w.mx = 0;
-        const int img = row / (OH * OW), rem = row - img * (OH * OW);
-        const int oy = rem / OW, ox = rem - oy * OW;
-        const int iy0 = oy * stride_h - pad_h, ix0 = ox * stride_w - pad_w;
-        if (row < rows) {
-            for (int i = 0; i < kh; i++) w.my |= ((unsigned)(iy0 + i) < (unsigned)H ? 1u : 0u) << i;
-            for (int i = 0; i < kw; i++) w.mx |= ((unsigned)(ix0 + i) < (unsigned)W ? 1u : 0u) << i;
-        }
-        w.origin = p + (((long long)img * H + iy0) * W + ix0) * Cw;
-        const int tap = word / Cw;
-        w.ky = tap / kw; w.kx = tap - w.ky * kw; w.cw = word - tap * Cw;
-        w.off_tap = (w.ky * W + w.kx) * Cw;
-        return w;
-    }
-    __device__ const uint64_t* cur(const Walk& w) const {
-        return ((w.my >> w.ky) & (w.mx >> w.kx) & 1u) ? w.origin + (w.off_tap + w.cw) : nullptr;
-    }
-    __device__ void step(Walk& w, int words) const {
-        w.cw += words;
-        while (w.cw >= Cw) {
-            w.cw -= Cw;
-            w.off_tap += Cw;
-            if (++w.kx == kw) { w.kx = 0; ++w.ky; w.off_tap += (W - kw) * Cw; }
-        }
     }
 };
 

@@ -37,12 +37,8 @@
 
 namespace dabnn {
 
-constexpr int TC5_CHUNK_WORDS = 4;                       // 256 bits of K per chunk (a thread owns two of the words)
-constexpr int TC5_CHUNK_BYTES = TC5_CHUNK_WORDS * 64;    // operand bytes per row per chunk
-constexpr int TC5_SBO = (TC5_CHUNK_BYTES / 16) * 128;    // byte stride between 8-row groups
 constexpr int TC5_LBO = 128;                             // byte stride between 16-byte K units
 constexpr int TC5_MAX_N = 128;
-constexpr int TC5_STAGES = 2;
 constexpr int TC5_ACCS = 4;                              // TMEM accumulators (4 x 128 columns = all of TMEM)
 constexpr int TC5_POPRING = 12;                          // tiles of row popcounts in flight (> stages + accumulators)
 constexpr int TC5_PRODUCERS = 256, TC5_EPILOGUE = 256;
@@ -52,9 +48,9 @@ constexpr uint32_t TC5_SPIN_LIMIT = 1u << 22;   // polls before a wait gives up 
 
 __device__ int g_tc5_status;  // 0 = ok; otherwise the code of the first wait that gave up
 
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, int sbo) {
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((TC5_LBO >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((TC5_SBO >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46);  // version 1, no swizzle
+           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46);  // version 1, no swizzle
 }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -92,14 +88,23 @@ __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t ad, uint64_t
                  ::"r"(d_tmem), "l"(ad), "l"(bd), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
 }
 
-struct Tc5Smem {
-    static constexpr int A_BYTES = 128 * TC5_CHUNK_BYTES;            // 16 KB
-    static constexpr int B_BYTES = TC5_MAX_N * TC5_CHUNK_BYTES;      // 16 KB
+// Shapes that depend on the K chunk: CW 64-bit words per chunk (a producer thread owns CW / 2 of them) and
+// 8 / CW ring stages, 128 KB of stages either way.  Long chunks amortise the per-stage hand-shake (a
+// tcgen05.commit alone costs the issuing thread ~270 cycles) over more MMAs; short K keeps short chunks so
+// that its few words still spread over several stages.
+template <int CW>
+struct Tc5Cfg {
+    static constexpr int WORDS = CW, WPT = CW / 2, STAGES = 8 / CW;
+    static constexpr int CHUNK_BYTES = CW * 64;                      // operand bytes per row per chunk
+    static constexpr int SBO = (CHUNK_BYTES / 16) * 128;             // byte stride between 8-row groups
+    static constexpr int A_BYTES = 128 * CHUNK_BYTES;
+    static constexpr int B_BYTES = TC5_MAX_N * CHUNK_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int SPITCH = 64 + 4;                            // staging tile pitch in floats (conflict-free 16-byte row accesses)
     static constexpr int STILE_BYTES = 128 * SPITCH * 4;             // 34 KB: 128 pixels x 64 channels of fp32
-    static constexpr int TOTAL = TC5_STAGES * STAGE_BYTES + 2 * STILE_BYTES + 1024 /*alignment slack*/;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 2 * STILE_BYTES + 1024 /*alignment slack*/;
 };
+__host__ __device__ inline int tc5_chunk_words(int kwords) { return kwords <= 12 ? 2 : 4; }
 
 // 32 bits -> 32 bytes {0,1}: output word s holds bits s, s+8, s+16, s+24.  Two 16-byte stores.
 __device__ __forceinline__ void expand32(unsigned char* dst_unit0, uint32_t w) {
@@ -120,29 +125,32 @@ __device__ __forceinline__ void expand_word(unsigned char* dst, uint64_t w) {
 // 16 KB image of the stage's weight half, exactly as the producers would write it, so that a stage's weights
 // become one bulk copy (global -> shared, completion on the stage's "full" mbarrier) issued by one thread.
 __host__ __device__ inline size_t tc5_expanded_bytes(int N, int kwords) {
-    return (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * ((kwords + TC5_CHUNK_WORDS - 1) / TC5_CHUNK_WORDS) * Tc5Smem::B_BYTES;
+    const int cw = tc5_chunk_words(kwords);
+    return (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * ((kwords + cw - 1) / cw) * (TC5_MAX_N * cw * 64);
 }
-template <class WOp>
+template <int CW, class WOp>
 __global__ void __launch_bounds__(256) tc5_expand_weights_kernel(const WOp wop, const int N, const int kwords, unsigned char* dst) {
+    using C = Tc5Cfg<CW>;
     const int c = blockIdx.x, nt = blockIdx.y, r = threadIdx.x & 127, h = threadIdx.x >> 7;
     const int n = nt * TC5_MAX_N + r;
-    for (int j = 0; j < 2; j++) {
-        const int q = c * TC5_CHUNK_WORDS + 2 * h + j;
+    for (int j = 0; j < C::WPT; j++) {
+        const int q = c * C::WORDS + C::WPT * h + j;
         uint64_t w = 0;
         if (n < N && q < kwords) {
             const uint64_t* p = wop.addr(wop.make_row(n), wop.decode(q));
             if (p) w = __ldg(p);
         }
-        expand_word(dst + ((size_t)nt * gridDim.x + c) * Tc5Smem::B_BYTES + (r >> 3) * TC5_SBO + (r & 7) * 16 + (2 * h + j) * 4 * TC5_LBO, w);
+        expand_word(dst + ((size_t)nt * gridDim.x + c) * C::B_BYTES + (r >> 3) * C::SBO + (r & 7) * 16 + (C::WPT * h + j) * 4 * TC5_LBO, w);
     }
 }
 
-template <class XOp, class WOp>
+template <int CW, class XOp, class WOp>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
     bcontract_tc5_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
                          const int kwords, const int ntiles_m) {
+    using C = Tc5Cfg<CW>;
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t bar_full[TC5_STAGES], bar_empty[TC5_STAGES], bar_acc_full[TC5_ACCS], bar_acc_empty[TC5_ACCS];
+    __shared__ __align__(8) uint64_t bar_full[C::STAGES], bar_empty[C::STAGES], bar_acc_full[TC5_ACCS], bar_acc_empty[TC5_ACCS];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_abort, epi_abort;
     __shared__ int popw[TC5_MAX_N], popx[TC5_POPRING][2][128];
@@ -153,7 +161,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
     const int n0 = blockIdx.y * TC5_MAX_N;
     const int n_this = min(TC5_MAX_N, N - n0);               // multiple of 16 (host-checked)
     unsigned char* stage0 = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-    const int nchunks = (kwords + TC5_CHUNK_WORDS - 1) / TC5_CHUNK_WORDS;
+    const int nchunks = (kwords + C::WORDS - 1) / C::WORDS;
     int tmem_cols = 32;
     while (tmem_cols < TC5_ACCS * n_this) tmem_cols <<= 1;
     const volatile int* abort_flag = &s_abort;
@@ -165,7 +173,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     if (tid == 0) {
-        for (int i = 0; i < TC5_STAGES; i++) { mbar_init(&bar_full[i], TC5_PRODUCERS / 32 + (pre ? 1 : 0)); mbar_init(&bar_empty[i], 1); }
+        for (int i = 0; i < C::STAGES; i++) { mbar_init(&bar_full[i], TC5_PRODUCERS / 32 + (pre ? 1 : 0)); mbar_init(&bar_empty[i], 1); }
         for (int i = 0; i < TC5_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], TC5_EPILOGUE / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
@@ -196,30 +204,32 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         // =========================== producers: thread = (operand row, word of the chunk) ===========================
         const int r = tid & 127, h = tid >> 7;
         const bool has_w = r < n_this && !pre;
-        const unsigned char* wsrc = pre ? ep.w_expanded + (size_t)blockIdx.y * nchunks * Tc5Smem::B_BYTES : nullptr;
-        const int roff = (r >> 3) * TC5_SBO + (r & 7) * 16 + 2 * h * 4 * TC5_LBO;
+        const unsigned char* wsrc = pre ? ep.w_expanded + (size_t)blockIdx.y * nchunks * C::B_BYTES : nullptr;
+        const RowCtx wrow = wop.make_row(n0 + r);
+        const int roff = (r >> 3) * C::SBO + (r & 7) * 16 + C::WPT * h * 4 * TC5_LBO;
         uint32_t s = 0, use = 0;   // ring stage to fill next and how often the ring has wrapped
         bool ok = true;
         int i = 0;
         for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
-            typename XOp::Walk xw = xop.walker(tile * 128 + r, 2 * h);   // position of the word being *loaded*
-            typename WOp::Walk ww = wop.walker(n0 + r, 2 * h);
-            int qload = 2 * h;                                           // index of the word being loaded
-            struct Pair { uint64_t a[2], b[2]; };
-            auto load_next = [&](Pair& v) {   // words 2h and 2h + 1 of the next chunk
+            const RowCtx xr = xop.make_row(tile * 128 + r);
+            typename XOp::Dec xd = xop.decode(C::WPT * h);   // decode state of the word being *loaded*
+            typename WOp::Dec wd = wop.decode(C::WPT * h);
+            int qload = C::WPT * h;                                           // index of the word being loaded
+            struct Pair { uint64_t a[C::WPT], b[C::WPT]; };
+            auto load_next = [&](Pair& v) {   // this thread's words of the next chunk
 #pragma unroll
-                for (int j = 0; j < 2; j++) {
+                for (int j = 0; j < C::WPT; j++) {
                     v.a[j] = 0; v.b[j] = 0;
                     if (qload + j < kwords) {
-                        const uint64_t* p = xop.cur(xw);
+                        const uint64_t* p = xop.addr(xr, xd);
                         if (p) v.a[j] = __ldg(p);
-                        if (has_w) { const uint64_t* w = wop.cur(ww); if (w) v.b[j] = __ldg(w); }
+                        if (has_w) { const uint64_t* w = wop.addr(wrow, wd); if (w) v.b[j] = __ldg(w); }
                     }
-                    const int adv = j == 0 ? 1 : TC5_CHUNK_WORDS - 1;
-                    xop.step(xw, adv);
-                    if (has_w) wop.step(ww, adv);
+                    const int adv = j == C::WPT - 1 ? C::WORDS - (C::WPT - 1) : 1;
+                    xop.advance(xd, adv);
+                    if (has_w) wop.advance(wd, adv);
                 }
-                qload += TC5_CHUNK_WORDS;
+                qload += C::WORDS;
             };
             Pair v0, v1;   // chunk c and chunk c+1; chunk c+2 is loaded inside the loop
             load_next(v0);
@@ -235,25 +245,24 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                     break;
                 }
                 if (pre && tid == 0) {   // this stage's weights: one bulk copy that completes on the stage's "full" barrier
-                    const uint32_t bytes = (uint32_t)n_this * TC5_CHUNK_BYTES, bar = smem_u32(&bar_full[s]);
+                    const uint32_t bytes = (uint32_t)n_this * C::CHUNK_BYTES, bar = smem_u32(&bar_full[s]);
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(smem_u32(stage0 + s * Tc5Smem::STAGE_BYTES + Tc5Smem::A_BYTES)), "l"(wsrc + (size_t)c * Tc5Smem::B_BYTES),
+                                 ::"r"(smem_u32(stage0 + s * C::STAGE_BYTES + C::A_BYTES)), "l"(wsrc + (size_t)c * C::B_BYTES),
                                    "r"(bytes), "r"(bar) : "memory");
                 }
-                unsigned char* st = stage0 + s * Tc5Smem::STAGE_BYTES + roff;
-                expand_word(st, v0.a[0]);
-                expand_word(st + 4 * TC5_LBO, v0.a[1]);
-                if (has_w) {
-                    expand_word(st + Tc5Smem::A_BYTES, v0.b[0]);
-                    expand_word(st + Tc5Smem::A_BYTES + 4 * TC5_LBO, v0.b[1]);
+                unsigned char* st = stage0 + s * C::STAGE_BYTES + roff;
+#pragma unroll
+                for (int j = 0; j < C::WPT; j++) {
+                    expand_word(st + j * 4 * TC5_LBO, v0.a[j]);
+                    if (has_w) expand_word(st + C::A_BYTES + j * 4 * TC5_LBO, v0.b[j]);
+                    px += __popcll(v0.a[j]);
                 }
-                px += __popcll(v0.a[0]) + __popcll(v0.a[1]);
                 if (c == nchunks - 1) popx[i % TC5_POPRING][h][r] = px;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_full[s]);   // one arrival per warp: arrivals on one mbarrier are serialised
-                if (++s == TC5_STAGES) { s = 0; use++; }
+                if (++s == C::STAGES) { s = 0; use++; }
                 v0 = v1; v1 = v2;
             }
         }
@@ -265,7 +274,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             // The issuing thread is a single instruction stream, so its own latency bounds the MMA rate: the
             // descriptors are built once and advanced by adding byte offsets >> 4 to their address field
             // (shared-memory addresses stay below 2^18, so the 14-bit field cannot carry).
-            const uint64_t d_a = umma_desc(smem_u32(stage0)), d_b = d_a + (Tc5Smem::A_BYTES >> 4);
+            const uint64_t d_a = umma_desc(smem_u32(stage0), C::SBO), d_b = d_a + (C::A_BYTES >> 4);
             uint32_t s = 0, par = 0;
             bool ok = true;
             int i = 0;
@@ -287,18 +296,18 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t ad = d_a + (uint64_t)(s * (Tc5Smem::STAGE_BYTES >> 4)), bd = d_b + (uint64_t)(s * (Tc5Smem::STAGE_BYTES >> 4));
+                    const uint64_t ad = d_a + (uint64_t)(s * (C::STAGE_BYTES >> 4)), bd = d_b + (uint64_t)(s * (C::STAGE_BYTES >> 4));
                     // one MMA per 32 bytes of K = two 16-byte units = 256 bytes of descriptor address
-                    const int slices = min(2 * TC5_CHUNK_WORDS, 2 * (kwords - c * TC5_CHUNK_WORDS));
+                    const int slices = min(2 * C::WORDS, 2 * (kwords - c * C::WORDS));
 #pragma unroll
-                    for (int j = 0; j < 2 * TC5_CHUNK_WORDS; j++) {
+                    for (int j = 0; j < 2 * C::WORDS; j++) {
                         if (j < slices) {
                             mma_i8_ss(d_tmem, ad + j * 16, bd + j * 16, idesc, accum);
                             accum = 1u;
                         }
                     }
                     umma_commit(&bar_empty[s]);
-                    if (++s == TC5_STAGES) { s = 0; par ^= 1u; }
+                    if (++s == C::STAGES) { s = 0; par ^= 1u; }
                 }
                 if (ok) umma_commit(&bar_acc_full[accbuf]);
             }
@@ -312,7 +321,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         // [barrier] -> write-out: coalesced fp32 stores and sign-bit words from the staging tile.
         const int et = tid - TC5_PRODUCERS;
         const int r = et & 127, h2 = et >> 7;          // drain role: TMEM lane quarter = warp % 4 = r / 32
-        float* sbuf0 = reinterpret_cast<float*>(stage0 + TC5_STAGES * Tc5Smem::STAGE_BYTES);
+        float* sbuf0 = reinterpret_cast<float*>(stage0 + C::STAGES * C::STAGE_BYTES);
         const float* addsrc = ep.shortcut ? ep.shortcut : (ep.accumulate ? ep.out : nullptr);
         const long long ld_add = ep.shortcut ? ep.ld_sc : ep.ld_out;
         const int nblk = (n_this + 63) >> 6;           // 64-channel blocks per tile
@@ -325,13 +334,13 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             if (addsrc && kb < total_blocks) {
                 const int tile = blockIdx.x + (kb / nblk) * gridDim.x, cb = (kb % nblk) * 64;
                 const int width = min(64, n_this - cb);
-                const uint32_t sbase = smem_u32(sbuf0 + (kb & 1) * Tc5Smem::SPITCH * 128);
+                const uint32_t sbase = smem_u32(sbuf0 + (kb & 1) * C::SPITCH * 128);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int it = et + j * TC5_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
                     const int row = tile * 128 + rr;
                     if (row < M && c4 < width)
-                        cp_async16(sbase + (rr * Tc5Smem::SPITCH + c4) * 4, addsrc + (long long)row * ld_add + n0 + cb + c4, 16);
+                        cp_async16(sbase + (rr * C::SPITCH + c4) * 4, addsrc + (long long)row * ld_add + n0 + cb + c4, 16);
                 }
             }
             cp_async_commit();
@@ -343,7 +352,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             const int tile = blockIdx.x + i * gridDim.x, cb = blk * 64;
             const int width = min(64, n_this - cb);
             const int accbuf = i % TC5_ACCS, accuse = i / TC5_ACCS;
-            float* sb = sbuf0 + (kb & 1) * Tc5Smem::SPITCH * 128;
+            float* sb = sbuf0 + (kb & 1) * C::SPITCH * 128;
             cp_async_wait<0>();                                               // my copies of block kb have landed
             asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // everybody's have; write-out of kb-1 is over
             prefetch(kb + 1);
@@ -373,7 +382,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                                  : "r"(t_addr + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float* srow = sb + r * Tc5Smem::SPITCH + h2 * 32;
+                float* srow = sb + r * C::SPITCH + h2 * 32;
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
                     if (q * 4 >= ncol) break;
@@ -406,7 +415,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 const int it = et + j * TC5_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
                 const int row = tile * 128 + rr;
                 const bool live = row < M && c4 < width;
-                const float4 o = *reinterpret_cast<const float4*>(sb + rr * Tc5Smem::SPITCH + c4);
+                const float4 o = *reinterpret_cast<const float4*>(sb + rr * C::SPITCH + c4);
                 if (ep.out && live) __stcs(reinterpret_cast<float4*>(ep.out + (long long)row * ep.ld_out + n0 + cb + c4), o);
                 if (ep.bits) {   // the 16 lanes of a row hold the 64 channels of one word (channel tiles are 64-multiples here)
                     const unsigned nib = (o.x > 0.f ? 1u : 0u) | (o.y > 0.f ? 2u : 0u) | (o.z > 0.f ? 4u : 0u) | (o.w > 0.f ? 8u : 0u);

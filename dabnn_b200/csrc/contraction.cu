@@ -43,22 +43,28 @@ static int launch_engine(const XOp& xop, const WOp& wop, const EpilogueParams& e
 }
 
 // tcgen05 engine: persistent warp-specialised CTAs, one per SM (it owns all of the SM's tensor memory)
-template <class XOp, class WOp>
-static int launch_tc5(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
-                      cudaStream_t stream) {
-    auto kern = bcontract_tc5_kernel<XOp, WOp>;
+template <int CW, class XOp, class WOp>
+static int launch_tc5_cw(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
+                         cudaStream_t stream) {
+    auto kern = bcontract_tc5_kernel<CW, XOp, WOp>;
     static thread_local int configured_device = -1;
     int dev = 0;
     DABNN_CUDA_OK(cudaGetDevice(&dev));
     if (configured_device != dev) {
-        DABNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc5Smem::TOTAL));
+        DABNN_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc5Cfg<CW>::TOTAL));
         configured_device = dev;
     }
     const int tiles_m = (M + 127) / 128, tiles_n = (N + TC5_MAX_N - 1) / TC5_MAX_N;
     const int per_n = std::max(1, sm_count() / tiles_n);
     dim3 grid(std::min(tiles_m, per_n), tiles_n);
-    kern<<<grid, TC5_THREADS, Tc5Smem::TOTAL, stream>>>(xop, wop, ep, M, N, kwords, tiles_m);
+    kern<<<grid, TC5_THREADS, Tc5Cfg<CW>::TOTAL, stream>>>(xop, wop, ep, M, N, kwords, tiles_m);
     return check_launch("bcontract_tc5_kernel");
+}
+template <class XOp, class WOp>
+static int launch_tc5(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
+                      cudaStream_t stream) {
+    return tc5_chunk_words(kwords) == 2 ? launch_tc5_cw<2>(xop, wop, ep, M, N, kwords, stream)
+                                        : launch_tc5_cw<4>(xop, wop, ep, M, N, kwords, stream);
 }
 
 static bool tc5_eligible(const EpilogueParams& ep, int N) {
@@ -73,7 +79,7 @@ int launch_bcontract(int engine, const XOp& xop, const WOp& wop, const EpilogueP
     if (M <= 0 || N <= 0) return DABNN_OK;
     DABNN_REQUIRE(kwords < (1 << 17), DABNN_ERR_SHAPE, "contraction: K must be below 2^23 bits");
     if (engine == DABNN_ENGINE_AUTO) engine = DABNN_ENGINE_TCGEN05;
-    if (engine == DABNN_ENGINE_TCGEN05 && (!tc5_eligible(ep, N) || !xop.walkable() || !wop.walkable())) engine = DABNN_ENGINE_IMMA;
+    if (engine == DABNN_ENGINE_TCGEN05 && !tc5_eligible(ep, N)) engine = DABNN_ENGINE_IMMA;
     switch (engine) {
         case DABNN_ENGINE_TCGEN05: return launch_tc5(xop, wop, ep, M, N, kwords, stream);
         case DABNN_ENGINE_POPC: return launch_engine<ENG_POPC>(xop, wop, ep, M, N, kwords, stream);
@@ -121,8 +127,10 @@ int bconv_expand_weights(const uint64_t* weight, size_t weight_words, int cout, 
                   "expand_weights: filter rows shorter than kwords");
     DABNN_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, DABNN_ERR_ARG, "expand_weights: dst must be 16-byte aligned");
     RowMajorOperand wop{weight, (long long)(weight_words / cout), cout, kwords};
-    dim3 grid((kwords + TC5_CHUNK_WORDS - 1) / TC5_CHUNK_WORDS, (cout + TC5_MAX_N - 1) / TC5_MAX_N);
-    tc5_expand_weights_kernel<<<grid, 256, 0, stream>>>(wop, cout, kwords, dst);
+    const int cw = tc5_chunk_words(kwords);
+    dim3 grid((kwords + cw - 1) / cw, (cout + TC5_MAX_N - 1) / TC5_MAX_N);
+    if (cw == 2) tc5_expand_weights_kernel<2><<<grid, 256, 0, stream>>>(wop, cout, kwords, dst);
+    else tc5_expand_weights_kernel<4><<<grid, 256, 0, stream>>>(wop, cout, kwords, dst);
     return check_launch("tc5_expand_weights_kernel");
 }
 
