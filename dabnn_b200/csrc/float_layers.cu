@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256) chain_kernel(const float* x, const float*
 #pragma unroll
             for (int q = 0; q < VEC; q++) nib |= (v[q] > 0.f ? 1u : 0u) << q;
         }
-        if (bits) store_sign_word(bits, i >> 4, nib, valid);  // VEC == 4 and c % 64 == 0 guaranteed by the host
+        if (bits) store_sign_word(bits, (size_t)(i >> 4), nib, valid);  // VEC == 4 and c % 64 == 0 guaranteed by the host
     }
 }
 
@@ -113,23 +113,26 @@ int elementwise_chain(const float* x, const float* a, const float* b, const floa
 }
 
 // ---- pooling -------------------------------------------------------------------------------------
-template <int VEC, bool IS_MAX>
+// IDX is the type of the flat output index: 32-bit whenever the tensor allows it, because the four
+// divisions that turn it into (image, y, x, channel group) cost several times more in 64 bits than the
+// nine loads they lead to.
+template <int VEC, bool IS_MAX, typename IDX>
 __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                    uint64_t* __restrict__ bits, int n, int h, int w, int c_vec,
                                                    int kh, int kw, int pad_h, int pad_w, int stride_h,
                                                    int stride_w, int oh, int ow) {
-    const size_t total = (size_t)n * oh * ow * c_vec;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const size_t bound = bits ? (total + 31) / 32 * 32 : total;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < bound; i += stride) {
+    const IDX total = (IDX)n * oh * ow * c_vec;
+    const IDX stride = (IDX)gridDim.x * blockDim.x;
+    const IDX bound = bits ? (total + 31) / 32 * 32 : total;
+    for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < bound; i += stride) {
         const bool valid = i < total;
         unsigned nib = 0;
         if (valid) {
-            const int cc = i % c_vec;
-            size_t p = i / c_vec;
-            const int ox = p % ow; p /= ow;
-            const int oy = p % oh;
-            const int img = p / oh;
+            const int cc = (int)(i % (IDX)c_vec);
+            IDX p = i / (IDX)c_vec;
+            const int ox = (int)(p % (IDX)ow); p /= (IDX)ow;
+            const int oy = (int)(p % (IDX)oh);
+            const int img = (int)(p / (IDX)oh);
             float acc[VEC];
 #pragma unroll
             for (int q = 0; q < VEC; q++) acc[q] = IS_MAX ? -FLT_MAX : 0.f;
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in,
                 for (int q = 0; q < VEC; q++) acc[q] = __fdiv_rn(acc[q], (float)cnt);
             }
             if (VEC == 4)
-                *reinterpret_cast<float4*>(out + i * 4) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+                *reinterpret_cast<float4*>(out + (size_t)i * 4) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
             else
                 out[i] = acc[0];
 #pragma unroll
@@ -181,12 +184,20 @@ static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h
     DABNN_REQUIRE(!bits || (vec && c % 64 == 0), DABNN_ERR_SHAPE, "sign-bit output needs c % 64 == 0");
     if (vec) {
         const size_t total = (size_t)n * oh * ow * (c / 4);
-        pool_kernel<4, IS_MAX><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
-                                                                         pad_w, stride_h, stride_w, oh, ow);
+        if (total + (size_t)grid_for(total, 256) * 256 + 32 < (1ull << 32))   // the grid-stride loop must not wrap either
+            pool_kernel<4, IS_MAX, uint32_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
+                                                                                       pad_w, stride_h, stride_w, oh, ow);
+        else
+            pool_kernel<4, IS_MAX, size_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
+                                                                                     pad_w, stride_h, stride_w, oh, ow);
     } else {
         const size_t total = (size_t)n * oh * ow * c;
-        pool_kernel<1, IS_MAX><<<grid_for(total, 256), 256, 0, stream>>>(in, out, nullptr, n, h, w, c, kh, kw, pad_h,
-                                                                         pad_w, stride_h, stride_w, oh, ow);
+        if (total + (size_t)grid_for(total, 256) * 256 + 32 < (1ull << 32))
+            pool_kernel<1, IS_MAX, uint32_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, nullptr, n, h, w, c, kh, kw, pad_h,
+                                                                                       pad_w, stride_h, stride_w, oh, ow);
+        else
+            pool_kernel<1, IS_MAX, size_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, nullptr, n, h, w, c, kh, kw, pad_h,
+                                                                                     pad_w, stride_h, stride_w, oh, ow);
     }
     return check_launch("pool_kernel");
 }
