@@ -59,22 +59,20 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait; gives up (returns false) when the barrier does not flip or the CTA is aborting.
-// HINT_NS > 0 passes a suspend-time hint: the hardware parks the thread until the phase completes or the
-// time runs out, so a role that is ahead of the others does not fill the issue slots with polling.
-template <int HINT_NS = 0>
+// Every poll is a shared-memory access, and these kernels are bound by the shared-memory pipe: SLEEP_NS > 0
+// makes a waiting thread sleep between polls, as long as the role's slack allows (the epilogue is four
+// accumulators behind, the producers a ring of stages ahead).
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
     const uint32_t addr = smem_u32(bar);
-    constexpr uint32_t LIMIT = HINT_NS > 0 ? (TC5_SPIN_LIMIT >> 6) : TC5_SPIN_LIMIT;
+    constexpr uint32_t LIMIT = SLEEP_NS >= 64 ? (1u << 28) / SLEEP_NS : TC5_SPIN_LIMIT;   // at least 0.1 s either way
     for (uint32_t it = 0; it < LIMIT; it++) {
         uint32_t done;
-        if (HINT_NS > 0)
-            asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
-                         : "=r"(done) : "r"(addr), "r"(parity), "r"((uint32_t)HINT_NS) : "memory");
-        else
-            asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
-                         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if ((it & (HINT_NS > 0 ? 15u : 1023u)) == (HINT_NS > 0 ? 15u : 1023u) && *abort_flag) return false;
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
+        if ((it & 255u) == 255u && *abort_flag) return false;
     }
     return false;
 }
@@ -119,6 +117,16 @@ __device__ __forceinline__ void expand32(unsigned char* dst_unit0, uint32_t w) {
 __device__ __forceinline__ void expand_word(unsigned char* dst, uint64_t w) {
     expand32(dst, (uint32_t)w);
     expand32(dst + 2 * TC5_LBO, (uint32_t)(w >> 32));
+}
+// the same into shared memory, by shared address
+__device__ __forceinline__ void expand32_smem(uint32_t dst_unit0, uint32_t w) {
+    const uint32_t M1 = 0x01010101u;
+    sts128(dst_unit0, w & M1, (w >> 1) & M1, (w >> 2) & M1, (w >> 3) & M1);
+    sts128(dst_unit0 + TC5_LBO, (w >> 4) & M1, (w >> 5) & M1, (w >> 6) & M1, (w >> 7) & M1);
+}
+__device__ __forceinline__ void expand_word_smem(uint32_t dst, uint64_t w) {
+    expand32_smem(dst, (uint32_t)w);
+    expand32_smem(dst + 2 * TC5_LBO, (uint32_t)(w >> 32));
 }
 
 // Weights expanded once instead of once per pixel tile: for every 128-channel block and every K chunk one
@@ -207,6 +215,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         const unsigned char* wsrc = pre ? ep.w_expanded + (size_t)blockIdx.y * nchunks * C::B_BYTES : nullptr;
         const RowCtx wrow = wop.make_row(n0 + r);
         const int roff = (r >> 3) * C::SBO + (r & 7) * 16 + C::WPT * h * 4 * TC5_LBO;
+        const uint32_t stage0_addr = smem_u32(stage0);
         uint32_t s = 0, use = 0;   // ring stage to fill next and how often the ring has wrapped
         bool ok = true;
         int i = 0;
@@ -238,7 +247,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             for (int c = 0; c < nchunks; c++) {
                 Pair v2;
                 load_next(v2);
-                if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<2000>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
+                if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<100>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                     atomicCAS(&g_tc5_status, 0, 1);
                     s_abort = 1;
                     ok = false;
@@ -251,11 +260,11 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                                  ::"r"(smem_u32(stage0 + s * C::STAGE_BYTES + C::A_BYTES)), "l"(wsrc + (size_t)c * C::B_BYTES),
                                    "r"(bytes), "r"(bar) : "memory");
                 }
-                unsigned char* st = stage0 + s * C::STAGE_BYTES + roff;
+                const uint32_t st = stage0_addr + s * C::STAGE_BYTES + roff;
 #pragma unroll
                 for (int j = 0; j < C::WPT; j++) {
-                    expand_word(st + j * 4 * TC5_LBO, v0.a[j]);
-                    if (has_w) expand_word(st + C::A_BYTES + j * 4 * TC5_LBO, v0.b[j]);
+                    expand_word_smem(st + j * 4 * TC5_LBO, v0.a[j]);
+                    if (has_w) expand_word_smem(st + C::A_BYTES + j * 4 * TC5_LBO, v0.b[j]);
                     px += __popcll(v0.a[j]);
                 }
                 if (c == nchunks - 1) popx[i % TC5_POPRING][h][r] = px;
@@ -289,7 +298,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 const uint32_t d_tmem = tmem_base + accbuf * n_this;
                 uint32_t accum = 0;
                 for (int c = 0; c < nchunks; c++) {
-                    if (!mbar_wait(&bar_full[s], par, abort_flag)) {
+                    if (!mbar_wait<32>(&bar_full[s], par, abort_flag)) {
                         atomicCAS(&g_tc5_status, 0, 4);
                         s_abort = 1;
                         ok = false;
@@ -352,14 +361,14 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             const int tile = blockIdx.x + i * gridDim.x, cb = blk * 64;
             const int width = min(64, n_this - cb);
             const int accbuf = i % TC5_ACCS, accuse = i / TC5_ACCS;
-            float* sb = sbuf0 + (kb & 1) * C::SPITCH * 128;
+            const uint32_t sb = smem_u32(sbuf0 + (kb & 1) * C::SPITCH * 128);
             cp_async_wait<0>();                                               // my copies of block kb have landed
             asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // everybody's have; write-out of kb-1 is over
             prefetch(kb + 1);
             // ---- drain ----
             const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
             if (blk == 0 && okw) {
-                okw = __all_sync(0xffffffffu, mbar_wait<2000>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
+                okw = __all_sync(0xffffffffu, mbar_wait<500>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
                 if (!okw) {
                     atomicCAS(&g_tc5_status, 0, 2);
                     s_abort = 1;
@@ -382,7 +391,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                                  : "r"(t_addr + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float* srow = sb + r * C::SPITCH + h2 * 32;
+                const uint32_t srow = sb + (r * C::SPITCH + h2 * 32) * 4;
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
                     if (q * 4 >= ncol) break;
@@ -395,11 +404,11 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                         o[e] = f;
                     }
                     if (addsrc) {
-                        const float4 ad = *reinterpret_cast<const float4*>(srow + q * 4);
+                        const float4 ad = lds128f(srow + q * 16);
                         o[0] = __fadd_rn(ad.x, o[0]); o[1] = __fadd_rn(ad.y, o[1]);
                         o[2] = __fadd_rn(ad.z, o[2]); o[3] = __fadd_rn(ad.w, o[3]);
                     }
-                    *reinterpret_cast<float4*>(srow + q * 4) = make_float4(o[0], o[1], o[2], o[3]);
+                    sts128f(srow + q * 16, o[0], o[1], o[2], o[3]);
                 }
             }
             if (blk == nblk - 1 && okw) {   // the whole accumulator has been read
@@ -415,7 +424,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                 const int it = et + j * TC5_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
                 const int row = tile * 128 + rr;
                 const bool live = row < M && c4 < width;
-                const float4 o = *reinterpret_cast<const float4*>(sb + rr * C::SPITCH + c4);
+                const float4 o = lds128f(sb + (rr * C::SPITCH + c4) * 4);
                 if (ep.out && live) __stcs(reinterpret_cast<float4*>(ep.out + (long long)row * ep.ld_out + n0 + cb + c4), o);
                 if (ep.bits) {   // the 16 lanes of a row hold the 64 channels of one word (channel tiles are 64-multiples here)
                     const unsigned nib = (o.x > 0.f ? 1u : 0u) | (o.y > 0.f ? 2u : 0u) | (o.z > 0.f ? 4u : 0u) | (o.w > 0.f ? 8u : 0u);

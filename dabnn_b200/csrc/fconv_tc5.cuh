@@ -138,7 +138,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     for (int k = tid; k < FT_MAXK; k += FT_THREADS) {
         if (k < K) {
             const int tap = k / p.cin, ky = tap / p.kw, kx = tap - ky * p.kw, ci = k - tap * p.cin;
-            tab_off[k] = MODE == FT_ROWS ? ky * pitch + kx * p.dil_w * p.cin + ci : (ky * p.dil_h * p.w + kx * p.dil_w) * p.cin + ci;
+            // ROWS: byte offset inside the patch; DIRECT: float offset inside the image
+            tab_off[k] = MODE == FT_ROWS ? (ky * pitch + kx * p.dil_w * p.cin + ci) * 4 : (ky * p.dil_h * p.w + kx * p.dil_w) * p.cin + ci;
             tab_yx[k] = (uint32_t)ky | ((uint32_t)kx << 8);
         } else {   // padded k: the weights there are zero, so any finite pixel value will do - take the window's first
             tab_off[k] = 0;
@@ -173,21 +174,22 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         const int roff = (r >> 3) * FT_A_SBO + (r & 7) * 16 + h * 4 * 128;
         uint32_t s = 0, use = 0;   // ring stage to fill next and how often the ring has wrapped
         bool ok = true;
+        const uint32_t stage0_addr = smem_u32(stage0);
         // split 16 values and publish them as this thread's share (four 16-byte units) of the next ring stage
         auto emit = [&](const float (&v)[16]) -> bool {
-            if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<2000>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
+            if (use >= 1 && !__all_sync(0xffffffffu, mbar_wait<100>(&bar_empty[s], (use - 1) & 1, abort_flag))) {   // warp-uniform
                 atomicCAS(&g_tc5_status, 0, 11);
                 s_abort = 1;
                 return false;
             }
-            unsigned char* st = stage0 + s * FT_STAGE_BYTES + roff;
+            const uint32_t st = stage0_addr + s * FT_STAGE_BYTES + roff;
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 uint32_t hi[4], lo[4];
 #pragma unroll
                 for (int q = 0; q < 4; q++) split_tf32(v[u * 4 + q], hi[q], lo[q]);
-                *reinterpret_cast<uint4*>(st + u * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(st + FT_HALF_BYTES + u * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                sts128(st + u * 128, hi[0], hi[1], hi[2], hi[3]);
+                sts128(st + FT_HALF_BYTES + u * 128, lo[0], lo[1], lo[2], lo[3]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -231,6 +233,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 cp_async_commit();
             };
             stage_patch(blockIdx.x, 0);
+            const uint32_t patch0_addr = smem_u32(patch0);
             int i = 0;
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, i++) {
                 cp_async_wait<0>();                                   // my copies of this tile's patch have landed
@@ -238,14 +241,15 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 stage_patch(tile + gridDim.x, (i + 1) & 1);
                 const int seg = tile % nseg, len = min(128, p.ow - seg * 128);
                 const int shift = vec16 ? ((seg * 128 * p.stride_w - p.pad_w) * p.cin) & 3 : 0;
-                const float* pb = patch0 + (i & 1) * patch_floats + shift + min(r, len - 1) * p.stride_w * p.cin;
+                const uint32_t pb = patch0_addr + ((i & 1) * patch_floats + shift + min(r, len - 1) * p.stride_w * p.cin) * 4;
                 for (int c = 0; c < nchunks && ok; c++) {
                     const int k0 = c * FT_CHUNK + h * 16;
                     float v[16];
 #pragma unroll
                     for (int u = 0; u < 4; u++) {
                         const int4 o = *reinterpret_cast<const int4*>(tab_off + k0 + u * 4);
-                        v[u * 4 + 0] = pb[o.x]; v[u * 4 + 1] = pb[o.y]; v[u * 4 + 2] = pb[o.z]; v[u * 4 + 3] = pb[o.w];
+                        v[u * 4 + 0] = lds_f32(pb + o.x); v[u * 4 + 1] = lds_f32(pb + o.y);
+                        v[u * 4 + 2] = lds_f32(pb + o.z); v[u * 4 + 3] = lds_f32(pb + o.w);
                     }
                     ok = emit(v);
                 }
@@ -324,7 +328,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 uint64_t bh = d_wh, bl = d_wl;
                 uint32_t accum = 0;
                 for (int c = 0; c < nchunks; c++) {
-                    if (!mbar_wait(&bar_full[s], par, abort_flag)) {
+                    if (!mbar_wait<32>(&bar_full[s], par, abort_flag)) {
                         atomicCAS(&g_tc5_status, 0, 14);
                         s_abort = 1;
                         ok = false;
@@ -360,13 +364,14 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         const int et = tid - FT_PRODUCERS;
         const int r = et & 127, h2 = et >> 7;          // drain role: TMEM lane quarter = warp % 4 = r / 32
         const int ncol = max(0, min(32, n_this - h2 * 32));   // 0, 16 or 32 columns for this thread
+        const uint32_t stile_addr = smem_u32(stile);
         int i = 0;
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, i++) {
             const int accbuf = i % FT_ACCS, accuse = i / FT_ACCS;
             long long rowbase;
             int len;
             ft_tile_rows<MODE>(tile, M, p.ow, nseg, rowbase, len);
-            const bool okw = __all_sync(0xffffffffu, mbar_wait<2000>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
+            const bool okw = __all_sync(0xffffffffu, mbar_wait<500>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
             if (!okw) {
                 atomicCAS(&g_tc5_status, 0, 12);
                 s_abort = 1;
@@ -395,7 +400,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                                    "=r"(x[24]), "=r"(x[25]), "=r"(x[26]), "=r"(x[27]), "=r"(x[28]), "=r"(x[29]), "=r"(x[30]), "=r"(x[31])
                                  : "r"(t_addr + FT_N + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float* srow = stile + r * FT_SPITCH + h2 * 32;
+                const uint32_t srow = stile_addr + (r * FT_SPITCH + h2 * 32) * 4;
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
                     if (q * 4 >= ncol) break;
@@ -409,7 +414,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                         if (p.relu) f = relu_ref(f);
                         o[e] = f;
                     }
-                    *reinterpret_cast<float4*>(srow + q * 4) = make_float4(o[0], o[1], o[2], o[3]);
+                    sts128f(srow + q * 16, o[0], o[1], o[2], o[3]);
                 }
             }
             if (okw) {   // the accumulator has been read: the MMA warp may reuse it
@@ -425,7 +430,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 const int it = et + j * FT_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
                 if (rr < len && c4 < n_this)
                     __stcs(reinterpret_cast<float4*>(p.out + (size_t)(rowbase + rr) * p.cout + n0 + c4),
-                           *reinterpret_cast<const float4*>(stile + rr * FT_SPITCH + c4));
+                           lds128f(stile_addr + (rr * FT_SPITCH + c4) * 4));
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the staging tile may be overwritten
         }
