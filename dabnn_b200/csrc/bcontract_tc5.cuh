@@ -326,8 +326,9 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         // The channels of a tile are handled in blocks of 64.  Per block k (a counter over the
         // whole kernel): [barrier] -> prefetch block k+1's shortcut into the other staging tile
         // with cp.async -> drain: thread (r, h2) reads 32 accumulator columns of row r, converts,
-        // applies the affine, adds the staged shortcut and writes the result back in place ->
-        // [barrier] -> write-out: coalesced fp32 stores and sign-bit words from the staging tile.
+        // applies the affine, adds the staged shortcut, writes the result back in place and stores
+        // the 32 sign bits it now holds -> [barrier] -> write-out: one bulk copy (shared -> global)
+        // per pixel row, so the fp32 output costs the load/store pipe nothing.
         const int et = tid - TC5_PRODUCERS;
         const int r = et & 127, h2 = et >> 7;          // drain role: TMEM lane quarter = warp % 4 = r / 32
         float* sbuf0 = reinterpret_cast<float*>(stage0 + C::STAGES * C::STAGE_BYTES);
@@ -363,7 +364,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             const int accbuf = i % TC5_ACCS, accuse = i / TC5_ACCS;
             const uint32_t sb = smem_u32(sbuf0 + (kb & 1) * C::SPITCH * 128);
             cp_async_wait<0>();                                               // my copies of block kb have landed
-            asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // everybody's have; write-out of kb-1 is over
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my row stores of block kb-1 have read their source
+            asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // everybody's have: the other staging tile is idle
             prefetch(kb + 1);
             // ---- drain ----
             const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
@@ -392,6 +394,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                                  : "r"(t_addr + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const uint32_t srow = sb + (r * C::SPITCH + h2 * 32) * 4;
+                uint32_t signs = 0;   // bit j: channel c0 + j of this row is positive
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
                     if (q * 4 >= ncol) break;
@@ -409,7 +412,12 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                         o[2] = __fadd_rn(ad.z, o[2]); o[3] = __fadd_rn(ad.w, o[3]);
                     }
                     sts128f(srow + q * 16, o[0], o[1], o[2], o[3]);
+                    signs |= ((o[0] > 0.f ? 1u : 0u) | (o[1] > 0.f ? 2u : 0u) | (o[2] > 0.f ? 4u : 0u) | (o[3] > 0.f ? 8u : 0u)) << (q * 4);
                 }
+                // this thread holds 32 consecutive channels of its row: half of one packed word (the low half first)
+                const long long row = (long long)tile * 128 + r;
+                if (ep.bits && row < M) reinterpret_cast<uint32_t*>(ep.bits + row * ep.ld_bits + ((n0 + cb) >> 6))[h2] = signs;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk store below reads what was just written
             }
             if (blk == nblk - 1 && okw) {   // the whole accumulator has been read
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -418,27 +426,16 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             }
             asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
             if (epi_abort) break;
-            // ---- write-out: item = (row, 4 channels); 16 consecutive lanes walk along a row ----
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int it = et + j * TC5_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
-                const int row = tile * 128 + rr;
-                const bool live = row < M && c4 < width;
-                const float4 o = lds128f(sb + (rr * C::SPITCH + c4) * 4);
-                if (ep.out && live) __stcs(reinterpret_cast<float4*>(ep.out + (long long)row * ep.ld_out + n0 + cb + c4), o);
-                if (ep.bits) {   // the 16 lanes of a row hold the 64 channels of one word (channel tiles are 64-multiples here)
-                    const unsigned nib = (o.x > 0.f ? 1u : 0u) | (o.y > 0.f ? 2u : 0u) | (o.z > 0.f ? 4u : 0u) | (o.w > 0.f ? 8u : 0u);
-                    const int sub = lane & 15;
-                    unsigned lo = sub < 8 ? nib << (4 * sub) : 0u, hi = sub >= 8 ? nib << (4 * (sub - 8)) : 0u;
-#pragma unroll
-                    for (int off = 1; off < 16; off <<= 1) {
-                        lo |= __shfl_xor_sync(0xffffffffu, lo, off);
-                        hi |= __shfl_xor_sync(0xffffffffu, hi, off);
-                    }
-                    if (sub == 0 && row < M) ep.bits[(long long)row * ep.ld_bits + ((n0 + cb) >> 6)] = ((unsigned long long)hi << 32) | lo;
-                }
+            // ---- write-out: one bulk copy per pixel row, shared -> global, issued by the row's first thread ----
+            if (ep.out && et < 128) {
+                const long long row = (long long)tile * 128 + et;
+                if (row < M)
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(ep.out + row * ep.ld_out + n0 + cb), "r"(sb + et * C::SPITCH * 4), "r"(width * 4) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
         }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the last row stores are complete before the CTA winds down
         cp_async_wait<0>();   // nothing of this thread's is in flight when the CTA winds down
     }
 
