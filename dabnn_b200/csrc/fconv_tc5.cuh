@@ -22,7 +22,7 @@
 //     block, K = 8) into one of four TMEM accumulators.
 //   * 8 epilogue warps: thread (r, half) reads 32 accumulator columns of row r, adds the bias,
 //     applies the affine (product and sum rounded separately) and the relu and parks the row in a
-//     shared staging tile, from which all 256 threads write coalesced 16-byte stores.
+//     shared staging tile, from which one bulk copy per pixel row (shared -> global) writes it out.
 // Every mbarrier wait is bounded (see bcontract_tc5.cuh): on a time-out the CTA records a code in
 // the device status word, raises its abort flag, frees its TMEM and returns.  Named barriers are
 // only reached by code paths that every thread of the role takes the same number of times.
@@ -416,6 +416,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     }
                     sts128f(srow + q * 16, o[0], o[1], o[2], o[3]);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk store below reads what was just written
             }
             if (okw) {   // the accumulator has been read: the MMA warp may reuse it
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -424,18 +425,19 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the tile is staged (or abort decided)
             if (epi_abort) break;
-            // ---- write-out: item = (row, 4 channels); 16 consecutive lanes walk along a row ----
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int it = et + j * FT_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
-                if (rr < len && c4 < n_this)
-                    __stcs(reinterpret_cast<float4*>(p.out + (size_t)(rowbase + rr) * p.cout + n0 + c4),
-                           lds128f(stile_addr + (rr * FT_SPITCH + c4) * 4));
+            // ---- write-out: one bulk copy per pixel row, shared -> global, issued by the row's first thread ----
+            if (et < 128) {
+                if (et < len)
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(p.out + (size_t)(rowbase + et) * p.cout + n0), "r"(stile_addr + et * FT_SPITCH * 4), "r"(n_this * 4) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the row has been read: it may be overwritten
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the staging tile may be overwritten
         }
     }
 
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // row stores are complete before the CTA winds down
     // ---- drain: everybody is past its last use of the tensor memory ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
