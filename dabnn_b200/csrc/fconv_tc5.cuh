@@ -36,7 +36,7 @@ constexpr int FT_CHUNK = 32;                    // floats of K per ring stage (f
 constexpr int FT_MAXK = 256;                    // padded K the resident weights may have
 constexpr int FT_ACCS = 4;
 constexpr int FT_PRODUCERS = 256, FT_EPILOGUE = 256;
-constexpr int FT_THREADS = FT_PRODUCERS + FT_EPILOGUE + 32;
+constexpr int FT_THREADS = FT_PRODUCERS + FT_EPILOGUE + 64;   // + the MMA warp and the patch loader warp
 constexpr int FT_MMA_WARP = (FT_PRODUCERS + FT_EPILOGUE) / 32;
 constexpr int FT_HALF_BYTES = 128 * FT_CHUNK * 4;        // hi (or lo) part of a stage: 16 KB
 constexpr int FT_STAGE_BYTES = 2 * FT_HALF_BYTES;
@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                      const int nseg, const int pitch, const int vec16, const int n_blk) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bar_full[FT_MAX_STAGES], bar_empty[FT_MAX_STAGES], bar_acc_full[FT_ACCS], bar_acc_empty[FT_ACCS];
+    __shared__ __align__(8) uint64_t patch_full[2], patch_empty[2];   // ROWS with bulk copies: patch buffer filled / drained
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_abort, epi_abort;
     __shared__ __align__(16) int tab_off[FT_MAXK];   // k -> float offset of (ky, kx, ci): in the patch (ROWS) or the image (DIRECT)
@@ -131,6 +132,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     if (tid == 0) {
         for (int i = 0; i < stages; i++) { mbar_init(&bar_full[i], FT_PRODUCERS / 32); mbar_init(&bar_empty[i], 1); }
         for (int i = 0; i < FT_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], FT_EPILOGUE / 32); }
+        for (int i = 0; i < 2; i++) { mbar_init(&patch_full[i], 1); mbar_init(&patch_empty[i], FT_PRODUCERS / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
         epi_abort = 0;
@@ -232,16 +234,42 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 }
                 cp_async_commit();
             };
-            stage_patch(blockIdx.x, 0);
             const uint32_t patch0_addr = smem_u32(patch0);
+            if (vec16) {   // the loader warp fills the patch buffers with bulk copies
+                int i = 0;
+                for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, i++) {
+                    if (!__all_sync(0xffffffffu, mbar_wait<100>(&patch_full[i & 1], (i >> 1) & 1, abort_flag))) {
+                        atomicCAS(&g_tc5_status, 0, 16);
+                        s_abort = 1;
+                        ok = false;
+                        break;
+                    }
+                    const int seg = tile % nseg, len = min(128, p.ow - seg * 128);
+                    const int shift = ((seg * 128 * p.stride_w - p.pad_w) * p.cin) & 3;
+                    const uint32_t pb = patch0_addr + ((i & 1) * patch_floats + shift + min(r, len - 1) * p.stride_w * p.cin) * 4;
+                    for (int c = 0; c < nchunks && ok; c++) {
+                        const int k0 = c * FT_CHUNK + h * 16;
+                        float v[16];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int4 o = *reinterpret_cast<const int4*>(tab_off + k0 + u * 4);
+                            v[u * 4 + 0] = lds_f32(pb + o.x); v[u * 4 + 1] = lds_f32(pb + o.y);
+                            v[u * 4 + 2] = lds_f32(pb + o.z); v[u * 4 + 3] = lds_f32(pb + o.w);
+                        }
+                        ok = emit(v);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&patch_empty[i & 1]);   // this warp has read its last float of the buffer
+                }
+            } else {
+            stage_patch(blockIdx.x, 0);
             int i = 0;
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, i++) {
                 cp_async_wait<0>();                                   // my copies of this tile's patch have landed
                 if (producers_sync_or(!ok || *abort_flag)) break;      // everybody's have, and the other buffer is idle
                 stage_patch(tile + gridDim.x, (i + 1) & 1);
                 const int seg = tile % nseg, len = min(128, p.ow - seg * 128);
-                const int shift = vec16 ? ((seg * 128 * p.stride_w - p.pad_w) * p.cin) & 3 : 0;
-                const uint32_t pb = patch0_addr + ((i & 1) * patch_floats + shift + min(r, len - 1) * p.stride_w * p.cin) * 4;
+                const uint32_t pb = patch0_addr + ((i & 1) * patch_floats + min(r, len - 1) * p.stride_w * p.cin) * 4;
                 for (int c = 0; c < nchunks && ok; c++) {
                     const int k0 = c * FT_CHUNK + h * 16;
                     float v[16];
@@ -253,6 +281,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     }
                     ok = emit(v);
                 }
+            }
             }
             cp_async_wait<0>();   // nothing of this thread's is in flight when the CTA winds down
         } else {
@@ -357,6 +386,53 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     if (++s == (uint32_t)stages) { s = 0; par ^= 1u; }
                 }
                 if (ok) umma_commit(&bar_acc_full[accbuf]);
+            }
+        }
+    } else if (warp == FT_MMA_WARP + 1) {
+        // =========================== patch loader (ROWS, 16-byte case): one warp ===========================
+        // Two tiles ahead of the producers: zero-fills what lies outside the image, then lane ky issues one
+        // bulk copy for input row ky; the copies complete on patch_full[b].  The producers only wait for
+        // patch_full and hand the buffer back through patch_empty.
+        if (MODE == FT_ROWS && vec16) {
+            const int row_floats = p.w * p.cin;
+            const uint32_t patch0_addr = smem_u32(patch0);
+            auto stage_patch_bulk = [&](int t, int b) {
+                if (t >= ntiles) return;
+                const int line = t / nseg, seg = t - line * nseg, img = line / p.oh, oy = line - img * p.oh;
+                const int iy0 = oy * p.stride_h - p.pad_h;
+                const int gx0 = (seg * 128 * p.stride_w - p.pad_w) * p.cin, shift = gx0 & 3, groups = pitch >> 2;
+                // patch group j holds image floats 4j - shift + gx0 .. + 3: inside the row for j_lo <= j < j_hi
+                const int j_lo = gx0 < shift ? (shift - gx0) >> 2 : 0;
+                const int j_hi = max(j_lo, min(groups, (row_floats - gx0 + shift) >> 2));
+                const uint32_t buf = patch0_addr + b * patch_floats * 4;
+                const int iy = iy0 + lane * p.dil_h;
+                const bool row_in = lane < p.kh && (unsigned)iy < (unsigned)p.h;
+                const int npad = j_lo + (groups - j_hi);
+                for (int idx = lane; idx < p.kh * npad; idx += 32) {   // left and right of the image
+                    const int ky = idx / npad, q = idx - ky * npad, j = q < j_lo ? q : j_hi + (q - j_lo);
+                    sts128f(buf + (ky * pitch + 4 * j) * 4, 0.f, 0.f, 0.f, 0.f);
+                }
+                for (int ky = 0; ky < p.kh; ky++)                      // rows above and below the image
+                    if ((unsigned)(iy0 + ky * p.dil_h) >= (unsigned)p.h)
+                        for (int j = j_lo + lane; j < j_hi; j += 32) sts128f(buf + (ky * pitch + 4 * j) * 4, 0.f, 0.f, 0.f, 0.f);
+                const uint32_t bytes = (uint32_t)(j_hi - j_lo) * 16u, bar = smem_u32(&patch_full[b]);
+                const uint32_t nrows = __popc(__ballot_sync(0xffffffffu, row_in));
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nrows * bytes) : "memory");
+                __syncwarp();
+                if (row_in && bytes > 0)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(buf + (lane * pitch + 4 * j_lo) * 4),
+                                   "l"(p.in + ((long long)img * p.h + iy) * row_floats + (4 * j_lo - shift + gx0)), "r"(bytes), "r"(bar) : "memory");
+            };
+            int i = 0;
+            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, i++) {
+                if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait<100>(&patch_empty[i & 1], ((i >> 1) - 1) & 1, abort_flag))) {
+                    atomicCAS(&g_tc5_status, 0, 15);
+                    s_abort = 1;
+                    break;
+                }
+                stage_patch_bulk(tile, i & 1);
             }
         }
     } else {
