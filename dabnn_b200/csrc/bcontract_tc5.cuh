@@ -132,9 +132,13 @@ __device__ __forceinline__ void expand_word_smem(uint32_t dst, uint64_t w) {
 // Weights expanded once instead of once per pixel tile: for every 128-channel block and every K chunk one
 // 16 KB image of the stage's weight half, exactly as the producers would write it, so that a stage's weights
 // become one bulk copy (global -> shared, completion on the stage's "full" mbarrier) issued by one thread.
-__host__ __device__ inline size_t tc5_expanded_bytes(int N, int kwords) {
+// The buffer ends with the popcount of every weight row (one int per channel, padded to whole channel blocks).
+__host__ __device__ inline size_t tc5_expanded_image_bytes(int N, int kwords) {
     const int cw = tc5_chunk_words(kwords);
     return (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * ((kwords + cw - 1) / cw) * (TC5_MAX_N * cw * 64);
+}
+__host__ __device__ inline size_t tc5_expanded_bytes(int N, int kwords) {
+    return tc5_expanded_image_bytes(N, kwords) + (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * TC5_MAX_N * sizeof(int);
 }
 template <int CW, class WOp>
 __global__ void __launch_bounds__(256) tc5_expand_weights_kernel(const WOp wop, const int N, const int kwords, unsigned char* dst) {
@@ -149,6 +153,19 @@ __global__ void __launch_bounds__(256) tc5_expand_weights_kernel(const WOp wop, 
             if (p) w = __ldg(p);
         }
         expand_word(dst + ((size_t)nt * gridDim.x + c) * C::B_BYTES + (r >> 3) * C::SBO + (r & 7) * 16 + (C::WPT * h + j) * 4 * TC5_LBO, w);
+    }
+    if (c == 0 && h == 0) {   // row popcounts, once
+        int pc = 0;
+        if (n < N) {
+            const RowCtx wr = wop.make_row(n);
+            typename WOp::Dec d = wop.decode(0);
+            for (int q = 0; q < kwords; q++) {
+                const uint64_t* p = wop.addr(wr, d);
+                pc += p ? __popcll(__ldg(p)) : 0;
+                wop.advance(d, 1);
+            }
+        }
+        reinterpret_cast<int*>(dst + tc5_expanded_image_bytes(N, kwords))[n] = pc;
     }
 }
 
@@ -189,7 +206,9 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
     }
     if (tid < TC5_MAX_N) {
         int pc = 0;
-        if (tid < n_this) {
+        if (pre) {
+            pc = __ldg(reinterpret_cast<const int*>(ep.w_expanded + tc5_expanded_image_bytes(N, kwords)) + n0 + tid);
+        } else if (tid < n_this) {
             const RowCtx wr = wop.make_row(n0 + tid);
             typename WOp::Dec d = wop.decode(0);
             for (int q = 0; q < kwords; q++) {

@@ -111,6 +111,7 @@ struct NetImpl {
     std::vector<float> time_ms;
 
     ~NetImpl() {
+        for (auto& g : graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
         for (auto e : events) cudaEventDestroy(e);
         for (auto e : tickets) if (e) cudaEventDestroy(e);
         for (int i = 0; i < 2; i++) {
@@ -129,6 +130,20 @@ struct NetImpl {
     int build();
     int run(const float* input, int batch, bool is_device);
     int run_plan(int batch);
+    int run_plan_graphed(int batch);
+
+    // The launch plan of one (sub-batch size, input pointer, output offset) captured as a CUDA graph on its second
+    // use: a small batch is bound by the host's launch rate (29 launches for Bi-Real-18), a graph replays them
+    // with one call.  Off while profiling (events between launches) and after any capture failure.
+    struct PlanGraph {
+        int batch;
+        const float* input;
+        size_t out_offset;
+        cudaGraphExec_t exec;
+    };
+    std::vector<PlanGraph> graphs;
+    bool use_graphs = true;
+    static constexpr size_t kMaxGraphs = 16;
     // blobs that outlive the run hold the whole batch; everything else is reused per sub-batch
     float* f32(int blob) const {
         if (blob == input_blob) return const_cast<float*>(cur_input);
@@ -642,7 +657,7 @@ int NetImpl::run(const float* input, int batch, bool is_device) {
     if (is_device) {
         cur_input = input;
         out_offset = 0;
-        return run_plan(batch);
+        return run_plan_graphed(batch);
     }
     // host input: sub-batches through two staging buffers; the copy of sub-batch k+1 is issued
     // before the kernels of sub-batch k so that PCIe transfer and compute overlap
@@ -670,11 +685,56 @@ int NetImpl::run(const float* input, int batch, bool is_device) {
         DABNN_CUDA_OK(cudaStreamWaitEvent(stream, copied[sb], 0));
         cur_input = staging[sb];
         out_offset = (size_t)i0;
-        rc = run_plan(cnt);
+        rc = run_plan_graphed(cnt);
         DABNN_CUDA_OK(cudaEventRecord(consumed[sb], stream));
     }
     out_offset = 0;
     return rc;
+}
+
+int NetImpl::run_plan_graphed(int batch) {
+    if (!use_graphs || profiling) return run_plan(batch);
+    PlanGraph* g = nullptr;
+    for (auto& c : graphs)
+        if (c.batch == batch && c.input == cur_input && c.out_offset == out_offset) g = &c;
+    if (g && g->exec) {
+        DABNN_CUDA_OK(cudaGraphLaunch(g->exec, stream));
+        return DABNN_OK;
+    }
+    if (!g) {   // first use of this key: run eagerly (this also performs the kernels' one-time attribute set-up)
+        if (graphs.size() >= kMaxGraphs) {   // callers that keep changing pointers: forget the oldest
+            if (graphs.front().exec) cudaGraphExecDestroy(graphs.front().exec);
+            graphs.erase(graphs.begin());
+        }
+        graphs.push_back(PlanGraph{batch, cur_input, out_offset, nullptr});
+        return run_plan(batch);
+    }
+    // second use: capture the same launches instead of running them, then replay
+    if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        use_graphs = false;
+        return run_plan(batch);
+    }
+    const int rc = run_plan(batch);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t end = cudaStreamEndCapture(stream, &graph);
+    if (rc != DABNN_OK || end != cudaSuccess || !graph) {
+        cudaGetLastError();
+        if (graph) cudaGraphDestroy(graph);
+        use_graphs = false;
+        return rc != DABNN_OK ? rc : run_plan(batch);
+    }
+    cudaGraphExec_t exec = nullptr;
+    const cudaError_t inst = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (inst != cudaSuccess || !exec) {
+        cudaGetLastError();
+        use_graphs = false;
+        return run_plan(batch);
+    }
+    g->exec = exec;
+    DABNN_CUDA_OK(cudaGraphLaunch(exec, stream));
+    return DABNN_OK;
 }
 
 int NetImpl::run_plan(int batch) {
