@@ -171,6 +171,73 @@ __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in,
     }
 }
 
+// 3x3 stride-2 pad-1 max pooling, four channels x a 2x2 block of outputs per thread: the four windows share a
+// 5x5 input patch, so a thread loads 25 float4 for four outputs instead of 36 (the kernel is bound by the
+// L2 -> SM traffic of those loads).  Each output folds its taps in the reference's order (ky, then kx,
+// `acc < t ? t : acc` from -FLT_MAX), so ties between -0 and +0 and NaN inputs resolve identically.
+__global__ void __launch_bounds__(256) maxpool3s2_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                         uint64_t* __restrict__ bits, int n, int h, int w, int c_vec,
+                                                         int oh, int ow) {
+    const int bh = (oh + 1) / 2, bw = (ow + 1) / 2;
+    const uint32_t total = (uint32_t)n * bh * bw * c_vec;
+    const uint32_t bound = (total + 31) / 32 * 32;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < bound; i += gridDim.x * blockDim.x) {
+        const bool valid = i < total;
+        const int cc = valid ? (int)(i % (uint32_t)c_vec) : 0;
+        uint32_t p = valid ? i / (uint32_t)c_vec : 0;
+        const int bx = (int)(p % (uint32_t)bw); p /= (uint32_t)bw;
+        const int by = (int)(p % (uint32_t)bh);
+        const int img = (int)(p / (uint32_t)bh);
+        float acc[2][2][4];
+#pragma unroll
+        for (int a = 0; a < 16; a++) (&acc[0][0][0])[a] = -FLT_MAX;
+        const int y0 = 4 * by - 1, x0 = 4 * bx - 1;
+        if (valid) {
+#pragma unroll
+            for (int ry = 0; ry < 5; ry++) {
+                const int y = y0 + ry;
+                if (y < 0 || y >= h) continue;
+                float4 t[5];
+#pragma unroll
+                for (int rx = 0; rx < 5; rx++) {
+                    const int x = x0 + rx;
+                    t[rx] = (x >= 0 && x < w) ? __ldg(reinterpret_cast<const float4*>(in + ((((size_t)img * h + y) * w + x) * c_vec + cc) * 4))
+                                              : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+                }
+#pragma unroll
+                for (int dy = 0; dy < 2; dy++) {
+                    if (ry < 2 * dy || ry > 2 * dy + 2) continue;
+#pragma unroll
+                    for (int dx = 0; dx < 2; dx++)
+#pragma unroll
+                        for (int kx = 0; kx < 3; kx++) {
+                            const int rx = 2 * dx + kx;
+                            if (x0 + rx < 0 || x0 + rx >= w) continue;   // the reference skips taps outside the image
+                            const float4 v = t[rx];
+                            float* a = acc[dy][dx];
+                            a[0] = a[0] < v.x ? v.x : a[0]; a[1] = a[1] < v.y ? v.y : a[1];
+                            a[2] = a[2] < v.z ? v.z : a[2]; a[3] = a[3] < v.w ? v.w : a[3];
+                        }
+                }
+            }
+        }
+#pragma unroll
+        for (int dy = 0; dy < 2; dy++)
+#pragma unroll
+            for (int dx = 0; dx < 2; dx++) {
+                const int oy = 2 * by + dy, ox = 2 * bx + dx;
+                const bool live = valid && oy < oh && ox < ow;
+                const size_t pix = ((size_t)img * oh + oy) * ow + ox;
+                const float* a = acc[dy][dx];
+                if (live) *reinterpret_cast<float4*>(out + (pix * c_vec + cc) * 4) = make_float4(a[0], a[1], a[2], a[3]);
+                if (bits) {
+                    const unsigned nib = (a[0] > 0.f ? 1u : 0u) | (a[1] > 0.f ? 2u : 0u) | (a[2] > 0.f ? 4u : 0u) | (a[3] > 0.f ? 8u : 0u);
+                    store_sign_word(bits, live ? (pix * c_vec + cc) >> 4 : 0, nib, live);
+                }
+            }
+    }
+}
+
 template <bool IS_MAX>
 static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h, int w, int c, int kh, int kw,
                        int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream) {
@@ -182,6 +249,12 @@ static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h
     DABNN_REQUIRE(pad_h < kh && pad_w < kw, DABNN_ERR_SHAPE, "pool: padding must be smaller than the kernel");
     const bool vec = c % 4 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     DABNN_REQUIRE(!bits || (vec && c % 64 == 0), DABNN_ERR_SHAPE, "sign-bit output needs c % 64 == 0");
+    if (vec && IS_MAX && kh == 3 && kw == 3 && stride_h == 2 && stride_w == 2 && pad_h == 1 && pad_w == 1 &&
+        (c / 4) % 16 == 0 && (size_t)n * ((oh + 1) / 2) * ((ow + 1) / 2) * (c / 4) < (1ull << 31)) {
+        const size_t blocks = (size_t)n * ((oh + 1) / 2) * ((ow + 1) / 2) * (c / 4);
+        maxpool3s2_kernel<<<grid_for(blocks, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, oh, ow);
+        return check_launch("maxpool3s2_kernel");
+    }
     if (vec) {
         const size_t total = (size_t)n * oh * ow * (c / 4);
         if (total + (size_t)grid_for(total, 256) * 256 + 32 < (1ull << 32))   // the grid-stride loop must not wrap either

@@ -280,7 +280,7 @@ def test_float_layers_golden(ops, k):
                                k["ref_fconv_p0_s1"], rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("shape", [(2, 56, 56, 64), (3, 7, 7, 512), (2, 5, 3, 7), (1, 1, 1, 1000)])
+@pytest.mark.parametrize("shape", [(2, 56, 56, 64), (3, 7, 7, 512), (2, 5, 3, 7), (1, 1, 1, 1000), (2, 9, 11, 64), (1, 18, 6, 128)])
 def test_float_layers_random(ops, port, shape):
     rng = np.random.default_rng(sum(shape))
     x = rng.normal(0, 1, shape).astype(np.float32)
