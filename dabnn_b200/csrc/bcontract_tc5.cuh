@@ -8,26 +8,29 @@
 //
 // A CTA (one per SM, persistent over pixel tiles) works on 128-pixel x (up to) 128-channel tiles
 // with three kinds of warps that only meet at mbarriers:
-//   * 8 producer warps; thread (r, h) owns 64-bit word h of every 128-bit K chunk of operand row r:
-//     it reads the word (implicit im2col: tap by tap, zero word outside the image; the tap decode
-//     is stepped, not divided), expands every 32 bits to 32 bytes with shift+mask pairs
+//   * 8 producer warps; thread (r, h) owns half of the 64-bit words of every K chunk of operand row
+//     r (chunks of 128 bits through four stages for short K, 256 bits through two stages otherwise:
+//     Tc5Cfg).  It reads its words (implicit im2col: tap by tap, zero word outside the image; the tap
+//     decode is stepped, not divided), expands every 32 bits to 32 bytes with shift+mask pairs
 //     ((w >> s) & 0x01010101 - the resulting bit -> K-slot permutation is the same for both
 //     operands, and a contraction is blind to it) and stores them in the K-major SWIZZLE_NONE
-//     canonical layout of UMMA shared-memory descriptors (8 rows x 16 B core matrices).  The same
-//     thread expands word h of weight row r when r < Ntile.  Chunks go through a 4-deep ring of
-//     32 KB buffers; loads run two chunks ahead of the expansion.  Row popcounts are accumulated
-//     on the way and handed to the epilogue through a small ring.
-//   * 1 MMA warp: one lane issues, per chunk, four tcgen05.mma (M = 128, N = Ntile, K = 32 bytes)
-//     from shared-memory descriptors into one of four TMEM accumulators and commits them to the
-//     ring's "empty" barrier, and to the accumulator's "full" barrier after the last chunk.
+//     canonical layout of UMMA shared-memory descriptors (8 rows x 16 B core matrices).  Loads run
+//     two chunks ahead of the expansion; a warp arrives once on the stage's "full" barrier.  Row
+//     popcounts are accumulated on the way and handed to the epilogue through a small ring.
+//     The weights of a stage are expanded the same way by the same threads, or - when the caller
+//     has expanded them once for all pixel tiles (tc5_expand_weights_kernel) - arrive as one bulk
+//     copy that completes on the same barrier.
+//   * 1 MMA warp: one lane issues, per chunk, one tcgen05.mma per 32 bytes of K (M = 128,
+//     N = Ntile) from shared-memory descriptors into one of four TMEM accumulators and commits
+//     them to the ring's "empty" barrier, and to the accumulator's "full" barrier after the last
+//     chunk.
 //   * 8 epilogue warps working on blocks of 128 pixels x 64 channels through two fp32 staging
 //     tiles in shared memory.  The shortcut (or the previous output, when accumulating) of the
 //     next block is copied into the idle tile with cp.async while the current block is handled,
 //     so its HBM latency is hidden behind a whole block of work.  Drain: thread (r, half)
 //     tcgen05.ld's 32 accumulator columns of row r, turns AND counts into XOR counts, applies the
-//     affine, adds the staged shortcut and writes the fp32 result back in place.  Write-out: the
-//     256 threads re-read the tile with consecutive lanes on consecutive channels, so the fp32
-//     stores are fully coalesced, and OR the sign bits of 64 channels together by shuffles.
+//     affine, adds the staged shortcut, writes the fp32 result back in place and stores the 32
+//     sign bits it now holds.  Write-out: one bulk copy (shared -> global) per pixel row.
 //
 // Every wait on an mbarrier is bounded: after a fixed number of polls the CTA records an error
 // code in a device-side status word, raises a CTA-wide abort flag that every role checks, frees

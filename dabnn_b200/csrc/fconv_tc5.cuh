@@ -7,19 +7,21 @@
 // K-major canonical layout of UMMA descriptors (8 rows x 16 B core matrices).  Three kinds of warps
 // meet only at mbarriers:
 //   * 8 producer warps build the pixel operand (implicit im2col), split it and store hi and lo
-//     into a ring of 16 KB stages; thread (r, h) owns 8 consecutive k of pixel row r per 16-float
+//     into a ring of 32 KB stages; thread (r, h) owns 16 consecutive k of pixel row r per 32-float
 //     K chunk.  Two ways to get at the pixels:
 //       ROWS   - a tile is (a 128-pixel segment of) one output row.  The kh input rows under it
-//                are copied once, coalesced, with cp.async into a double-buffered patch in shared
-//                memory (next tile's patch while this tile is expanded), out-of-image parts
-//                zero-filled, so that the k loop is a table look-up and one shared-memory load
-//                per element with no predicate, and every input byte crosses L2 -> SM once per
-//                tile instead of once per tap;
+//                are copied once into a double-buffered patch in shared memory, out-of-image
+//                parts zero-filled, so that the k loop is a table look-up and one shared-memory
+//                load per element with no predicate, and every input byte crosses L2 -> SM once
+//                per tile instead of once per tap.  With 16-byte-aligned rows a loader warp does
+//                the copying, two tiles ahead, with one bulk copy per input row; otherwise the
+//                producers do it themselves with 4-byte cp.async, one tile ahead;
 //       DIRECT - a tile is 128 consecutive output pixels and elements come straight from global
 //                memory through a k -> (offset, ky, kx) table and two per-row validity masks
 //                (1x1 convolutions, where nothing is reused, and windows too large to stage).
-//   * 1 MMA warp: one lane issues, per 8-float slice, lo*hi, hi*lo and hi*hi (M = 128, N = channel
-//     block, K = 8) into one of four TMEM accumulators.
+//   * 1 MMA warp: one lane issues, per 8-float slice, hi*[hi; lo] as one N = 128 instruction (the
+//     lo rows of the weights follow the hi rows) and lo*hi (M = 128, K = 8) into one of four TMEM
+//     accumulators; the two column halves are added in the epilogue.
 //   * 8 epilogue warps: thread (r, half) reads 32 accumulator columns of row r, adds the bias,
 //     applies the affine (product and sum rounded separately) and the relu and parks the row in a
 //     shared staging tile, from which one bulk copy per pixel row (shared -> global) writes it out.
