@@ -40,6 +40,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--engines", default="tcgen05")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--movers", action="store_true", help="also time bit-packing, im2col, elementwise and pooling kernels")
     args = ap.parse_args()
     B = args.batch
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -58,6 +59,31 @@ def main():
                       "block_ms": round(t_blk, 4), "block_Tbitop_s": round(bitops / t_blk / 1e9, 1),
                       "block_GB_s": round(B * (H * H * cin / 8 + oh * oh * cout * 8.125) / t_blk / 1e6, 1)}
         print(json.dumps(row), flush=True)
+    if args.movers:
+        movers(B, args.iters)
+
+
+def movers(B, iters):
+    """The data-movement functions of the path, in GB/s of algorithmic bytes (each tensor once)."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn((B, 56, 56, 64), device="cuda", generator=g)
+    y = torch.randn((B, 56, 56, 64), device="cuda", generator=g)
+    a, b = torch.rand(64, device="cuda", generator=g), torch.rand(64, device="cuda", generator=g)
+    x128 = torch.randn((B, 28, 28, 128), device="cuda", generator=g)
+    stem = torch.randn((B, 112, 112, 64), device="cuda", generator=g)
+    n = x.numel()
+    cases = [
+        ("pack_mat 56x56x64", lambda: ops.pack_mat(x), n * 4 + n / 8),
+        ("fused_binarize_im2col 28x28x128 k3 p1", lambda: ops.fused_binarize_im2col(x128, 3, 3, 1, 1, 1, 1),
+         x128.numel() * 4 + B * 28 * 28 * 18 * 8),
+        ("affine 56x56x64 (in place)", lambda: ops.affine_(x, a, b), n * 8),
+        ("add 56x56x64 (in place)", lambda: ops.add_(x, y), n * 12),
+        ("maxpool 3x3 s2 p1 112x112x64", lambda: ops.maxpool(stem, 3, 3, 1, 1, 2, 2), stem.numel() * 4 * 1.25),
+        ("avepool 2x2 s2 56x56x64", lambda: ops.avepool(x, 2, 2, 0, 0, 2, 2), n * 4 * 1.25),
+    ]
+    for name, fn, nbytes in cases:
+        t = timeit(fn, iters)
+        print(json.dumps({"kernel": name, "batch": B, "ms": round(t, 4), "GB_s": round(nbytes / t / 1e6, 1)}), flush=True)
 
 
 if __name__ == "__main__":

@@ -468,7 +468,19 @@ int NetImpl::build() {
         // which op index consumes each blob, to decide what can be fused
         const int nl = (int)lops.size();
         std::vector<char> used(nl, 0);
+        // A block whose Add comes later in the file (Bi-Real's stride-2 blocks: BinConv, Affine, then the
+        // downsample branch AvePool / FpConv / Affine, then Add) is held back until that Add, so that the
+        // shortcut is added in the block's own epilogue.  Legal when nothing in between touches the block's
+        // output or overwrites its input; the sum itself is the same two operands either way.
+        Op held{};
+        int held_until = -1;
         for (int i = 0; i < nl; i++) {
+            if (i == held_until) {
+                held.in2 = lops[i].op.in2;
+                plan.push_back(held);
+                held_until = -1;
+                continue;
+            }
             if (used[i]) continue;
             Op o = lops[i].op;
             used[i] = 1;
@@ -479,8 +491,24 @@ int NetImpl::build() {
             };
             if (o.kind == OpKind::BConvBlock) {
                 if (next_is(LayerType::Affine)) { o.a = lops[j].op.a; o.b = lops[j].op.b; used[j++] = 1; }
-                if (next_is(LayerType::Add) && lops[j].op.in2 != o.out) { o.in2 = lops[j].op.in2; used[j++] = 1; }
                 o.cls = "Bin Conv block";
+                if (next_is(LayerType::Add) && lops[j].op.in2 != o.out) {
+                    o.in2 = lops[j].op.in2;
+                    used[j++] = 1;
+                } else if (held_until < 0) {
+                    for (int k = j; k < nl; k++) {
+                        const Op& q = lops[k].op;
+                        if (used[k]) break;
+                        if (lops[k].type == LayerType::Add && q.kind == OpKind::Chain && q.in == o.out && q.in2 != o.out) {
+                            held = o;
+                            held_until = k;
+                            used[k] = 1;
+                            break;
+                        }
+                        if (q.in == o.out || q.in2 == o.out || q.out == o.out || q.out == o.in) break;   // not independent
+                    }
+                    if (held_until >= 0) continue;   // emitted when the loop reaches the Add
+                }
             } else if (o.kind == OpKind::FConv && lops[i].type == LayerType::FpConv2D) {
                 if (next_is(LayerType::Affine)) { o.a = lops[j].op.a; o.b = lops[j].op.b; used[j++] = 1; }
                 if (next_is(LayerType::Relu)) { o.relu = 1; used[j++] = 1; }
