@@ -319,13 +319,14 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                         }
                     }
                 };
-                float cur[16], nxt[16];
+                float cur[16], nx1[16], nx2[16];   // loads run two chunks ahead of the expansion (an L2 round trip each)
                 gather(0, cur);
+                if (nchunks > 1) gather(1, nx1);
                 for (int c = 0; c < nchunks && ok; c++) {
-                    if (c + 1 < nchunks) gather(c + 1, nxt);   // loads run one chunk ahead of the expansion
+                    if (c + 2 < nchunks) gather(c + 2, nx2);
                     ok = emit(cur);
 #pragma unroll
-                    for (int q = 0; q < 16; q++) cur[q] = nxt[q];
+                    for (int q = 0; q < 16; q++) { cur[q] = nx1[q]; nx1[q] = nx2[q]; }
                 }
             }
         }
