@@ -36,6 +36,8 @@
 // code in a device-side status word, raises a CTA-wide abort flag that every role checks, frees
 // its TMEM and returns.
 #pragma once
+#include <cuda.h>   // CUtensorMap (type only; the encoder is fetched from the driver at run time)
+
 #include "bcontract.cuh"
 
 namespace dabnn {
@@ -101,8 +103,11 @@ struct Tc5Cfg {
     static constexpr int A_BYTES = 128 * CHUNK_BYTES;
     static constexpr int B_BYTES = TC5_MAX_N * CHUNK_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int SPITCH = 64 + 4;                            // staging tile pitch in floats (conflict-free 16-byte row accesses)
-    static constexpr int STILE_BYTES = 128 * SPITCH * 4;             // 34 KB: 128 pixels x 64 channels of fp32
+    // Staging tile of a block: two boxes of 128 pixels x 32 channels of fp32 in the 128-byte-swizzled layout of
+    // TMA tensor copies: 16-byte chunk q of row r of a box sits at r * 128 + ((q ^ (r & 7)) << 4).  Thread-per-row
+    // accesses are then conflict-free, and one tensor store per box writes the block out.
+    static constexpr int SBOX_BYTES = 128 * 128;                     // 16 KB
+    static constexpr int STILE_BYTES = 2 * SBOX_BYTES;               // 32 KB: 128 pixels x 64 channels of fp32
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 2 * STILE_BYTES + 1024 /*alignment slack*/;
 };
 __host__ __device__ inline int tc5_chunk_words(int kwords) { return kwords <= 12 ? 2 : 4; }
@@ -175,7 +180,7 @@ __global__ void __launch_bounds__(256) tc5_expand_weights_kernel(const WOp wop, 
 template <int CW, class XOp, class WOp>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
     bcontract_tc5_kernel(const XOp xop, const WOp wop, const EpilogueParams ep, const int M, const int N,
-                         const int kwords, const int ntiles_m) {
+                         const int kwords, const int ntiles_m, const __grid_constant__ CUtensorMap out_map) {
     using C = Tc5Cfg<CW>;
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bar_full[C::STAGES], bar_empty[C::STAGES], bar_acc_full[TC5_ACCS], bar_acc_empty[TC5_ACCS];
@@ -349,11 +354,11 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         // whole kernel): [barrier] -> prefetch block k+1's shortcut into the other staging tile
         // with cp.async -> drain: thread (r, h2) reads 32 accumulator columns of row r, converts,
         // applies the affine, adds the staged shortcut, writes the result back in place and stores
-        // the 32 sign bits it now holds -> [barrier] -> write-out: one bulk copy (shared -> global)
-        // per pixel row, so the fp32 output costs the load/store pipe nothing.
+        // the 32 sign bits it now holds -> [barrier] -> write-out: one TMA tensor store per 32-channel
+        // box, so the fp32 output costs the load/store pipe nothing and the copy engine two requests.
         const int et = tid - TC5_PRODUCERS;
         const int r = et & 127, h2 = et >> 7;          // drain role: TMEM lane quarter = warp % 4 = r / 32
-        float* sbuf0 = reinterpret_cast<float*>(stage0 + C::STAGES * C::STAGE_BYTES);
+        const uint32_t sbuf0_addr = smem_u32(stage0 + C::STAGES * C::STAGE_BYTES);
         const float* addsrc = ep.shortcut ? ep.shortcut : (ep.accumulate ? ep.out : nullptr);
         const long long ld_add = ep.shortcut ? ep.ld_sc : ep.ld_out;
         const int nblk = (n_this + 63) >> 6;           // 64-channel blocks per tile
@@ -366,13 +371,14 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             if (addsrc && kb < total_blocks) {
                 const int tile = blockIdx.x + (kb / nblk) * gridDim.x, cb = (kb % nblk) * 64;
                 const int width = min(64, n_this - cb);
-                const uint32_t sbase = smem_u32(sbuf0 + (kb & 1) * C::SPITCH * 128);
+                const uint32_t sbase = sbuf0_addr + (kb & 1) * C::STILE_BYTES;
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int it = et + j * TC5_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
                     const int row = tile * 128 + rr;
                     if (row < M && c4 < width)
-                        cp_async16(sbase + (rr * C::SPITCH + c4) * 4, addsrc + (long long)row * ld_add + n0 + cb + c4, 16);
+                        cp_async16(sbase + (c4 >> 5) * C::SBOX_BYTES + rr * 128 + ((((c4 & 31) >> 2) ^ (rr & 7)) << 4),
+                                   addsrc + (long long)row * ld_add + n0 + cb + c4, 16);
                 }
             }
             cp_async_commit();
@@ -384,7 +390,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             const int tile = blockIdx.x + i * gridDim.x, cb = blk * 64;
             const int width = min(64, n_this - cb);
             const int accbuf = i % TC5_ACCS, accuse = i / TC5_ACCS;
-            const uint32_t sb = smem_u32(sbuf0 + (kb & 1) * C::SPITCH * 128);
+            const uint32_t sb = sbuf0_addr + (kb & 1) * C::STILE_BYTES;
             cp_async_wait<0>();                                               // my copies of block kb have landed
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my row stores of block kb-1 have read their source
             asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // everybody's have: the other staging tile is idle
@@ -415,7 +421,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                                  : "r"(t_addr + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const uint32_t srow = sb + (r * C::SPITCH + h2 * 32) * 4;
+                const uint32_t srow = sb + h2 * C::SBOX_BYTES + r * 128;   // chunk q of this row: srow + ((q ^ (r & 7)) << 4)
                 uint32_t signs = 0;   // bit j: channel c0 + j of this row is positive
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
@@ -429,11 +435,11 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
                         o[e] = f;
                     }
                     if (addsrc) {
-                        const float4 ad = lds128f(srow + q * 16);
+                        const float4 ad = lds128f(srow + ((q ^ (r & 7)) << 4));
                         o[0] = __fadd_rn(ad.x, o[0]); o[1] = __fadd_rn(ad.y, o[1]);
                         o[2] = __fadd_rn(ad.z, o[2]); o[3] = __fadd_rn(ad.w, o[3]);
                     }
-                    sts128f(srow + q * 16, o[0], o[1], o[2], o[3]);
+                    sts128f(srow + ((q ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
                     signs |= ((o[0] > 0.f ? 1u : 0u) | (o[1] > 0.f ? 2u : 0u) | (o[2] > 0.f ? 4u : 0u) | (o[3] > 0.f ? 8u : 0u)) << (q * 4);
                 }
                 // this thread holds 32 consecutive channels of its row: half of one packed word (the low half first)
@@ -448,12 +454,11 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
             }
             asm volatile("bar.sync 1, %0;" ::"n"(TC5_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
             if (epi_abort) break;
-            // ---- write-out: one bulk copy per pixel row, shared -> global, issued by the row's first thread ----
-            if (ep.out && et < 128) {
-                const long long row = (long long)tile * 128 + et;
-                if (row < M)
-                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                                 ::"l"(ep.out + row * ep.ld_out + n0 + cb), "r"(sb + et * C::SPITCH * 4), "r"(width * 4) : "memory");
+            // ---- write-out: one tensor store (shared -> global, rows beyond M and channels beyond N clipped) per box ----
+            if (ep.out && (et == 0 || (et == 128 && width > 32))) {
+                const int hb = et >> 7;
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                             ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + cb + hb * 32), "r"(tile * 128), "r"(sb + hb * C::SBOX_BYTES) : "memory");
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
         }
