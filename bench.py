@@ -140,7 +140,7 @@ def run_ours(args):
     from dabnn_b200.bireal import OUTPUT_BLOB, build_bireal18
     from dabnn_b200.dab_format import write_dab
     from dabnn_b200.net import Net
-    from dabnn_b200.replicas import gather_logits
+    from dabnn_b200.replicas import bind_to_gpu_cpus, gather_logits
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -148,6 +148,7 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
     torch.cuda.set_device(local)
+    numa_bound = bind_to_gpu_cpus(local)   # before any pinned allocation
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
@@ -277,7 +278,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": f"Bi-Real-Net-18-shaped BNN, 224x224x3 fp32 N(0,1) inputs, random-init, batch {B} per GPU, "
                                    "independent replicas",
-                       "global_batch": B * world, "per_gpu_batch": B, "engine": eng,
+                       "global_batch": B * world, "per_gpu_batch": B, "engine": eng, "cpu_affinity": "gpu-local" if numa_bound else "default",
                        "l2": "inputs (617 MB) and activations (GBs) exceed the 126 MB L2; no flush needed"},
             "e2e": {"value": round(world * B * args.steps / (ms_e2e * 1e-3), 1), "unit": "images/s",
                     "h2d_bytes_per_step": B * IMAGE_HW * IMAGE_HW * 3 * 4, "d2h_bytes_per_step": B * CLASSES * 4,

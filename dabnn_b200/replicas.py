@@ -40,3 +40,23 @@ def gather_logits(local: torch.Tensor, total: int) -> torch.Tensor:
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded.contiguous())
     return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)
+
+
+def bind_to_gpu_cpus(device_index: int) -> bool:
+    """Pin the calling process to the CPU cores NVML reports as local to GPU `device_index` (its NUMA node), so
+    that the pinned host buffers it allocates next, and the copies from them, do not cross the socket link.
+    With eight replicas copying 617 MB per step each, unplaced buffers leave the host side as the bottleneck.
+    Changes only this process's CPU affinity; returns False (and changes nothing) when NVML is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        pynvml.nvmlDeviceSetCpuAffinity(handle)
+        return True
+    except Exception:
+        return False
+
