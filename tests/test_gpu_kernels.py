@@ -206,7 +206,10 @@ def test_bconv_odd_shapes(ops, port, engine):
     rng = np.random.default_rng(9)
     for (h, w_, cw, cout, kh, kw, ph, pw, sh, sw) in [(5, 6, 1, 8, 3, 3, 1, 1, 1, 1), (9, 4, 3, 24, 5, 3, 2, 1, 2, 1),
                                                       (3, 3, 2, 128, 3, 3, 0, 0, 2, 2), (1, 1, 1, 3, 1, 1, 0, 0, 1, 1),
-                                                      (64, 64, 2, 128, 5, 5, 2, 2, 2, 2)]:
+                                                      (64, 64, 2, 128, 5, 5, 2, 2, 2, 2),
+                                                      # channel counts that end in a clipped 32-channel box
+                                                      (10, 10, 1, 48, 3, 3, 1, 1, 1, 1), (6, 6, 2, 80, 3, 3, 1, 1, 1, 1),
+                                                      (12, 12, 1, 144, 3, 3, 1, 1, 1, 1)]:
         x = rand_bits(rng, (2, h, w_, cw))
         wt = rand_bits(rng, cout * kh * kw * cw)
         out = host(ops.bconv(dev_bits(x), dev_bits(wt), cout, kh, kw, ph, pw, sh, sw, engine))
