@@ -42,33 +42,6 @@ static int launch_engine(const XOp& xop, const WOp& wop, const EpilogueParams& e
                   : launch_one<ENGINE, 4, 2, false>(xop, wop, ep, M, N, kwords, stream);
 }
 
-// TMA descriptor of the fp32 output [M][N] (row pitch ld_out floats) for 32-channel x 128-pixel boxes in the
-// 128-byte-swizzled shared-memory layout the epilogue stages them in.  The encoder is a driver entry point,
-// fetched once through the runtime (the library links no driver stub).  Returns false when it cannot be made.
-static bool make_out_map(CUtensorMap* map, float* out, long long ld_out, int M, int N) {
-    typedef CUresult (*Encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static Encode encode = nullptr;
-    static bool looked = false;
-    if (!looked) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult st;
-        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &st) == cudaSuccess &&
-            st == cudaDriverEntryPointSuccess)
-            encode = reinterpret_cast<Encode>(fn);
-        else
-            cudaGetLastError();
-        looked = true;
-    }
-    if (!encode || !out) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld_out * sizeof(float)};
-    const cuuint32_t box[2] = {32, 128}, estr[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // tcgen05 engine: persistent warp-specialised CTAs, one per SM (it owns all of the SM's tensor memory)
 template <int CW, class XOp, class WOp>
 static int launch_tc5_cw(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
@@ -85,7 +58,9 @@ static int launch_tc5_cw(const XOp& xop, const WOp& wop, const EpilogueParams& e
     const int per_n = std::max(1, sm_count() / tiles_n);
     dim3 grid(std::min(tiles_m, per_n), tiles_n);
     CUtensorMap out_map{};
-    if (ep.out && !make_out_map(&out_map, ep.out, ep.ld_out, M, N))
+    const unsigned long long dims[2] = {(unsigned long long)N, (unsigned long long)M}, strides[1] = {(unsigned long long)ep.ld_out * sizeof(float)};
+    const unsigned box[2] = {32, 128};
+    if (ep.out && !make_f32_tensor_map(&out_map, ep.out, 2, dims, strides, box))
         return launch_engine<ENG_IMMA>(xop, wop, ep, M, N, kwords, stream);   // no TMA descriptor: the mma.sync engine
     kern<<<grid, TC5_THREADS, Tc5Cfg<CW>::TOTAL, stream>>>(xop, wop, ep, M, N, kwords, tiles_m, out_map);
     return check_launch("bcontract_tc5_kernel");

@@ -24,7 +24,7 @@
 //     accumulators; the two column halves are added in the epilogue.
 //   * 8 epilogue warps: thread (r, half) reads 32 accumulator columns of row r, adds the bias,
 //     applies the affine (product and sum rounded separately) and the relu and parks the row in a
-//     shared staging tile, from which one bulk copy per pixel row (shared -> global) writes it out.
+//     shared staging tile (two 128-byte-swizzled boxes), which two TMA tensor stores write out.
 // Every mbarrier wait is bounded (see bcontract_tc5.cuh): on a time-out the CTA records a code in
 // the device status word, raises its abort flag, frees its TMEM and returns.  Named barriers are
 // only reached by code paths that every thread of the role takes the same number of times.
@@ -43,8 +43,10 @@ constexpr int FT_MMA_WARP = (FT_PRODUCERS + FT_EPILOGUE) / 32;
 constexpr int FT_HALF_BYTES = 128 * FT_CHUNK * 4;        // hi (or lo) part of a stage: 16 KB
 constexpr int FT_STAGE_BYTES = 2 * FT_HALF_BYTES;
 constexpr int FT_A_SBO = (FT_CHUNK / 4) * 128;           // 8-row group stride inside a stage
-constexpr int FT_SPITCH = FT_N + 4;                      // staging tile pitch in floats
-constexpr int FT_STILE_BYTES = 128 * FT_SPITCH * 4;
+// staging tile: two boxes of 128 pixels x 32 channels in the 128-byte-swizzled layout of TMA tensor copies
+// (16-byte chunk q of row r at r * 128 + ((q ^ (r & 7)) << 4)); 1 KB more for its 1024-byte alignment
+constexpr int FT_SBOX_BYTES = 128 * 128;
+constexpr int FT_STILE_BYTES = 2 * FT_SBOX_BYTES + 1024;
 constexpr int FT_MAX_STAGES = 8;
 constexpr int FT_DIRECT = 0, FT_ROWS = 1;
 constexpr int FT_MAX_PATCH_BYTES = 72 * 1024;            // both patch buffers together
@@ -102,7 +104,7 @@ __device__ __forceinline__ void ft_tile_rows(int t, int M, int ow, int nseg, lon
 template <int MODE>
 __global__ void __launch_bounds__(FT_THREADS, 1)
     fconv_tc5_kernel(const FconvParams p, const int M, const int K, const int kpad, const int ntiles, const int stages,
-                     const int nseg, const int pitch, const int vec16, const int n_blk) {
+                     const int nseg, const int pitch, const int vec16, const int n_blk, const __grid_constant__ CUtensorMap out_map) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bar_full[FT_MAX_STAGES], bar_empty[FT_MAX_STAGES], bar_acc_full[FT_ACCS], bar_acc_empty[FT_ACCS];
     __shared__ __align__(8) uint64_t patch_full[2], patch_empty[2];   // ROWS with bulk copies: patch buffer filled / drained
@@ -120,7 +122,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     float* patch0 = reinterpret_cast<float*>(wbase + 2 * w_half);
     const int patch_floats = MODE == FT_ROWS ? p.kh * pitch : 0;        // one buffer
     unsigned char* stage0 = reinterpret_cast<unsigned char*>(patch0 + 2 * patch_floats);
-    float* stile = reinterpret_cast<float*>(stage0 + stages * FT_STAGE_BYTES);
+    unsigned char* stile = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(stage0 + stages * FT_STAGE_BYTES) + 1023) & ~uintptr_t(1023));
     const int nchunks = (kpad + FT_CHUNK - 1) / FT_CHUNK;
     const volatile int* abort_flag = &s_abort;
     constexpr int ACC_COLS = 2 * FT_N;                         // hi*hi + lo*hi in the first 64 columns, hi*lo in the others
@@ -479,7 +481,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                                    "=r"(x[24]), "=r"(x[25]), "=r"(x[26]), "=r"(x[27]), "=r"(x[28]), "=r"(x[29]), "=r"(x[30]), "=r"(x[31])
                                  : "r"(t_addr + FT_N + 16));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const uint32_t srow = stile_addr + (r * FT_SPITCH + h2 * 32) * 4;
+                const uint32_t srow = stile_addr + h2 * FT_SBOX_BYTES + r * 128;   // chunk q of this row: srow + ((q ^ (r & 7)) << 4)
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
                     if (q * 4 >= ncol) break;
@@ -493,7 +495,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                         if (p.relu) f = relu_ref(f);
                         o[e] = f;
                     }
-                    sts128f(srow + q * 16, o[0], o[1], o[2], o[3]);
+                    sts128f(srow + ((q ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the bulk store below reads what was just written
             }
@@ -504,13 +506,16 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the tile is staged (or abort decided)
             if (epi_abort) break;
-            // ---- write-out: one bulk copy per pixel row, shared -> global, issued by the row's first thread ----
-            if (et < 128) {
-                if (et < len)
-                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                                 ::"l"(p.out + (size_t)(rowbase + et) * p.cout + n0), "r"(stile_addr + et * FT_SPITCH * 4), "r"(n_this * 4) : "memory");
+            // ---- write-out: one tensor store (shared -> global) per 32-channel box; the descriptor is [line][pixel][channel],
+            //      so pixels beyond the row (ROWS) or beyond M (DIRECT) and channels beyond Cout are clipped ----
+            if (et == 0 || (et == 128 && n_this > 32)) {
+                const int hb = et >> 7;
+                int c1, c2;
+                if (MODE == FT_ROWS) { c2 = tile / nseg; c1 = (tile - c2 * nseg) * 128; } else { c2 = 0; c1 = tile * 128; }
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                             ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + hb * 32), "r"(c1), "r"(c2), "r"(stile_addr + hb * FT_SBOX_BYTES) : "memory");
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the row has been read: it may be overwritten
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the box has been read: it may be overwritten
             }
             asm volatile("bar.sync 1, %0;" ::"n"(FT_EPILOGUE) : "memory");   // the staging tile may be overwritten
         }

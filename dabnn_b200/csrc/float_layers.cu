@@ -2,6 +2,8 @@
 // convolution.  Elementwise kernels move 16 bytes per thread and follow the reference's operation
 // order exactly (product and sum rounded separately, no FMA contraction) so that results - and the
 // sign bits derived from them - are bit-identical to the reference's x86 build.
+#include <cuda.h>   // CUtensorMap (type only)
+
 #include <cfloat>
 
 #include <algorithm>
@@ -570,10 +572,20 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
         const int ntiles = plan.mode == FT_ROWS ? n * oh * nseg : (M + 127) / 128;
         dim3 tgrid(std::min(ntiles, std::max(1, sm_count() / ny)), ny);
         const int smem = ft_smem_bytes(kpad, plan.n_blk, plan.stages, plan.patch_bytes);
+        // output descriptor [line][pixel][channel]: ROWS = (n * oh, ow, cout), DIRECT = (1, M, cout)
+        CUtensorMap out_map{};
+        const bool rows = plan.mode == FT_ROWS;
+        const unsigned long long dims[3] = {(unsigned long long)cout, (unsigned long long)(rows ? ow : M), (unsigned long long)(rows ? n * oh : 1)};
+        const unsigned long long strides[2] = {(unsigned long long)cout * 4, (unsigned long long)(rows ? ow : M) * cout * 4};
+        const unsigned box[3] = {32, 128, 1};
+        if (!make_f32_tensor_map(&out_map, out, 3, dims, strides, box)) {
+            fconv_kernel<<<grid, FNT, 0, stream>>>(prm);   // no TMA descriptor: the mma.sync kernel
+            return check_launch("fconv_kernel");
+        }
         if (plan.mode == FT_ROWS)
-            fconv_tc5_kernel<FT_ROWS><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, plan.pitch, plan.vec16, plan.n_blk);
+            fconv_tc5_kernel<FT_ROWS><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, plan.pitch, plan.vec16, plan.n_blk, out_map);
         else
-            fconv_tc5_kernel<FT_DIRECT><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, 0, plan.vec16, plan.n_blk);
+            fconv_tc5_kernel<FT_DIRECT><<<tgrid, FT_THREADS, smem, stream>>>(prm, M, K, kpad, ntiles, plan.stages, nseg, 0, plan.vec16, plan.n_blk, out_map);
         return check_launch("fconv_tc5_kernel");
     }
     fconv_kernel<<<grid, FNT, 0, stream>>>(prm);

@@ -5,7 +5,16 @@
 #include <cstddef>
 #include <cstdint>
 
+struct CUtensorMap_st;
+
 namespace dabnn {
+
+// TMA descriptor of an fp32 tensor for tiled copies of `box` elements per dimension (innermost first) in the
+// 128-byte-swizzled shared-memory layout (inner box = 32 floats).  dims[rank], strides_bytes[rank - 1] (the
+// innermost stride is one element).  The encoder is a driver entry point fetched once through the runtime - the
+// library links no driver stub.  Returns false when the descriptor cannot be made.
+bool make_f32_tensor_map(CUtensorMap_st* map, float* base, int rank, const unsigned long long* dims,
+                         const unsigned long long* strides_bytes, const unsigned* box);
 
 // Weights of a binary convolution expanded once to the TCGEN05 engine's stage layout (bytes {0,1}, 8x the packed
 // size): size of the buffer, and the kernel that fills it.  bconv_block_impl takes the buffer as w_expanded.
