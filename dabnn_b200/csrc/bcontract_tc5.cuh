@@ -245,31 +245,43 @@ __global__ void __launch_bounds__(TC5_THREADS, 1)
         const uint32_t stage0_addr = smem_u32(stage0);
         uint32_t s = 0, use = 0;   // ring stage to fill next and how often the ring has wrapped
         bool ok = true;
+        // The loads run two chunks ahead of the expansion and do not stop at tile boundaries: the cursor below walks
+        // (tile, chunk) for the word being *loaded*, so that the first chunks of a tile are already in flight while the
+        // last chunks of the tile before are expanded (with a few chunks per tile their latency would otherwise be
+        // paid once per tile).
+        struct Pair { uint64_t a[C::WPT], b[C::WPT]; };
+        int ltile = blockIdx.x, lchunk = 0, qload = C::WPT * h;          // cursor: tile, chunk, first word index
+        RowCtx xr = xop.make_row(ltile * 128 + r);
+        typename XOp::Dec xd = xop.decode(C::WPT * h);
+        typename WOp::Dec wd = wop.decode(C::WPT * h);
+        auto load_next = [&](Pair& v) {   // this thread's words of the next chunk
+#pragma unroll
+            for (int j = 0; j < C::WPT; j++) {
+                v.a[j] = 0; v.b[j] = 0;
+                if (ltile < ntiles_m && qload + j < kwords) {
+                    const uint64_t* p = xop.addr(xr, xd);
+                    if (p) v.a[j] = __ldg(p);
+                    if (has_w) { const uint64_t* w = wop.addr(wrow, wd); if (w) v.b[j] = __ldg(w); }
+                }
+                const int adv = j == C::WPT - 1 ? C::WORDS - (C::WPT - 1) : 1;
+                xop.advance(xd, adv);
+                if (has_w) wop.advance(wd, adv);
+            }
+            qload += C::WORDS;
+            if (++lchunk == nchunks) {   // on to the next tile of this CTA
+                lchunk = 0;
+                ltile += gridDim.x;
+                qload = C::WPT * h;
+                xr = xop.make_row(ltile * 128 + r);
+                xd = xop.decode(C::WPT * h);
+                wd = wop.decode(C::WPT * h);
+            }
+        };
+        Pair v0, v1;   // chunk c and chunk c+1; chunk c+2 is loaded inside the loop
+        load_next(v0);
+        load_next(v1);
         int i = 0;
         for (int tile = blockIdx.x; tile < ntiles_m && ok; tile += gridDim.x, i++) {
-            const RowCtx xr = xop.make_row(tile * 128 + r);
-            typename XOp::Dec xd = xop.decode(C::WPT * h);   // decode state of the word being *loaded*
-            typename WOp::Dec wd = wop.decode(C::WPT * h);
-            int qload = C::WPT * h;                                           // index of the word being loaded
-            struct Pair { uint64_t a[C::WPT], b[C::WPT]; };
-            auto load_next = [&](Pair& v) {   // this thread's words of the next chunk
-#pragma unroll
-                for (int j = 0; j < C::WPT; j++) {
-                    v.a[j] = 0; v.b[j] = 0;
-                    if (qload + j < kwords) {
-                        const uint64_t* p = xop.addr(xr, xd);
-                        if (p) v.a[j] = __ldg(p);
-                        if (has_w) { const uint64_t* w = wop.addr(wrow, wd); if (w) v.b[j] = __ldg(w); }
-                    }
-                    const int adv = j == C::WPT - 1 ? C::WORDS - (C::WPT - 1) : 1;
-                    xop.advance(xd, adv);
-                    if (has_w) wop.advance(wd, adv);
-                }
-                qload += C::WORDS;
-            };
-            Pair v0, v1;   // chunk c and chunk c+1; chunk c+2 is loaded inside the loop
-            load_next(v0);
-            load_next(v1);
             int px = 0;
             for (int c = 0; c < nchunks; c++) {
                 Pair v2;
