@@ -290,42 +290,54 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             cp_async_wait<0>();   // nothing of this thread's is in flight when the CTA winds down
         } else {
             const int ohw = p.oh * p.ow;
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            // what a thread needs to gather its pixel's row of a tile: the address of tap (0, 0) and, as bit ky / kx of
+            // my / mx, whether that tap row / column lies inside the image
+            struct PixelCtx { const float* src; uint32_t my, mx; };
+            auto make_ctx = [&](int tile) {
+                PixelCtx cx{p.in, 0u, 0u};
                 const int pm = tile * 128 + r;
-                long long base = 0;
-                uint32_t my = 0, mx = 0;   // bit ky / kx set <=> that tap row / column lies inside the image for this pixel
-                if (pm < M) {
+                if (tile < ntiles && pm < M) {
                     const int img = pm / ohw, rem = pm - img * ohw, oy = rem / p.ow, ox = rem - oy * p.ow;
                     const int iy0 = oy * p.stride_h - p.pad_h, ix0 = ox * p.stride_w - p.pad_w;
-                    base = (((long long)img * p.h + iy0) * p.w + ix0) * p.cin;
-                    for (int ky = 0; ky < p.kh; ky++) my |= ((unsigned)(iy0 + ky * p.dil_h) < (unsigned)p.h ? 1u : 0u) << ky;
-                    for (int kx = 0; kx < p.kw; kx++) mx |= ((unsigned)(ix0 + kx * p.dil_w) < (unsigned)p.w ? 1u : 0u) << kx;
+                    cx.src = p.in + (((long long)img * p.h + iy0) * p.w + ix0) * p.cin;
+                    for (int ky = 0; ky < p.kh; ky++) cx.my |= ((unsigned)(iy0 + ky * p.dil_h) < (unsigned)p.h ? 1u : 0u) << ky;
+                    for (int kx = 0; kx < p.kw; kx++) cx.mx |= ((unsigned)(ix0 + kx * p.dil_w) < (unsigned)p.w ? 1u : 0u) << kx;
                 }
-                const float* src = p.in + base;
-                auto gather = [&](int c, float (&v)[16]) {
-                    const int k0 = c * FT_CHUNK + h * 16;
-                    if (vec16) {   // channels are a multiple of 4 and 16-byte aligned: a unit is four channels of one tap
+                return cx;
+            };
+            auto gather = [&](const PixelCtx& cx, int c, float (&v)[16]) {
+                const int k0 = c * FT_CHUNK + h * 16;
+                if (vec16) {   // channels are a multiple of 4 and 16-byte aligned: a unit is four channels of one tap
 #pragma unroll
-                        for (int u = 0; u < 4; u++) {
-                            const uint32_t yx = tab_yx[k0 + u * 4];
-                            const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
-                            const float4 t = valid ? __ldg(reinterpret_cast<const float4*>(src + tab_off[k0 + u * 4])) : make_float4(0.f, 0.f, 0.f, 0.f);
-                            v[u * 4 + 0] = t.x; v[u * 4 + 1] = t.y; v[u * 4 + 2] = t.z; v[u * 4 + 3] = t.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int q = 0; q < 16; q++) {
-                            const uint32_t yx = tab_yx[k0 + q];
-                            const bool valid = ((my >> (yx & 31u)) & (mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
-                            v[q] = valid ? __ldg(src + tab_off[k0 + q]) : 0.f;
-                        }
+                    for (int u = 0; u < 4; u++) {
+                        const uint32_t yx = tab_yx[k0 + u * 4];
+                        const bool valid = ((cx.my >> (yx & 31u)) & (cx.mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
+                        const float4 t = valid ? __ldg(reinterpret_cast<const float4*>(cx.src + tab_off[k0 + u * 4])) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        v[u * 4 + 0] = t.x; v[u * 4 + 1] = t.y; v[u * 4 + 2] = t.z; v[u * 4 + 3] = t.w;
                     }
-                };
-                float cur[16], nx1[16], nx2[16];   // loads run two chunks ahead of the expansion (an L2 round trip each)
-                gather(0, cur);
-                if (nchunks > 1) gather(1, nx1);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; q++) {
+                        const uint32_t yx = tab_yx[k0 + q];
+                        const bool valid = ((cx.my >> (yx & 31u)) & (cx.mx >> ((yx >> 8) & 31u)) & 1u) && !(yx >> 31);
+                        v[q] = valid ? __ldg(cx.src + tab_off[k0 + q]) : 0.f;
+                    }
+                }
+            };
+            // Loads run two chunks ahead of the expansion (an L2 round trip each), and the cursor they follow crosses
+            // tile boundaries, so the first chunks of a tile are in flight while the previous tile is still expanding.
+            int ltile = blockIdx.x, lchunk = 0;
+            PixelCtx lcx = make_ctx(ltile);
+            auto gather_next = [&](float (&v)[16]) {
+                gather(lcx, lchunk, v);   // past the last tile the context masks every tap: zeros, no loads
+                if (++lchunk == nchunks) { lchunk = 0; ltile += gridDim.x; lcx = make_ctx(ltile); }
+            };
+            float cur[16], nx1[16], nx2[16];
+            gather_next(cur);
+            gather_next(nx1);
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
                 for (int c = 0; c < nchunks && ok; c++) {
-                    if (c + 2 < nchunks) gather(c + 2, nx2);
+                    gather_next(nx2);
                     ok = emit(cur);
 #pragma unroll
                     for (int q = 0; q < 16; q++) { cur[q] = nx1[q]; nx1[q] = nx2[q]; }
