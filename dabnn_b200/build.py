@@ -13,7 +13,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "lib" / "libdabnn_b200.so"
-SOURCES = ["api.cu", "bitpack.cu", "float_layers.cu", "contraction.cu", "net.cu", "peaks.cu", "binconv_static.cu"]
+SOURCES = ["api.cu", "bitpack.cu", "float_layers.cu", "contraction.cu", "bconv_u8.cu", "net.cu", "peaks.cu", "binconv_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--cudart=static"]
 

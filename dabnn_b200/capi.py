@@ -40,6 +40,11 @@ _SIGNATURES = {
     "dabnn_binconv_forward": [_p, _p, _z, _p] + [_i] * 11 + [_p, _z, _i, _p],
     "dabnn_binconv_forward_static": [_p, _p, _z, _p] + [_i] * 11 + [_i, _p],
     "dabnn_bconv_block": [_p, _p, _z, _p, _p, _p, _p, _p] + [_i] * 12 + [_p],
+    "dabnn_binarize_u8": [_p, _p, _z, _p],
+    "dabnn_bconv_u8_supported": [_i] * 11,
+    "dabnn_bconv_u8_weight_bytes": [_i, _i],
+    "dabnn_bconv_u8_expand_weights": [_p, _z, _i, _i, _p, _p],
+    "dabnn_bconv_u8_block": [_p, _p, _p, _p, _p, _p, _p, _p] + [_i] * 11 + [_p],
     "dabnn_affine": [_p, _p, _p, _z, _i, _p],
     "dabnn_add": [_p, _p, _z, _p],
     "dabnn_relu": [_p, _z, _p],
@@ -73,7 +78,7 @@ _SIGNATURES = {
     "dabnn_device_count": [],
 }
 _RESTYPES = {"dabnn_last_error": C.c_char_p, "dabnn_version": C.c_char_p, "dabnn_net_destroy": None,
-             "dabnn_binconv_workspace_bytes": C.c_size_t, "dabnn_net_output_name": C.c_char_p,
+             "dabnn_binconv_workspace_bytes": C.c_size_t, "dabnn_bconv_u8_weight_bytes": C.c_size_t, "dabnn_net_output_name": C.c_char_p,
              "dabnn_net_stream": C.c_void_p}
 
 _lib = None

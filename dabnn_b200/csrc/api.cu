@@ -28,22 +28,27 @@ int sm_count() {
     return cached[dev];
 }
 
-bool make_f32_tensor_map(CUtensorMap_st* map, float* base, int rank, const unsigned long long* dims,
-                         const unsigned long long* strides_bytes, const unsigned* box) {
-    typedef CUresult (*Encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static Encode encode = nullptr;
+typedef CUresult (*TensorMapEncode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncode tensor_map_encoder() {
+    static TensorMapEncode encode = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult st;
         if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &st) == cudaSuccess &&
             st == cudaDriverEntryPointSuccess)
-            encode = reinterpret_cast<Encode>(fn);
+            encode = reinterpret_cast<TensorMapEncode>(fn);
         else
             cudaGetLastError();
     });
+    return encode;
+}
+
+bool make_f32_tensor_map(CUtensorMap_st* map, float* base, int rank, const unsigned long long* dims,
+                         const unsigned long long* strides_bytes, const unsigned* box) {
+    const TensorMapEncode encode = tensor_map_encoder();
     if (!encode || !base || rank < 2 || rank > 3) return false;
     cuuint64_t d[3], s[2];
     cuuint32_t b[3], e[3] = {1, 1, 1};
@@ -51,6 +56,19 @@ bool make_f32_tensor_map(CUtensorMap_st* map, float* base, int rank, const unsig
     for (int i = 0; i + 1 < rank; i++) s[i] = strides_bytes[i];
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, base, d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_u8_tensor_map(CUtensorMap_st* map, const unsigned char* base, int rank, const unsigned long long* dims,
+                        const unsigned long long* strides_bytes, const unsigned* box) {
+    const TensorMapEncode encode = tensor_map_encoder();
+    if (!encode || !base || rank < 2 || rank > 5 || box[0] != 64) return false;
+    cuuint64_t d[5], s[4];
+    cuuint32_t b[5], e[5] = {1, 1, 1, 1, 1};
+    for (int i = 0; i < rank; i++) { d[i] = dims[i]; b[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; i++) s[i] = strides_bytes[i];
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<unsigned char*>(base), d, s, b, e,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace dabnn

@@ -1,0 +1,178 @@
+// Host side of the byte-activation binary convolution (bconv_u8.cuh): geometry, tensor maps, launches, C ABI.
+#include <algorithm>
+
+#include "bconv_u8.cuh"
+#include "kernels.h"
+
+namespace dabnn {
+
+namespace {
+
+struct U8Plan {
+    int OH = 0, OW = 0, rows = 0, imgs = 0, tiles_per_img = 0, ntiles = 0, G = 0, stages = 0, wb = 0, nboxes = 0;
+    int smem = 0;
+};
+
+// Shapes the engine takes: whole 64-channel groups, channel counts in 16s, stride 1 or 2 (even H and W), no
+// dilation, output rows of at most 128 pixels.
+bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
+             U8Plan& pl) {
+    if (n <= 0 || h <= 0 || w <= 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || pad_h < 0 || pad_w < 0) return false;
+    if (cin % 64 || cout % 16 || stride_h != stride_w || (stride_h != 1 && stride_h != 2)) return false;
+    if (stride_h == 2 && ((h | w) & 1)) return false;
+    pl.OH = conv_out_dim(h, pad_h, 1, kh, stride_h);
+    pl.OW = conv_out_dim(w, pad_w, 1, kw, stride_w);
+    if (pl.OH <= 0 || pl.OW <= 0 || pl.OW > 128) return false;
+    if ((long long)n * pl.OH * pl.OW >= (1ll << 31) || kh > 255 || kw > 255) return false;
+    const int ohw = pl.OH * pl.OW;
+    if (ohw <= 128) {
+        pl.imgs = 128 / ohw; pl.rows = pl.OH; pl.tiles_per_img = 1;
+        pl.ntiles = (n + pl.imgs - 1) / pl.imgs;
+    } else {
+        const int rmax = 128 / pl.OW;
+        pl.tiles_per_img = (pl.OH + rmax - 1) / rmax;
+        pl.rows = (pl.OH + pl.tiles_per_img - 1) / pl.tiles_per_img;
+        pl.imgs = 1;
+        pl.ntiles = n * pl.tiles_per_img;
+    }
+    pl.nboxes = kh * kw * (cin / 64);
+    pl.wb = u8_weight_rows(cout);
+    pl.G = pl.nboxes % 3 == 0 ? 3 : pl.nboxes % 4 == 0 ? 4 : pl.nboxes % 2 == 0 ? 2 : std::min(pl.nboxes, 3);
+    const int stage_bytes = pl.G * (U8_BOX_BYTES + pl.wb * 64);
+    const int avail = U8_MAX_SMEM - 1024 - 2 * U8_STILE_BYTES - 3072 /* static shared memory */;
+    pl.stages = std::min(8, avail / stage_bytes);
+    if (pl.stages < 2) return false;
+    pl.smem = pl.stages * stage_bytes + 2 * U8_STILE_BYTES + 1024;
+    return true;
+}
+
+// maps[0] / maps[1]: the input seen from even / odd rows (the same map twice for stride 1)
+bool u8_input_maps(const unsigned char* in, int n, int h, int w, int cin, int stride, const U8Plan& pl, CUtensorMap* maps) {
+    const unsigned long long C = cin;
+    const unsigned box[5] = {64u, (unsigned)pl.OW, (unsigned)pl.rows, (unsigned)pl.imgs, 1u};
+    if (stride == 1) {
+        const unsigned long long dims[5] = {C, (unsigned long long)w, (unsigned long long)h, (unsigned long long)n, 1ull};
+        const unsigned long long strides[4] = {C, C * w, C * w * h, C * w * h * n};
+        if (!make_u8_tensor_map(&maps[0], in, 5, dims, strides, box)) return false;
+        maps[1] = maps[0];
+        return true;
+    }
+    for (int hp = 0; hp < 2; hp++) {
+        const unsigned long long dims[5] = {C, (unsigned long long)(w / 2), (unsigned long long)(h / 2), (unsigned long long)n, 2ull};
+        const unsigned long long strides[4] = {2 * C, 2 * C * w, C * w * h, C};
+        if (!make_u8_tensor_map(&maps[hp], in + (size_t)hp * w * cin, 5, dims, strides, box)) return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+bool bconv_u8_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w) {
+    U8Plan pl;
+    if (!u8_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, pl)) return false;
+    // the encoder only looks at the address's alignment: try the descriptors of this shape once
+    CUtensorMap maps[2];
+    return u8_input_maps(reinterpret_cast<const unsigned char*>(uintptr_t(1) << 20), n, h, w, cin, stride_h, pl, maps);
+}
+
+size_t bconv_u8_weight_bytes(int cout, int nboxes) { return u8_weight_bytes(cout, nboxes); }
+
+int bconv_u8_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int nboxes, unsigned char* dst,
+                            cudaStream_t stream) {
+    DABNN_REQUIRE(weight && dst && cout > 0 && nboxes > 0, DABNN_ERR_ARG, "bconv_u8_expand_weights: bad arguments");
+    DABNN_REQUIRE(weight_words % (size_t)cout == 0 && weight_words / cout >= (size_t)nboxes, DABNN_ERR_SHAPE,
+                  "bconv_u8_expand_weights: filter rows shorter than kh*kw*cin/64 words");
+    DABNN_REQUIRE((reinterpret_cast<uintptr_t>(dst) & 15) == 0, DABNN_ERR_ARG, "bconv_u8_expand_weights: dst must be 16-byte aligned");
+    dim3 grid(nboxes, (cout + TC5_MAX_N - 1) / TC5_MAX_N);
+    bconv_u8_expand_weights_kernel<<<grid, 256, 0, stream>>>(weight, (long long)(weight_words / cout), cout, nboxes, dst);
+    return check_launch("bconv_u8_expand_weights_kernel");
+}
+
+int binarize_u8_impl(const float* in, unsigned char* out, size_t count, cudaStream_t stream) {
+    if (count == 0) return DABNN_OK;
+    DABNN_REQUIRE(in && out, DABNN_ERR_ARG, "binarize_u8: null pointer");
+    DABNN_REQUIRE(((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0, DABNN_ERR_ARG,
+                  "binarize_u8: pointers must be 16-byte aligned");
+    const size_t n16 = count / 16;
+    const int blocks = (int)std::min<size_t>((n16 + 255) / 256 + 1, (size_t)sm_count() * 16);
+    binarize_u8_kernel<<<blocks, 256, 0, stream>>>(in, out, n16, count);
+    return check_launch("binarize_u8_kernel");
+}
+
+int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, const float* a, const float* b,
+                        const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, int n, int h, int w,
+                        int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
+                        cudaStream_t stream) {
+    DABNN_REQUIRE(in_u8 && w_img, DABNN_ERR_ARG, "bconv_u8: null pointer");
+    DABNN_REQUIRE((a == nullptr) == (b == nullptr), DABNN_ERR_ARG, "bconv_u8: a and b go together");
+    DABNN_REQUIRE(out_f32 || out_u8 || out_bits, DABNN_ERR_ARG, "bconv_u8: no output requested");
+    U8Plan pl;
+    DABNN_REQUIRE(u8_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, pl), DABNN_ERR_SHAPE,
+                  "bconv_u8: shape not supported by the byte-activation engine");
+    DABNN_REQUIRE(!out_bits || cout % 64 == 0, DABNN_ERR_SHAPE, "bconv_u8: bit output needs cout % 64 == 0");
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    DABNN_REQUIRE(al16(in_u8) && al16(w_img) && al16(shortcut) && al16(out_f32) && al16(out_u8) && al16(out_bits), DABNN_ERR_ARG,
+                  "bconv_u8: pointers must be 16-byte aligned");
+    static thread_local int configured_device = -1;
+    int dev = 0;
+    DABNN_CUDA_OK(cudaGetDevice(&dev));
+    if (configured_device != dev) {
+        DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_u8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
+        configured_device = dev;
+    }
+    CUtensorMap in_maps[2], out_map{};
+    DABNN_REQUIRE(u8_input_maps(in_u8, n, h, w, cin, stride_h, pl, in_maps), DABNN_ERR_CUDA, "bconv_u8: cannot encode the input's tensor map");
+    if (out_f32) {
+        const unsigned long long dims[3] = {(unsigned long long)cout, (unsigned long long)pl.OH * pl.OW, (unsigned long long)n};
+        const unsigned long long strides[2] = {(unsigned long long)cout * 4, (unsigned long long)cout * 4 * pl.OH * pl.OW};
+        const unsigned box[3] = {32u, (unsigned)(pl.rows * pl.OW), (unsigned)pl.imgs};
+        DABNN_REQUIRE(make_f32_tensor_map(&out_map, out_f32, 3, dims, strides, box), DABNN_ERR_CUDA,
+                      "bconv_u8: cannot encode the output's tensor map");
+    }
+    U8Params p{};
+    p.w_img = w_img; p.a = a; p.b = b; p.shortcut = shortcut; p.out = out_f32; p.out_u8 = out_u8; p.out_bits = out_bits;
+    p.B = n; p.OH = pl.OH; p.OW = pl.OW; p.N = cout;
+    p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w; p.stride = stride_h; p.cw = cin / 64;
+    p.rows = pl.rows; p.imgs = pl.imgs; p.tiles_per_img = pl.tiles_per_img; p.ntiles = pl.ntiles;
+    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes;
+    const int tiles_n = (cout + TC5_MAX_N - 1) / TC5_MAX_N;
+    const int per_n = std::max(1, sm_count() / tiles_n);
+    dim3 grid(std::min(pl.ntiles, per_n), tiles_n);
+    bconv_u8_kernel<<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
+    return check_launch("bconv_u8_kernel");
+}
+
+int bconv_u8_status(int* status) {
+    DABNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_u8_status, sizeof(int)));
+    return DABNN_OK;
+}
+
+}  // namespace dabnn
+
+using namespace dabnn;
+
+extern "C" int dabnn_binarize_u8(const float* in, unsigned char* out, size_t count, dabnn_stream_t s) {
+    return binarize_u8_impl(in, out, count, static_cast<cudaStream_t>(s));
+}
+
+extern "C" int dabnn_bconv_u8_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w,
+                                        int stride_h, int stride_w) {
+    return bconv_u8_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w) ? 1 : 0;
+}
+
+extern "C" size_t dabnn_bconv_u8_weight_bytes(int cout, int kwords) {
+    return cout > 0 && kwords > 0 ? bconv_u8_weight_bytes(cout, kwords) : 0;
+}
+
+extern "C" int dabnn_bconv_u8_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int kwords,
+                                             unsigned char* dst, dabnn_stream_t s) {
+    return bconv_u8_expand_weights(weight, weight_words, cout, kwords, dst, static_cast<cudaStream_t>(s));
+}
+
+extern "C" int dabnn_bconv_u8_block(const unsigned char* in_u8, const unsigned char* w_expanded, const float* a, const float* b,
+                                    const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, int n,
+                                    int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                                    int stride_w, dabnn_stream_t s) {
+    return bconv_u8_block_impl(in_u8, w_expanded, a, b, shortcut, out_f32, out_u8, out_bits, n, h, w, cin, cout, kh, kw, pad_h,
+                               pad_w, stride_h, stride_w, static_cast<cudaStream_t>(s));
+}

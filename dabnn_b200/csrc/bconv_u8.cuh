@@ -1,0 +1,392 @@
+// Binary convolution on activations kept as {0,1} bytes: TMA feeds tcgen05.mma kind::i8 directly.
+//
+// The engine in bcontract_tc5.cuh reads packed bits and spends its time expanding them to bytes in shared
+// memory with eight producer warps.  Here the layer that produces an activation also writes it as one byte per
+// channel (NHWC, 8x the packed size, a quarter of the fp32 copy that is written anyway), and then the pixel
+// operand of a convolution tap is a rectangle of that tensor: for a tile of whole output rows,
+//
+//   A_tap[(row, ow)][c] = x8[img][row * s + ky - pad][ow * s + kx - pad][c]     (zero outside the image),
+//
+// which is one tiled TMA load per tap and 64-channel group, 64-byte-swizzled, landing in exactly the K-major
+// layout tcgen05.mma reads.  Zero fill outside the image is the reference's padding (bit 0).  No thread touches
+// the operand: one lane issues the loads, one lane issues the MMAs, the other warps are the epilogue.
+//
+//   cnt[p][n] = popc(x[p]) + popc(w[n]) - 2 * sum_k a[p][k] * b[n][k]
+//
+// popc(x[p]) (over the zero-padded window) comes out of the same MMA: the weight image of every channel block
+// carries one extra row of ones, so accumulator column n_this is the row popcount.
+//
+// Tiles: OW <= 128.  If an image has more than 128 output pixels a tile is `rows` whole output rows of one image
+// (rows * OW <= 128), else `imgs` whole images.  The M = 128 rows of the MMA beyond the tile's pixels hold stale
+// bytes; their accumulator lanes are never read.  The input's tensor map has five dimensions (c, w, h, image,
+// column parity): stride 1 uses parity 0 only; stride 2 views W as (W / 2, parity) and folds the row parity into
+// the base address (two tensor maps), so that a tap is still a dense box.
+//
+// Weights: expanded once (bconv_u8_expand_weights_kernel) into per-(channel block, K box) images in the
+// SWIZZLE_NONE K-major core-matrix layout, streamed per stage by one bulk copy.
+//
+// Every wait is bounded; a wait that gives up records a code in a status word, raises the CTA's abort flag,
+// and the CTA frees its tensor memory and returns.
+#pragma once
+#include "bcontract_tc5.cuh"
+
+namespace dabnn {
+
+constexpr int U8_BOX_BYTES = 128 * 64;       // one K box of the pixel operand: 128 rows x 64 bytes
+constexpr int U8_ACCS = 3;                   // TMEM accumulators of up to 144 columns
+constexpr int U8_EPI_WARPS = 8;
+constexpr int U8_EPILOGUE = U8_EPI_WARPS * 32;
+constexpr int U8_THREADS = 64 + U8_EPILOGUE;  // warp 0: loads, warp 1: MMA, then the epilogue warps
+constexpr int U8_SBOX_BYTES = 128 * 128;     // staging box: 128 pixels x 32 channels of fp32, 128-byte-swizzled
+constexpr int U8_STILE_BYTES = 2 * U8_SBOX_BYTES;
+constexpr int U8_MAX_SMEM = 227 * 1024;
+
+__device__ int g_u8_status;   // 0 = ok; 21 loader, 22 MMA (accumulator), 23 MMA (stage), 24 epilogue
+
+struct U8Params {
+    const unsigned char* w_img;   // expanded weights (bconv_u8_expand_weights_kernel)
+    const float *a, *b;           // per-channel affine (both or neither)
+    const float* shortcut;        // fp32 [M][N] added after the affine, or null
+    float* out;                   // fp32 [M][N] or null
+    unsigned char* out_u8;        // {0,1} bytes [M][N] or null
+    uint64_t* out_bits;           // packed sign bits [M][N/64] or null
+    int B, OH, OW, N;
+    int kh, kw, pad_h, pad_w, stride, cw;
+    int rows, imgs, tiles_per_img, ntiles;
+    int G, stages, wb, nboxes;    // K boxes per stage, ring stages, rows of a weight box image, kh*kw*cw
+};
+
+__host__ __device__ inline int u8_weight_rows(int N) { return min(N, TC5_MAX_N) + 16; }
+__host__ __device__ inline size_t u8_weight_image_bytes(int N, int nboxes) {
+    return (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * nboxes * u8_weight_rows(N) * 64;
+}
+__host__ __device__ inline size_t u8_weight_bytes(int N, int nboxes) {
+    return u8_weight_image_bytes(N, nboxes) + (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * TC5_MAX_N * sizeof(int);
+}
+
+// grid (nboxes, channel blocks): the image of K box q (= packed word q) of one channel block: wb rows x 64 bytes,
+// byte k of row n = bit k of the word, stored as 8-row x 16-byte core matrices ([row / 8][k / 16][row % 8][k % 16]).
+// Row n_this is all ones (it yields the pixel rows' popcounts), the rows after it are zero.
+__global__ void __launch_bounds__(256) bconv_u8_expand_weights_kernel(const uint64_t* w, const long long ldw, const int N,
+                                                                      const int nboxes, unsigned char* dst) {
+    const int q = blockIdx.x, nb = blockIdx.y, wb = u8_weight_rows(N);
+    const int n0 = nb * TC5_MAX_N, n_this = min(TC5_MAX_N, N - n0);
+    unsigned char* img = dst + ((size_t)nb * nboxes + q) * wb * 64;
+    for (int idx = threadIdx.x; idx < wb * 4; idx += blockDim.x) {
+        const int row = idx >> 2, unit = idx & 3;
+        uint32_t bits = 0;
+        if (row < n_this) bits = (uint32_t)(__ldg(w + (long long)(n0 + row) * ldw + q) >> (unit * 16)) & 0xffffu;
+        else if (row == n_this) bits = 0xffffu;
+        uint4 v;
+        v.x = ((bits & 0xfu) * 0x00204081u) & 0x01010101u;
+        v.y = (((bits >> 4) & 0xfu) * 0x00204081u) & 0x01010101u;
+        v.z = (((bits >> 8) & 0xfu) * 0x00204081u) & 0x01010101u;
+        v.w = (((bits >> 12) & 0xfu) * 0x00204081u) & 0x01010101u;
+        *reinterpret_cast<uint4*>(img + (row >> 3) * 512 + unit * 128 + (row & 7) * 16) = v;
+    }
+    if (q == 0 && threadIdx.x < TC5_MAX_N) {
+        int pc = 0;
+        if ((int)threadIdx.x < n_this)
+            for (int k = 0; k < nboxes; k++) pc += __popcll(__ldg(w + (long long)(n0 + threadIdx.x) * ldw + k));
+        reinterpret_cast<int*>(dst + u8_weight_image_bytes(N, nboxes))[n0 + threadIdx.x] = pc;
+    }
+}
+
+// fp32 -> {0,1} bytes (x > 0), 16 elements per thread step
+__global__ void __launch_bounds__(256) binarize_u8_kernel(const float* __restrict__ in, unsigned char* __restrict__ out, const size_t n16,
+                                                           const size_t count) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        uint32_t wds[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(in) + i * 4 + j);
+            wds[j] = (f.x > 0.f ? 1u : 0u) | (f.y > 0.f ? 0x100u : 0u) | (f.z > 0.f ? 0x10000u : 0u) | (f.w > 0.f ? 0x1000000u : 0u);
+        }
+        reinterpret_cast<uint4*>(out)[i] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+    }
+    if (blockIdx.x == 0)   // tail
+        for (size_t i = n16 * 16 + threadIdx.x; i < count; i += blockDim.x) out[i] = in[i] > 0.f ? 1 : 0;
+}
+
+// K-major SWIZZLE_64B shared-memory descriptor: 8-row groups 512 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)4 << 61);
+}
+
+__global__ void __launch_bounds__(U8_THREADS, 1)
+    bconv_u8_kernel(const U8Params p, const __grid_constant__ CUtensorMap in_map0, const __grid_constant__ CUtensorMap in_map1,
+                    const __grid_constant__ CUtensorMap out_map) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_acc_full[U8_ACCS], bar_acc_empty[U8_ACCS];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int s_abort, epi_abort;
+    __shared__ int popw[TC5_MAX_N];
+    __shared__ __align__(16) float chan_a[TC5_MAX_N];
+    __shared__ __align__(16) float chan_b[TC5_MAX_N];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.y * TC5_MAX_N;
+    const int n_this = min(TC5_MAX_N, p.N - n0);   // multiple of 16 (host-checked)
+    const int n_mma = n_this + 16;                  // + the row of ones
+    const int a_bytes = p.G * U8_BOX_BYTES, wbox_bytes = p.wb * 64, stage_bytes = a_bytes + p.G * wbox_bytes;
+    unsigned char* stage0 = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    const int nst = (p.nboxes + p.G - 1) / p.G;     // stages per tile
+    int tmem_cols = 32;
+    while (tmem_cols < U8_ACCS * n_mma) tmem_cols <<= 1;
+    const volatile int* abort_flag = &s_abort;
+    const int ohw = p.OH * p.OW;
+    const int box_px = p.rows * p.OW * p.imgs;      // pixels a tile's loads and stores cover
+
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid == 0) {
+        for (int i = 0; i < p.stages; i++) { mbar_init(&bar_full[i], 1); mbar_init(&bar_empty[i], 1); }
+        for (int i = 0; i < U8_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], U8_EPI_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::);
+        s_abort = 0;
+        epi_abort = 0;
+    }
+    if (tid < TC5_MAX_N) {
+        popw[tid] = __ldg(reinterpret_cast<const int*>(p.w_img + u8_weight_image_bytes(p.N, p.nboxes)) + n0 + tid);
+        const bool have = p.a && tid < n_this;
+        chan_a[tid] = have ? __ldg(p.a + n0 + tid) : 1.f;
+        chan_b[tid] = have ? __ldg(p.b + n0 + tid) : 0.f;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        // =========================== loads: one lane ===========================
+        if (lane == 0) {
+            const unsigned char* wsrc = p.w_img + (size_t)blockIdx.y * p.nboxes * wbox_bytes;
+            const uint32_t stage0_addr = smem_u32(stage0);
+            const uint32_t box_tx = (uint32_t)box_px * 64u;   // a load always delivers its whole box (zeros outside the tensor)
+            uint32_t s = 0, use = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
+                const int tq = tile / p.tiles_per_img;
+                const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
+                int cg = 0, ky = 0, kx = 0;
+                for (int st = 0; st < nst; st++) {
+                    if (use >= 1 && !mbar_wait<32>(&bar_empty[s], (use - 1) & 1, abort_flag)) {
+                        atomicCAS(&g_u8_status, 0, 21);
+                        s_abort = 1;
+                        ok = false;
+                        break;
+                    }
+                    const int nb = min(p.G, p.nboxes - st * p.G);
+                    const uint32_t bar = smem_u32(&bar_full[s]), sa = stage0_addr + s * stage_bytes;
+                    const uint32_t wbytes = (uint32_t)(nb * wbox_bytes);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(wbytes + nb * box_tx) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(sa + a_bytes), "l"(wsrc + (size_t)st * p.G * wbox_bytes), "r"(wbytes), "r"(bar) : "memory");
+                    for (int b = 0; b < nb; b++) {
+                        const int dy = ky - p.pad_h, dx = kx - p.pad_w;
+                        int c1 = 0, c2 = dx, c3 = oh0 + dy;
+                        const CUtensorMap* map = &in_map0;
+                        if (p.stride == 2) {
+                            const int hp = dy & 1, wp = dx & 1;
+                            c1 = wp; c2 = (dx - wp) >> 1; c3 = oh0 + ((dy - hp) >> 1);
+                            if (hp) map = &in_map1;
+                        }
+                        asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                                     ::"r"(sa + b * U8_BOX_BYTES), "l"(reinterpret_cast<uint64_t>(map)), "r"(cg * 64), "r"(c2), "r"(c3), "r"(img0),
+                                       "r"(c1), "r"(bar) : "memory");
+                        if (++cg == p.cw) { cg = 0; if (++kx == p.kw) { kx = 0; ky++; } }
+                    }
+                    if (++s == (uint32_t)p.stages) { s = 0; use++; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // =========================== MMA issue: one lane ===========================
+        if (lane == 0) {
+            // instruction descriptor: D = s32, A = u8, B = u8, both K-major, N = n_mma, M = 128
+            const uint32_t idesc = (2u << 4) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            const uint64_t d_a = umma_desc_sw64(smem_u32(stage0)), d_b = umma_desc(smem_u32(stage0) + a_bytes, 512);
+            uint32_t s = 0, par = 0;
+            bool ok = true;
+            int i = 0;
+            for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, i++) {
+                const int accbuf = i % U8_ACCS, accuse = i / U8_ACCS;
+                if (accuse >= 1 && !mbar_wait(&bar_acc_empty[accbuf], (accuse - 1) & 1, abort_flag)) {
+                    atomicCAS(&g_u8_status, 0, 22);
+                    s_abort = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + accbuf * n_mma;
+                uint32_t accum = 0;
+                for (int st = 0; st < nst; st++) {
+                    if (!mbar_wait(&bar_full[s], par, abort_flag)) {
+                        atomicCAS(&g_u8_status, 0, 23);
+                        s_abort = 1;
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const int nb = min(p.G, p.nboxes - st * p.G);
+                    uint64_t ad = d_a + (uint64_t)(s * (stage_bytes >> 4)), bd = d_b + (uint64_t)(s * (stage_bytes >> 4));
+                    for (int b = 0; b < nb; b++) {
+                        // one MMA per 32 bytes of K: 32 bytes along the swizzled row of A, two 16-byte units (256 bytes) of B
+                        mma_i8_ss(d_tmem, ad, bd, idesc, accum);
+                        mma_i8_ss(d_tmem, ad + 2, bd + 16, idesc, 1u);
+                        accum = 1u;
+                        ad += U8_BOX_BYTES >> 4;
+                        bd += (uint64_t)(wbox_bytes >> 4);
+                    }
+                    umma_commit(&bar_empty[s]);
+                    if (++s == (uint32_t)p.stages) { s = 0; par ^= 1u; }
+                }
+                if (ok) umma_commit(&bar_acc_full[accbuf]);
+            }
+        }
+    } else {
+        // =========================== epilogue ===========================
+        // Blocks of 64 channels through two fp32 staging tiles: the shortcut of block k+1 is copied into the idle
+        // tile with cp.async while block k is drained (thread (r, h2): 32 accumulator columns of pixel r), then one
+        // TMA tensor store per 32-channel box writes the fp32 result; the {0,1} bytes and the packed sign bits of
+        // the result go straight from registers to global memory.
+        const int et = tid - 64, ew = warp - 2;
+        const int r = (warp & 3) * 32 + lane, h2 = ew >> 2;   // TMEM lane quarter of a warp = warp % 4
+        const uint32_t sbuf0_addr = smem_u32(stage0 + p.stages * stage_bytes);
+        const int nblk = (n_this + 63) >> 6;
+        int my_tiles = 0;
+        for (int t = blockIdx.x; t < p.ntiles; t += gridDim.x) my_tiles++;
+        const int total_blocks = my_tiles * nblk;
+        // first output pixel of a tile and how many of its pixels exist
+        auto tile_span = [&](int tile, long long& base, int& nvalid) {
+            const int tq = tile / p.tiles_per_img;
+            const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
+            base = ((long long)img0 * p.OH + oh0) * p.OW;
+            nvalid = p.imgs > 1 ? min(p.imgs, p.B - img0) * ohw : min(p.rows, p.OH - oh0) * p.OW;
+        };
+        auto prefetch = [&](int kb) {
+            if (p.shortcut && kb < total_blocks) {
+                const int tile = blockIdx.x + (kb / nblk) * gridDim.x, cb = (kb % nblk) * 64;
+                const int width = min(64, n_this - cb);
+                long long base; int nvalid;
+                tile_span(tile, base, nvalid);
+                const uint32_t sbase = sbuf0_addr + (kb & 1) * U8_STILE_BYTES;
+#pragma unroll
+                for (int j = 0; j < 2048 / U8_EPILOGUE; j++) {
+                    const int it = et + j * U8_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
+                    if (rr < nvalid && c4 < width)
+                        cp_async16(sbase + (c4 >> 5) * U8_SBOX_BYTES + rr * 128 + ((((c4 & 31) >> 2) ^ (rr & 7)) << 4),
+                                   p.shortcut + (base + rr) * p.N + n0 + cb + c4, 16);
+                }
+            }
+            cp_async_commit();
+        };
+        prefetch(0);
+        bool okw = true;
+        for (int kb = 0; kb < total_blocks; kb++) {
+            const int i = kb / nblk, blk = kb % nblk;
+            const int tile = blockIdx.x + i * gridDim.x, cb = blk * 64;
+            const int width = min(64, n_this - cb);
+            const int accbuf = i % U8_ACCS, accuse = i / U8_ACCS;
+            const uint32_t sb = sbuf0_addr + (kb & 1) * U8_STILE_BYTES;
+            long long base; int nvalid;
+            tile_span(tile, base, nvalid);
+            cp_async_wait<0>();                                               // my copies of block kb have landed
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my tensor stores of block kb-1 have read their source
+            asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");    // everybody's have: the other staging tile is idle
+            prefetch(kb + 1);
+            const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
+            if (blk == 0 && okw) {
+                okw = __all_sync(0xffffffffu, mbar_wait<200>(&bar_acc_full[accbuf], accuse & 1, abort_flag));
+                if (!okw) {
+                    atomicCAS(&g_u8_status, 0, 24);
+                    s_abort = 1;
+                    epi_abort = 1;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (okw && ncol > 0) {
+                const int c0 = cb + h2 * 32;
+                const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * n_mma;
+                uint32_t v[32], pxu;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                               "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                             : "r"(t_row + c0));
+                if (ncol > 16)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                                 : "r"(t_row + c0 + 16));
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(pxu) : "r"(t_row + n_this));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int px = (int)pxu;
+                const uint32_t srow = sb + h2 * U8_SBOX_BYTES + r * 128;   // chunk q of this row: srow + ((q ^ (r & 7)) << 4)
+                uint32_t signs = 0;   // bit j: channel c0 + j of this pixel is positive
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    if (q * 4 >= ncol) break;
+                    float o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int cl = c0 + q * 4 + e;
+                        float f = small_int_to_float(px + popw[cl] - 2 * (int)v[q * 4 + e]);
+                        if (p.a) f = __fadd_rn(__fmul_rn(chan_a[cl], f), chan_b[cl]);
+                        o[e] = f;
+                    }
+                    if (p.shortcut) {
+                        const float4 ad = lds128f(srow + ((q ^ (r & 7)) << 4));
+                        o[0] = __fadd_rn(ad.x, o[0]); o[1] = __fadd_rn(ad.y, o[1]);
+                        o[2] = __fadd_rn(ad.z, o[2]); o[3] = __fadd_rn(ad.w, o[3]);
+                    }
+                    sts128f(srow + ((q ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
+                    signs |= ((o[0] > 0.f ? 1u : 0u) | (o[1] > 0.f ? 2u : 0u) | (o[2] > 0.f ? 4u : 0u) | (o[3] > 0.f ? 8u : 0u)) << (q * 4);
+                }
+                if (r < nvalid) {
+                    const long long row = base + r;
+                    if (p.out_bits && ncol == 32) reinterpret_cast<uint32_t*>(p.out_bits + row * (p.N >> 6) + ((n0 + cb) >> 6))[h2] = signs;
+                    if (p.out_u8) {
+                        uint4* dst = reinterpret_cast<uint4*>(p.out_u8 + row * p.N + n0 + c0);
+                        uint32_t w8[8];
+#pragma unroll
+                        for (int q = 0; q < 8; q++) w8[q] = (((signs >> (q * 4)) & 0xfu) * 0x00204081u) & 0x01010101u;
+                        dst[0] = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+                        if (ncol > 16) dst[1] = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor store below reads what was just written
+            }
+            if (blk == nblk - 1 && okw) {   // the whole accumulator has been read
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_acc_empty[accbuf]);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
+            if (epi_abort) break;
+            // ---- write-out: one tensor store per 32-channel box; pixels beyond the image / batch and channels beyond N are clipped ----
+            if (p.out && (et == 0 || (et == 128 && width > 32))) {
+                const int hb = et >> 7;
+                const int tq = tile / p.tiles_per_img;
+                const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                             ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + cb + hb * 32), "r"(oh0 * p.OW), "r"(img0),
+                               "r"(sb + hb * U8_SBOX_BYTES) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        cp_async_wait<0>();
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols));
+    }
+}
+
+}  // namespace dabnn

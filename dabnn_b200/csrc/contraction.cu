@@ -242,6 +242,10 @@ extern "C" int dabnn_engine_status(int* status) {
     DABNN_REQUIRE(status, DABNN_ERR_ARG, "null output");
     DABNN_CUDA_OK(cudaDeviceSynchronize());
     DABNN_CUDA_OK(cudaMemcpyFromSymbol(status, g_tc5_status, sizeof(int)));
-    if (*status == 0) return fconv_tc5_status(status);   // the float convolution keeps its own word (codes 11-14)
+    if (*status == 0) {   // the float convolution (codes 11-16) and the byte-activation engine (21-24) keep their own words
+        const int rc = fconv_tc5_status(status);
+        if (rc) return rc;
+    }
+    if (*status == 0) return bconv_u8_status(status);
     return DABNN_OK;
 }

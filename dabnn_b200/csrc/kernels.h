@@ -16,6 +16,11 @@ namespace dabnn {
 bool make_f32_tensor_map(CUtensorMap_st* map, float* base, int rank, const unsigned long long* dims,
                          const unsigned long long* strides_bytes, const unsigned* box);
 
+// The same for a tensor of bytes, up to five dimensions, inner box 64 bytes, 64-byte-swizzled (the layout a
+// K-major SWIZZLE_64B shared-memory descriptor of tcgen05.mma reads); elements outside the tensor read as zero.
+bool make_u8_tensor_map(CUtensorMap_st* map, const unsigned char* base, int rank, const unsigned long long* dims,
+                        const unsigned long long* strides_bytes, const unsigned* box);
+
 // Weights of a binary convolution expanded once to the TCGEN05 engine's stage layout (bytes {0,1}, 8x the packed
 // size): size of the buffer, and the kernel that fills it.  bconv_block_impl takes the buffer as w_expanded.
 size_t bconv_expanded_weight_bytes(int cout, int kwords);
@@ -26,6 +31,19 @@ int bconv_block_impl(const uint64_t* in_bits, const uint64_t* weight, size_t wei
                      const float* b, const float* shortcut, float* out_f32, uint64_t* out_bits, int n, int h,
                      int w, int cw, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
                      int stride_w, int engine, cudaStream_t stream, const unsigned char* w_expanded = nullptr);
+
+// Byte-activation engine (bconv_u8.cuh): activations as {0,1} bytes in NHWC, fed to the tensor cores by TMA.
+// bconv_u8_supported: whether the shape is taken (and its tensor maps can be encoded on this driver).
+bool bconv_u8_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w);
+size_t bconv_u8_weight_bytes(int cout, int nboxes);
+int bconv_u8_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int nboxes, unsigned char* dst,
+                            cudaStream_t stream);
+int binarize_u8_impl(const float* in, unsigned char* out, size_t count, cudaStream_t stream);
+int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, const float* a, const float* b,
+                        const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, int n, int h, int w,
+                        int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
+                        cudaStream_t stream);
+int bconv_u8_status(int* status);
 
 // Elementwise chain on an fp32 NHWC tensor, in one pass:  v = x;  if (a) v = a[c]*v + b[c];
 // if (add) v += add;  if (relu) v = max(v, 0);  optional fp32 store and optional sign-bit store.

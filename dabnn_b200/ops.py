@@ -155,6 +155,42 @@ def bconv_block(x_bits, weight, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, 
     return out, bits
 
 
+def binarize_u8(x):
+    """fp32 -> {0,1} bytes, byte = x > 0: the byte-activation engine's counterpart of pack_mat (bitpack.h:277)."""
+    x = _cuda(x, torch.float32)
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    check(capi.load().dabnn_binarize_u8(_ptr(x), _ptr(out), x.numel(), _stream()))
+    return out
+
+
+def bconv_u8_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w):
+    return bool(capi.load().dabnn_bconv_u8_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w))
+
+
+def bconv_u8_expand_weights(weight, cout, kwords):
+    """Packed filters (cout rows of kwords words) -> the byte-activation engine's weight buffer (a uint8 tensor)."""
+    weight = _cuda(weight, torch.int64)
+    buf = torch.empty(capi.load().dabnn_bconv_u8_weight_bytes(cout, kwords), dtype=torch.uint8, device=weight.device)
+    check(capi.load().dabnn_bconv_u8_expand_weights(_ptr(weight), weight.numel(), cout, kwords, _ptr(buf), _stream()))
+    return buf
+
+
+def bconv_u8_block(x_u8, w_expanded, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, a=None, b=None, shortcut=None,
+                   want_f32=True, want_u8=False, want_bits=False):
+    """The fused block of bconv_block on {0,1}-byte activations (see dabnn_bconv_u8_block).  Returns (f32, u8, bits)."""
+    x4 = _cuda(x_u8, torch.uint8)
+    n, h, w, cin = x4.shape
+    oh, ow = out_dim(h, pad_h, 1, kh, stride_h), out_dim(w, pad_w, 1, kw, stride_w)
+    dev = x4.device
+    out = torch.empty((n, oh, ow, cout), dtype=torch.float32, device=dev) if want_f32 else None
+    o8 = torch.empty((n, oh, ow, cout), dtype=torch.uint8, device=dev) if want_u8 else None
+    bits = torch.empty((n, oh, ow, cout // 64), dtype=torch.int64, device=dev) if want_bits else None
+    check(capi.load().dabnn_bconv_u8_block(_ptr(x4), _ptr(w_expanded), _ptr(a), _ptr(b), _ptr(shortcut), _ptr(out), _ptr(o8),
+                                           _ptr(bits), n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w,
+                                           _stream()))
+    return out, o8, bits
+
+
 def affine_(x, a, b):
     """In place x = a[c]*x + b[c]   (reference dabnn/layers/Affine.cpp:10)."""
     c = x.shape[-1]

@@ -147,6 +147,25 @@ int dabnn_bconv_block(const uint64_t* in_bits, const uint64_t* weight, size_t we
                       uint64_t* out_bits, int n, int h, int w, int cw, int cout, int kh, int kw,
                       int pad_h, int pad_w, int stride_h, int stride_w, int engine, dabnn_stream_t s);
 
+/* The same block on activations kept as {0,1} bytes (one byte per channel, NHWC) instead of packed words: the
+ * layout in which a convolution tap is a rectangle that the GPU's copy engine loads straight into the tensor
+ * cores' operand format.  It replaces the same reference sequence as dabnn_bconv_block, with the reference's
+ * pack_mat (bitpack.h:277) becoming dabnn_binarize_u8 (byte = x > 0).  Shapes taken: cin % 64 == 0,
+ * cout % 16 == 0, stride 1 or 2 (equal in both directions; even h and w for 2), output rows of at most 128
+ * pixels; dabnn_bconv_u8_supported tells.  The weights are the reference's packed filters
+ * (cout rows of kh*kw*cin/64 words) expanded once by dabnn_bconv_u8_expand_weights into a buffer of
+ * dabnn_bconv_u8_weight_bytes(cout, kh*kw*cin/64) bytes.  Outputs: any of fp32, {0,1} bytes, packed sign bits. */
+int dabnn_binarize_u8(const float* in, unsigned char* out, size_t count, dabnn_stream_t s);
+int dabnn_bconv_u8_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w,
+                             int stride_h, int stride_w);
+size_t dabnn_bconv_u8_weight_bytes(int cout, int kwords);
+int dabnn_bconv_u8_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int kwords,
+                                  unsigned char* dst, dabnn_stream_t s);
+int dabnn_bconv_u8_block(const unsigned char* in_u8, const unsigned char* w_expanded, const float* a, const float* b,
+                         const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, int n,
+                         int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                         int stride_w, dabnn_stream_t s);
+
 /* reference dabnn/layers/Affine.cpp:10 affine_inplace: x = a[c]*x + b[c] (in place). */
 int dabnn_affine(float* x, const float* a, const float* b, size_t pixels, int c, dabnn_stream_t s);
 /* reference dabnn/layers/Add.cpp:7 add_inplace: x += y. */
