@@ -10,7 +10,7 @@ namespace {
 
 struct U8Plan {
     int OH = 0, OW = 0, rows = 0, imgs = 0, tiles_per_img = 0, ntiles = 0, G = 0, stages = 0, wb = 0, nboxes = 0;
-    int smem = 0;
+    int smem = 0, resident = 0, stiles = 2;
 };
 
 // Shapes the engine takes: whole 64-channel groups, channel counts in 16s, stride 1 or 2 (even H and W), no
@@ -38,11 +38,16 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
     pl.nboxes = kh * kw * (cin / 64);
     pl.wb = u8_weight_rows(cout);
     pl.G = pl.nboxes % 3 == 0 ? 3 : pl.nboxes % 4 == 0 ? 4 : pl.nboxes % 2 == 0 ? 2 : std::min(pl.nboxes, 3);
-    const int stage_bytes = pl.G * (U8_BOX_BYTES + pl.wb * 64);
-    const int avail = U8_MAX_SMEM - 1024 - 2 * U8_STILE_BYTES - 3072 /* static shared memory */;
+    const int res_bytes = pl.nboxes * pl.wb * 64;
+    pl.resident = res_bytes <= 48 * 1024;   // a channel block's weights stay in shared memory
+    // with resident weights the ring carries pixel boxes only and there is room for a third staging tile
+    pl.stiles = pl.resident ? 3 : 2;
+    int avail = U8_MAX_SMEM - 1024 - pl.stiles * U8_STILE_BYTES - 3072 /* static shared memory */;
+    if (pl.resident) avail -= res_bytes;
+    const int stage_bytes = pl.G * (U8_BOX_BYTES + (pl.resident ? 0 : pl.wb * 64));
     pl.stages = std::min(8, avail / stage_bytes);
     if (pl.stages < 2) return false;
-    pl.smem = pl.stages * stage_bytes + 2 * U8_STILE_BYTES + 1024;
+    pl.smem = (pl.resident ? res_bytes : 0) + pl.stages * stage_bytes + pl.stiles * U8_STILE_BYTES + 1024;
     return true;
 }
 
@@ -134,7 +139,7 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     p.B = n; p.OH = pl.OH; p.OW = pl.OW; p.N = cout;
     p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w; p.stride = stride_h; p.cw = cin / 64;
     p.rows = pl.rows; p.imgs = pl.imgs; p.tiles_per_img = pl.tiles_per_img; p.ntiles = pl.ntiles;
-    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes;
+    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles;
     const int tiles_n = (cout + TC5_MAX_N - 1) / TC5_MAX_N;
     const int per_n = std::max(1, sm_count() / tiles_n);
     dim3 grid(std::min(pl.ntiles, per_n), tiles_n);

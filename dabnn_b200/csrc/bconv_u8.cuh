@@ -23,7 +23,9 @@
 // the base address (two tensor maps), so that a tap is still a dense box.
 //
 // Weights: expanded once (bconv_u8_expand_weights_kernel) into per-(channel block, K box) images in the
-// SWIZZLE_NONE K-major core-matrix layout, streamed per stage by one bulk copy.
+// SWIZZLE_NONE K-major core-matrix layout, streamed per stage by one bulk copy - or, when a channel block's
+// weights are small (the 64-channel layers: 45 KB), loaded once per CTA and kept in shared memory, which takes
+// them off the L2 -> shared-memory path that bounds this kernel.
 //
 // Every wait is bounded; a wait that gives up records a code in a status word, raises the CTA's abort flag,
 // and the CTA frees its tensor memory and returns.
@@ -34,11 +36,12 @@ namespace dabnn {
 
 constexpr int U8_BOX_BYTES = 128 * 64;       // one K box of the pixel operand: 128 rows x 64 bytes
 constexpr int U8_ACCS = 3;                   // TMEM accumulators of up to 144 columns
-constexpr int U8_EPI_WARPS = 8;
+constexpr int U8_EPI_WARPS = 16;
 constexpr int U8_EPILOGUE = U8_EPI_WARPS * 32;
 constexpr int U8_THREADS = 64 + U8_EPILOGUE;  // warp 0: loads, warp 1: MMA, then the epilogue warps
 constexpr int U8_SBOX_BYTES = 128 * 128;     // staging box: 128 pixels x 32 channels of fp32, 128-byte-swizzled
-constexpr int U8_STILE_BYTES = 2 * U8_SBOX_BYTES;
+constexpr int U8_STILE_BYTES = 2 * U8_SBOX_BYTES;   // 128 pixels x 64 channels
+constexpr int U8_MAX_STILES = 3;             // staging tiles: one being drained and stored, the others being prefetched
 constexpr int U8_MAX_SMEM = 227 * 1024;
 
 __device__ int g_u8_status;   // 0 = ok; 21 loader, 22 MMA (accumulator), 23 MMA (stage), 24 epilogue
@@ -54,6 +57,8 @@ struct U8Params {
     int kh, kw, pad_h, pad_w, stride, cw;
     int rows, imgs, tiles_per_img, ntiles;
     int G, stages, wb, nboxes;    // K boxes per stage, ring stages, rows of a weight box image, kh*kw*cw
+    int resident;                 // the channel block's weights stay in shared memory (loaded once per CTA)
+    int stiles;                   // staging tiles (2 or 3): the shortcut is prefetched stiles - 1 blocks ahead
 };
 
 __host__ __device__ inline int u8_weight_rows(int N) { return min(N, TC5_MAX_N) + 16; }
@@ -119,10 +124,10 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     bconv_u8_kernel(const U8Params p, const __grid_constant__ CUtensorMap in_map0, const __grid_constant__ CUtensorMap in_map1,
                     const __grid_constant__ CUtensorMap out_map) {
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_acc_full[U8_ACCS], bar_acc_empty[U8_ACCS];
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_acc_full[U8_ACCS], bar_acc_empty[U8_ACCS], bar_w;
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_abort, epi_abort;
-    __shared__ int popw[TC5_MAX_N];
+    __shared__ __align__(16) int popw[TC5_MAX_N];
     __shared__ __align__(16) float chan_a[TC5_MAX_N];
     __shared__ __align__(16) float chan_b[TC5_MAX_N];
 
@@ -130,8 +135,9 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     const int n0 = blockIdx.y * TC5_MAX_N;
     const int n_this = min(TC5_MAX_N, p.N - n0);   // multiple of 16 (host-checked)
     const int n_mma = n_this + 16;                  // + the row of ones
-    const int a_bytes = p.G * U8_BOX_BYTES, wbox_bytes = p.wb * 64, stage_bytes = a_bytes + p.G * wbox_bytes;
-    unsigned char* stage0 = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    const int a_bytes = p.G * U8_BOX_BYTES, wbox_bytes = p.wb * 64, stage_bytes = a_bytes + (p.resident ? 0 : p.G * wbox_bytes);
+    unsigned char* wres = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+    unsigned char* stage0 = wres + (p.resident ? p.nboxes * wbox_bytes : 0);   // a multiple of 1024 bytes further
     const int nst = (p.nboxes + p.G - 1) / p.G;     // stages per tile
     int tmem_cols = 32;
     while (tmem_cols < U8_ACCS * n_mma) tmem_cols <<= 1;
@@ -146,6 +152,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     if (tid == 0) {
         for (int i = 0; i < p.stages; i++) { mbar_init(&bar_full[i], 1); mbar_init(&bar_empty[i], 1); }
         for (int i = 0; i < U8_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], U8_EPI_WARPS); }
+        mbar_init(&bar_w, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
         epi_abort = 0;
@@ -169,6 +176,12 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             const uint32_t box_tx = (uint32_t)box_px * 64u;   // a load always delivers its whole box (zeros outside the tensor)
             uint32_t s = 0, use = 0;
             bool ok = true;
+            if (p.resident) {   // the whole channel block, once
+                const uint32_t bytes = (uint32_t)(p.nboxes * wbox_bytes), bar = smem_u32(&bar_w);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(smem_u32(wres)), "l"(wsrc), "r"(bytes), "r"(bar) : "memory");
+            }
             for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
                 const int tq = tile / p.tiles_per_img;
                 const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
@@ -182,10 +195,11 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     }
                     const int nb = min(p.G, p.nboxes - st * p.G);
                     const uint32_t bar = smem_u32(&bar_full[s]), sa = stage0_addr + s * stage_bytes;
-                    const uint32_t wbytes = (uint32_t)(nb * wbox_bytes);
+                    const uint32_t wbytes = p.resident ? 0u : (uint32_t)(nb * wbox_bytes);
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(wbytes + nb * box_tx) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(sa + a_bytes), "l"(wsrc + (size_t)st * p.G * wbox_bytes), "r"(wbytes), "r"(bar) : "memory");
+                    if (!p.resident)
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(sa + a_bytes), "l"(wsrc + (size_t)st * p.G * wbox_bytes), "r"(wbytes), "r"(bar) : "memory");
                     for (int b = 0; b < nb; b++) {
                         const int dy = ky - p.pad_h, dx = kx - p.pad_w;
                         int c1 = 0, c2 = dx, c3 = oh0 + dy;
@@ -209,9 +223,14 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         if (lane == 0) {
             // instruction descriptor: D = s32, A = u8, B = u8, both K-major, N = n_mma, M = 128
             const uint32_t idesc = (2u << 4) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            const uint64_t d_a = umma_desc_sw64(smem_u32(stage0)), d_b = umma_desc(smem_u32(stage0) + a_bytes, 512);
+            const uint64_t d_a = umma_desc_sw64(smem_u32(stage0));
+            const uint64_t d_b = p.resident ? umma_desc(smem_u32(wres), 512) : umma_desc(smem_u32(stage0) + a_bytes, 512);
+            if (p.resident && !mbar_wait(&bar_w, 0, abort_flag)) {
+                atomicCAS(&g_u8_status, 0, 23);
+                s_abort = 1;
+            }
             uint32_t s = 0, par = 0;
-            bool ok = true;
+            bool ok = !s_abort;
             int i = 0;
             for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, i++) {
                 const int accbuf = i % U8_ACCS, accuse = i / U8_ACCS;
@@ -232,7 +251,8 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const int nb = min(p.G, p.nboxes - st * p.G);
-                    uint64_t ad = d_a + (uint64_t)(s * (stage_bytes >> 4)), bd = d_b + (uint64_t)(s * (stage_bytes >> 4));
+                    uint64_t ad = d_a + (uint64_t)(s * (stage_bytes >> 4));
+                    uint64_t bd = d_b + (uint64_t)(p.resident ? st * p.G * (wbox_bytes >> 4) : s * (stage_bytes >> 4));
                     for (int b = 0; b < nb; b++) {
                         // one MMA per 32 bytes of K: 32 bytes along the swizzled row of A, two 16-byte units (256 bytes) of B
                         mma_i8_ss(d_tmem, ad, bd, idesc, accum);
@@ -249,12 +269,13 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         }
     } else {
         // =========================== epilogue ===========================
-        // Blocks of 64 channels through two fp32 staging tiles: the shortcut of block k+1 is copied into the idle
-        // tile with cp.async while block k is drained (thread (r, h2): 32 accumulator columns of pixel r), then one
-        // TMA tensor store per 32-channel box writes the fp32 result; the {0,1} bytes and the packed sign bits of
-        // the result go straight from registers to global memory.
+        // Blocks of 64 channels through p.stiles fp32 staging tiles: the shortcut of block k + stiles - 1 is copied into
+        // the idle tile with cp.async (one or two blocks ahead: at 60 % of the HBM bandwidth one 32 KB block in flight per
+        // SM does not cover the latency) while block k is drained (thread (r, hq): 16 accumulator columns of pixel r), then one
+        // TMA tensor store per 32-channel box writes the fp32 result; the {0,1} bytes and the packed sign bits of the result go straight from registers to global
+        // memory.
         const int et = tid - 64, ew = warp - 2;
-        const int r = (warp & 3) * 32 + lane, h2 = ew >> 2;   // TMEM lane quarter of a warp = warp % 4
+        const int r = (warp & 3) * 32 + lane, hq = ew >> 2;   // TMEM lane quarter of a warp = warp % 4; column quarter 0..3
         const uint32_t sbuf0_addr = smem_u32(stage0 + p.stages * stage_bytes);
         const int nblk = (n_this + 63) >> 6;
         int my_tiles = 0;
@@ -273,7 +294,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                 const int width = min(64, n_this - cb);
                 long long base; int nvalid;
                 tile_span(tile, base, nvalid);
-                const uint32_t sbase = sbuf0_addr + (kb & 1) * U8_STILE_BYTES;
+                const uint32_t sbase = sbuf0_addr + (kb % p.stiles) * U8_STILE_BYTES;
 #pragma unroll
                 for (int j = 0; j < 2048 / U8_EPILOGUE; j++) {
                     const int it = et + j * U8_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
@@ -284,21 +305,21 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             }
             cp_async_commit();
         };
-        prefetch(0);
+        for (int d = 0; d + 1 < p.stiles; d++) prefetch(d);
         bool okw = true;
         for (int kb = 0; kb < total_blocks; kb++) {
-            const int i = kb / nblk, blk = kb % nblk;
+            const int i = kb / nblk, blk = kb - i * nblk;
             const int tile = blockIdx.x + i * gridDim.x, cb = blk * 64;
             const int width = min(64, n_this - cb);
             const int accbuf = i % U8_ACCS, accuse = i / U8_ACCS;
-            const uint32_t sb = sbuf0_addr + (kb & 1) * U8_STILE_BYTES;
+            const uint32_t sb = sbuf0_addr + (kb % p.stiles) * U8_STILE_BYTES;
             long long base; int nvalid;
             tile_span(tile, base, nvalid);
-            cp_async_wait<0>();                                               // my copies of block kb have landed
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my tensor stores of block kb-1 have read their source
-            asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");    // everybody's have: the other staging tile is idle
-            prefetch(kb + 1);
-            const int ncol = max(0, min(32, width - h2 * 32));               // 0, 16 or 32 columns for this thread
+            if (p.stiles == 3) cp_async_wait<1>(); else cp_async_wait<0>();   // my copies of block kb have landed
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my tensor store of block kb-1 has read its tile
+            asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");    // everybody's have: block kb-1's tile is idle
+            prefetch(kb + p.stiles - 1);
+            const bool mine = width > hq * 16;                               // this thread's 16 columns exist
             if (blk == 0 && okw) {
                 okw = __all_sync(0xffffffffu, mbar_wait<200>(&bar_acc_full[accbuf], accuse & 1, abort_flag));
                 if (!okw) {
@@ -308,53 +329,51 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            if (okw && ncol > 0) {
-                const int c0 = cb + h2 * 32;
+            if (okw && mine) {
+                const int c0 = cb + hq * 16;
                 const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * n_mma;
-                uint32_t v[32], pxu;
+                uint32_t v[16], pxu;
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
                                "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                              : "r"(t_row + c0));
-                if (ncol > 16)
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                 : "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                                 : "r"(t_row + c0 + 16));
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(pxu) : "r"(t_row + n_this));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int px = (int)pxu;
-                const uint32_t srow = sb + h2 * U8_SBOX_BYTES + r * 128;   // chunk q of this row: srow + ((q ^ (r & 7)) << 4)
+                // chunk qq (4 channels) of this pixel's row in box hq / 2: srow + ((qq ^ (r & 7)) << 4)
+                const uint32_t srow = sb + (hq >> 1) * U8_SBOX_BYTES + r * 128;
                 uint32_t signs = 0;   // bit j: channel c0 + j of this pixel is positive
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    if (q * 4 >= ncol) break;
+                for (int q = 0; q < 4; q++) {
+                    const int cl = c0 + q * 4;
+                    const int4 pw = *reinterpret_cast<const int4*>(popw + cl);
                     float o[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const int cl = c0 + q * 4 + e;
-                        float f = small_int_to_float(px + popw[cl] - 2 * (int)v[q * 4 + e]);
-                        if (p.a) f = __fadd_rn(__fmul_rn(chan_a[cl], f), chan_b[cl]);
-                        o[e] = f;
+                    o[0] = small_int_to_float(px + pw.x - 2 * (int)v[q * 4 + 0]);
+                    o[1] = small_int_to_float(px + pw.y - 2 * (int)v[q * 4 + 1]);
+                    o[2] = small_int_to_float(px + pw.z - 2 * (int)v[q * 4 + 2]);
+                    o[3] = small_int_to_float(px + pw.w - 2 * (int)v[q * 4 + 3]);
+                    if (p.a) {
+                        const float4 ca = *reinterpret_cast<const float4*>(chan_a + cl), cbv = *reinterpret_cast<const float4*>(chan_b + cl);
+                        o[0] = __fadd_rn(__fmul_rn(ca.x, o[0]), cbv.x); o[1] = __fadd_rn(__fmul_rn(ca.y, o[1]), cbv.y);
+                        o[2] = __fadd_rn(__fmul_rn(ca.z, o[2]), cbv.z); o[3] = __fadd_rn(__fmul_rn(ca.w, o[3]), cbv.w);
                     }
+                    const uint32_t sa = srow + ((((hq & 1) * 4 + q) ^ (r & 7)) << 4);
                     if (p.shortcut) {
-                        const float4 ad = lds128f(srow + ((q ^ (r & 7)) << 4));
+                        const float4 ad = lds128f(sa);
                         o[0] = __fadd_rn(ad.x, o[0]); o[1] = __fadd_rn(ad.y, o[1]);
                         o[2] = __fadd_rn(ad.z, o[2]); o[3] = __fadd_rn(ad.w, o[3]);
                     }
-                    sts128f(srow + ((q ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
+                    sts128f(sa, o[0], o[1], o[2], o[3]);
                     signs |= ((o[0] > 0.f ? 1u : 0u) | (o[1] > 0.f ? 2u : 0u) | (o[2] > 0.f ? 4u : 0u) | (o[3] > 0.f ? 8u : 0u)) << (q * 4);
                 }
                 if (r < nvalid) {
                     const long long row = base + r;
-                    if (p.out_bits && ncol == 32) reinterpret_cast<uint32_t*>(p.out_bits + row * (p.N >> 6) + ((n0 + cb) >> 6))[h2] = signs;
+                    if (p.out_bits) reinterpret_cast<unsigned short*>(p.out_bits + row * (p.N >> 6) + ((n0 + cb) >> 6))[hq] = (unsigned short)signs;
                     if (p.out_u8) {
-                        uint4* dst = reinterpret_cast<uint4*>(p.out_u8 + row * p.N + n0 + c0);
-                        uint32_t w8[8];
+                        uint32_t w8[4];
 #pragma unroll
-                        for (int q = 0; q < 8; q++) w8[q] = (((signs >> (q * 4)) & 0xfu) * 0x00204081u) & 0x01010101u;
-                        dst[0] = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-                        if (ncol > 16) dst[1] = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                        for (int q = 0; q < 4; q++) w8[q] = (((signs >> (q * 4)) & 0xfu) * 0x00204081u) & 0x01010101u;
+                        *reinterpret_cast<uint4*>(p.out_u8 + row * p.N + n0 + c0) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor store below reads what was just written
@@ -367,15 +386,15 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
             if (epi_abort) break;
             // ---- write-out: one tensor store per 32-channel box; pixels beyond the image / batch and channels beyond N are clipped ----
-            if (p.out && (et == 0 || (et == 128 && width > 32))) {
-                const int hb = et >> 7;
+            if (p.out && (et == 0 || (et == 32 && width > 32))) {
+                const int hb = et >> 5;
                 const int tq = tile / p.tiles_per_img;
                 const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
                              ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + cb + hb * 32), "r"(oh0 * p.OW), "r"(img0),
                                "r"(sb + hb * U8_SBOX_BYTES) : "memory");
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // every thread, every block: group k is block k's store
         }
         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         cp_async_wait<0>();

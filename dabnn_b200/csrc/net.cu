@@ -44,6 +44,7 @@ struct Blob {                // one activation buffer (aliases share a Blob)
     bool keep = false;       // must survive the run (network output / unfused plan)
     bool need_f32 = true;    // some op reads or exposes the float values
     bool need_bits = false;  // some op reads the sign bits
+    bool u8 = false;         // the sign bits are kept as {0,1} bytes (byte-activation engine), not packed words
     size_t f32_off = (size_t)-1, bits_off = (size_t)-1;
     size_t per_image() const { return (size_t)h * w * c; }
 };
@@ -59,6 +60,7 @@ struct Op {
     int relu = 0;
     bool write_f32 = true, write_bits = false;
     const unsigned char* w_expanded = nullptr;   // BConvBlock: the weights in the TCGEN05 engine's stage layout
+    bool u8 = false;                             // BConvBlock: runs on the byte-activation engine (its input blob is u8)
 };
 
 struct Layer {
@@ -153,6 +155,10 @@ struct NetImpl {
     uint64_t* bits(int blob) const {
         const Blob& b = blobs[blob];
         return reinterpret_cast<uint64_t*>(arena + b.bits_off) + (b.keep ? out_offset * b.h * b.w * (b.c / 64) : 0);
+    }
+    unsigned char* bytes(int blob) const {   // the same buffer when the blob keeps its signs as bytes
+        const Blob& b = blobs[blob];
+        return arena + b.bits_off + (b.keep ? out_offset * b.per_image() : 0);
     }
 };
 
@@ -532,6 +538,21 @@ int NetImpl::build() {
         // sign bits: every blob read by a BConvBlock needs bits; let its producer emit them
         for (auto& o : plan)
             if (o.kind == OpKind::BConvBlock) blobs[o.in].need_bits = true;
+        // A blob keeps its signs as {0,1} bytes when every reader is a binary convolution that the byte-activation
+        // engine takes (the Binarize layer exposes packed words, so a blob it reads stays packed).
+        if (engine == DABNN_ENGINE_AUTO || engine == DABNN_ENGINE_TCGEN05) {
+            std::vector<char> can(blobs.size(), 1);
+            for (auto& o : plan) {
+                if (o.kind == OpKind::Pack) can[o.in] = 0;
+                if (o.kind == OpKind::BConvBlock &&
+                    !bconv_u8_supported(max_batch, blobs[o.in].h, blobs[o.in].w, blobs[o.in].c, blobs[o.out].c, o.kh, o.kw,
+                                        o.pad_h, o.pad_w, o.stride_h, o.stride_w))
+                    can[o.in] = 0;
+            }
+            for (size_t i = 0; i < blobs.size(); i++) blobs[i].u8 = blobs[i].need_bits && can[i];
+            for (auto& o : plan)
+                if (o.kind == OpKind::BConvBlock) o.u8 = blobs[o.in].u8;
+        }
         std::vector<Op> with_packs;
         std::vector<char> bits_ready(blobs.size(), 0);
         for (auto& o : plan) {
@@ -552,6 +573,8 @@ int NetImpl::build() {
                         if (seen && q.out == o.out && q.kind != OpKind::Pack) later_writer = true;
                     }
                     emits = !later_writer;
+                    // bytes are written by the byte-activation engine only; any other producer is followed by a Pack
+                    if (blobs[o.out].u8 && !(o.kind == OpKind::BConvBlock && o.u8)) emits = false;
                 }
                 o.write_bits = emits;
                 bits_ready[o.out] = emits;
@@ -586,7 +609,7 @@ int NetImpl::build() {
         const int first = b.keep ? 0 : b.def_op;
         if (i != input_blob) items.push_back({i, false, fbytes, first, last, 0});
         if (b.need_bits) {
-            const size_t bb = ((size_t)max_batch * b.h * b.w * (b.c / 64) * 8 + 255) / 256 * 256;
+            const size_t bb = ((size_t)max_batch * b.h * b.w * (b.u8 ? b.c : b.c / 64 * 8) + 255) / 256 * 256;
             items.push_back({i, true, bb, first, last, 0});
         }
     }
@@ -646,7 +669,8 @@ int NetImpl::build() {
         for (const Op& o : plan) {
             if (o.kind != OpKind::BConvBlock) continue;
             offs.push_back(expanded_bytes);
-            expanded_bytes += bconv_expanded_weight_bytes(blobs[o.out].c, o.kh * o.kw * (blobs[o.in].c / 64));
+            const int kwords = o.kh * o.kw * (blobs[o.in].c / 64);
+            expanded_bytes += ((o.u8 ? bconv_u8_weight_bytes(blobs[o.out].c, kwords) : bconv_expanded_weight_bytes(blobs[o.out].c, kwords)) + 255) / 256 * 256;
         }
         if (expanded_bytes) {
             if (cudaMalloc(&expanded, expanded_bytes) != cudaSuccess) {
@@ -657,8 +681,9 @@ int NetImpl::build() {
             for (Op& o : plan) {
                 if (o.kind != OpKind::BConvBlock) continue;
                 unsigned char* dst = expanded + offs[k++];
-                const int rc = bconv_expand_weights(static_cast<const uint64_t*>(o.w->dev), o.w->count, blobs[o.out].c,
-                                                    o.kh * o.kw * (blobs[o.in].c / 64), dst, stream);
+                const int kwords = o.kh * o.kw * (blobs[o.in].c / 64);
+                const int rc = o.u8 ? bconv_u8_expand_weights(static_cast<const uint64_t*>(o.w->dev), o.w->count, blobs[o.out].c, kwords, dst, stream)
+                                    : bconv_expand_weights(static_cast<const uint64_t*>(o.w->dev), o.w->count, blobs[o.out].c, kwords, dst, stream);
                 if (rc) return rc;
                 o.w_expanded = dst;
             }
@@ -775,10 +800,20 @@ int NetImpl::run_plan(int batch) {
         const size_t pixels_in = (size_t)batch * ib.h * ib.w;
         switch (o.kind) {
             case OpKind::Pack:
-                rc = dabnn_pack_64(f32(o.in), bits(o.in), pixels_in * ib.c, stream);
+                rc = ib.u8 ? binarize_u8_impl(f32(o.in), bytes(o.in), pixels_in * ib.c, stream)
+                           : dabnn_pack_64(f32(o.in), bits(o.in), pixels_in * ib.c, stream);
                 break;
             case OpKind::BConvBlock: {
                 const Blob& ob = blobs[o.out];
+                if (o.u8) {
+                    rc = bconv_u8_block_impl(bytes(o.in), o.w_expanded, o.a ? static_cast<const float*>(o.a->dev) : nullptr,
+                                             o.b ? static_cast<const float*>(o.b->dev) : nullptr,
+                                             o.in2 >= 0 ? f32(o.in2) : nullptr, f32(o.out),
+                                             o.write_bits && ob.u8 ? bytes(o.out) : nullptr,
+                                             o.write_bits && !ob.u8 ? bits(o.out) : nullptr, batch, ib.h, ib.w, ib.c, ob.c, o.kh,
+                                             o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, stream);
+                    break;
+                }
                 rc = bconv_block_impl(bits(o.in), static_cast<const uint64_t*>(o.w->dev), o.w->count,
                                       o.a ? static_cast<const float*>(o.a->dev) : nullptr,
                                       o.b ? static_cast<const float*>(o.b->dev) : nullptr,
