@@ -178,8 +178,8 @@ __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in,
 // L2 -> SM traffic of those loads).  Each output folds its taps in the reference's order (ky, then kx,
 // `acc < t ? t : acc` from -FLT_MAX), so ties between -0 and +0 and NaN inputs resolve identically.
 __global__ void __launch_bounds__(256) maxpool3s2_kernel(const float* __restrict__ in, float* __restrict__ out,
-                                                         uint64_t* __restrict__ bits, int n, int h, int w, int c_vec,
-                                                         int oh, int ow) {
+                                                         uint64_t* __restrict__ bits, unsigned char* __restrict__ out_u8, int n, int h,
+                                                         int w, int c_vec, int oh, int ow) {
     const int bh = (oh + 1) / 2, bw = (ow + 1) / 2;
     const uint32_t total = (uint32_t)n * bh * bw * c_vec;
     const uint32_t bound = (total + 31) / 32 * 32;
@@ -236,13 +236,16 @@ __global__ void __launch_bounds__(256) maxpool3s2_kernel(const float* __restrict
                     const unsigned nib = (a[0] > 0.f ? 1u : 0u) | (a[1] > 0.f ? 2u : 0u) | (a[2] > 0.f ? 4u : 0u) | (a[3] > 0.f ? 8u : 0u);
                     store_sign_word(bits, live ? (pix * c_vec + cc) >> 4 : 0, nib, live);
                 }
+                if (out_u8 && live)   // the signs as {0,1} bytes, four channels per store
+                    reinterpret_cast<uint32_t*>(out_u8)[pix * c_vec + cc] =
+                        (a[0] > 0.f ? 1u : 0u) | (a[1] > 0.f ? 0x100u : 0u) | (a[2] > 0.f ? 0x10000u : 0u) | (a[3] > 0.f ? 0x1000000u : 0u);
             }
     }
 }
 
 template <bool IS_MAX>
 static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h, int w, int c, int kh, int kw,
-                       int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream) {
+                       int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream, unsigned char* out_u8 = nullptr) {
     DABNN_REQUIRE(in && out, DABNN_ERR_ARG, "pool: null pointer");
     DABNN_REQUIRE(n > 0 && h > 0 && w > 0 && c > 0 && kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 &&
                       pad_h >= 0 && pad_w >= 0, DABNN_ERR_ARG, "pool: bad dims");
@@ -254,7 +257,7 @@ static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h
     if (vec && IS_MAX && kh == 3 && kw == 3 && stride_h == 2 && stride_w == 2 && pad_h == 1 && pad_w == 1 &&
         (c / 4) % 16 == 0 && (size_t)n * ((oh + 1) / 2) * ((ow + 1) / 2) * (c / 4) < (1ull << 31)) {
         const size_t blocks = (size_t)n * ((oh + 1) / 2) * ((ow + 1) / 2) * (c / 4);
-        maxpool3s2_kernel<<<grid_for(blocks, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, oh, ow);
+        maxpool3s2_kernel<<<grid_for(blocks, 256), 256, 0, stream>>>(in, out, bits, out_u8, n, h, w, c / 4, oh, ow);
         return check_launch("maxpool3s2_kernel");
     }
     if (vec) {
@@ -274,12 +277,14 @@ static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h
             pool_kernel<1, IS_MAX, size_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, nullptr, n, h, w, c, kh, kw, pad_h,
                                                                                      pad_w, stride_h, stride_w, oh, ow);
     }
-    return check_launch("pool_kernel");
+    const int rc = check_launch("pool_kernel");
+    if (rc || !out_u8) return rc;
+    return binarize_u8_impl(out, out_u8, (size_t)n * oh * ow * c, stream);   // only the 3x3 / 2 kernel writes the bytes itself
 }
 
 int maxpool_impl(const float* in, float* out, uint64_t* out_bits, int n, int h, int w, int c, int kh, int kw,
-                 int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream) {
-    return launch_pool<true>(in, out, out_bits, n, h, w, c, kh, kw, pad_h, pad_w, stride_h, stride_w, stream);
+                 int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream, unsigned char* out_u8) {
+    return launch_pool<true>(in, out, out_bits, n, h, w, c, kh, kw, pad_h, pad_w, stride_h, stride_w, stream, out_u8);
 }
 
 // ---- concat --------------------------------------------------------------------------------------

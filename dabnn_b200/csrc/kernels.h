@@ -57,8 +57,8 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
                int relu, float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
                int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream);
 
-// Max pooling that also emits the sign bits of its output (the first binary conv's input).
+// Max pooling that also emits the signs of its output (the first binary conv's input), packed and / or as bytes.
 int maxpool_impl(const float* in, float* out, uint64_t* out_bits, int n, int h, int w, int c, int kh, int kw,
-                 int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream);
+                 int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream, unsigned char* out_u8 = nullptr);
 
 }  // namespace dabnn

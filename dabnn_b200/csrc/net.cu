@@ -573,8 +573,8 @@ int NetImpl::build() {
                         if (seen && q.out == o.out && q.kind != OpKind::Pack) later_writer = true;
                     }
                     emits = !later_writer;
-                    // bytes are written by the byte-activation engine only; any other producer is followed by a Pack
-                    if (blobs[o.out].u8 && !(o.kind == OpKind::BConvBlock && o.u8)) emits = false;
+                    // bytes are written by the byte-activation engine and the max pool; any other producer is followed by a Pack
+                    if (blobs[o.out].u8 && !((o.kind == OpKind::BConvBlock && o.u8) || o.kind == OpKind::MaxPool)) emits = false;
                 }
                 o.write_bits = emits;
                 bits_ready[o.out] = emits;
@@ -849,8 +849,9 @@ int NetImpl::run_plan(int batch) {
                                  ib.c, stream);
                 break;
             case OpKind::MaxPool:
-                rc = maxpool_impl(f32(o.in), f32(o.out), o.write_bits ? bits(o.out) : nullptr, batch, ib.h, ib.w, ib.c,
-                                  o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, stream);
+                rc = maxpool_impl(f32(o.in), f32(o.out), o.write_bits && !blobs[o.out].u8 ? bits(o.out) : nullptr, batch, ib.h,
+                                  ib.w, ib.c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, stream,
+                                  o.write_bits && blobs[o.out].u8 ? bytes(o.out) : nullptr);
                 break;
             case OpKind::AvePool:
                 rc = dabnn_avepool(f32(o.in), f32(o.out), batch, ib.h, ib.w, ib.c, o.kh, o.kw, o.pad_h, o.pad_w,

@@ -265,6 +265,74 @@ def test_bconv_block_fused_equals_layer_sequence(ops, port, engine, H, cin, cout
     assert torch.equal(b2, b3)
 
 
+# ------------------------------------------------------------------------------------ byte-activation engine
+U8_SHAPES = [  # n, H, W, cin, cout, k, pad, stride
+    (3, 14, 14, 64, 64, 3, 1, 1),      # whole images per tile would not fit: two tiles of 7 rows
+    (5, 7, 7, 128, 128, 3, 1, 1),      # two images per tile, odd batch: the last tile is half empty
+    (2, 56, 56, 64, 64, 3, 1, 1),      # resident weights, 2 rows per tile
+    (2, 28, 28, 128, 256, 3, 1, 2),    # stride 2 (parity view), two channel blocks
+    (2, 15, 13, 64, 48, 3, 1, 1),      # ragged rows per tile, 48 channels (a 16-column tail)
+    (2, 20, 20, 128, 80, 1, 0, 1),     # 1x1, two boxes
+    (1, 9, 9, 64, 192, 5, 2, 1),       # 5x5, channel blocks of 128 + 64
+    (2, 12, 12, 64, 64, 3, 0, 1),      # no padding
+    (2, 16, 16, 64, 64, 2, 0, 2),      # 2x2 stride 2
+]
+
+
+@pytest.mark.parametrize("n,H,W,cin,cout,k,pad,stride", U8_SHAPES)
+def test_bconv_u8_block_equals_layer_sequence(ops, port, n, H, W, cin, cout, k, pad, stride):
+    rng = np.random.default_rng(H * 131 + cout)
+    xf = rng.normal(0, 1, (n, H, W, cin)).astype(np.float32)
+    wf = np.where(rng.random((cout, k, k, cin)) < 0.5, -1.0, 1.0).astype(np.float32)
+    w = port.pack_weight(wf)
+    a = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    b = rng.normal(0, 1, cout).astype(np.float32)
+    oh, ow = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+    sc = rng.normal(0, 1, (n, oh, ow, cout)).astype(np.float32)
+    assert ops.bconv_u8_supported(n, H, W, cin, cout, k, k, pad, pad, stride, stride)
+    x8 = ops.binarize_u8(dev_f32(xf))
+    assert np.array_equal(x8.cpu().numpy(), (xf > 0).astype(np.uint8))
+    kwords = k * k * cin // 64
+    we = ops.bconv_u8_expand_weights(dev_bits(w), cout, kwords)
+    want_bits = cout % 64 == 0
+    f32, o8, bits = ops.bconv_u8_block(x8, we, cout, k, k, pad, pad, stride, stride, dev_f32(a), dev_f32(b), dev_f32(sc),
+                                       want_f32=True, want_u8=True, want_bits=want_bits)
+    raw, _, _ = ops.bconv_u8_block(x8, we, cout, k, k, pad, pad, stride, stride)
+    assert ops.engine_status() == 0
+    for i in range(n):
+        cnt = port.binconv_forward(xf[i], w, cout, k, k, pad, pad, stride, stride)
+        exp = port.add(port.affine(cnt, a, b), sc[i])
+        assert same_bits(host(raw[i]), cnt)                     # BinConv.cpp:144: mismatch counts as fp32
+        assert same_bits(host(f32[i]), exp)
+        assert np.array_equal(o8[i].cpu().numpy(), (exp > 0).astype(np.uint8))
+        if want_bits:
+            assert same_bits(host_bits(bits[i]), port.pack_mat(exp))
+    # the byte output alone equals the byte output of the full form
+    _, o8b, _ = ops.bconv_u8_block(x8, we, cout, k, k, pad, pad, stride, stride, dev_f32(a), dev_f32(b), dev_f32(sc),
+                                   want_f32=False, want_u8=True)
+    assert torch.equal(o8, o8b)
+
+
+def test_binarize_u8_edge_values(ops):
+    vals = np.array([0.0, -0.0, 1e-45, -1e-45, np.inf, -np.inf, np.nan, 1.0, -1.0, 3e-39, -3e-39], dtype=np.float32)
+    x = np.resize(vals, 16 * 5 + 7).astype(np.float32)          # a vector body and a scalar tail
+    got = ops.binarize_u8(dev_f32(x)).cpu().numpy()
+    with np.errstate(invalid="ignore"):
+        assert np.array_equal(got, (x > 0).astype(np.uint8))    # strict >, NaN -> 0 (bitpack.h:29-37)
+
+
+def test_bconv_u8_refuses_other_shapes(ops):
+    assert not ops.bconv_u8_supported(1, 14, 14, 32, 64, 3, 3, 1, 1, 1, 1)      # cin % 64
+    assert not ops.bconv_u8_supported(1, 14, 14, 64, 40, 3, 3, 1, 1, 1, 1)      # cout % 16
+    assert not ops.bconv_u8_supported(1, 15, 15, 64, 64, 3, 3, 1, 1, 2, 2)      # stride 2 needs even h, w
+    assert not ops.bconv_u8_supported(1, 14, 300, 64, 64, 3, 3, 1, 1, 1, 1)     # rows of more than 128 pixels
+    assert not ops.bconv_u8_supported(1, 14, 14, 64, 64, 3, 3, 1, 1, 3, 3)      # stride 3
+    x8 = torch.zeros((1, 14, 14, 32), dtype=torch.uint8, device="cuda")
+    we = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(Exception):
+        ops.bconv_u8_block(x8, we, 64, 3, 3, 1, 1, 1, 1)
+
+
 # ------------------------------------------------------------------------------------ float layers
 def test_float_layers_golden(ops, k):
     x, a, b, other = k["fl_in"], k["fl_a"], k["fl_b"], k["fl_other"][0]
