@@ -6,6 +6,8 @@ batch, for one or more contraction engines.  Prints one JSON line per shape:
 
 raw   = dabnn_bconv on packed bits (fp32 mismatch counts out),
 block = dabnn_bconv_block (counts -> affine -> + shortcut -> fp32 and sign bits out).
+Engine "u8" is the byte-activation engine (dabnn_bconv_u8_block: {0,1}-byte activations in and out,
+weights expanded beforehand); shapes it does not take are reported as null.
 Tbit-op/s counts 2*M*N*K with K the true bits; GB/s counts the block's algorithmic bytes
 (bits in, shortcut in, fp32 + bits out).  Inputs are seeded random words; CUDA-event timing after
 three warm-up calls.
@@ -38,13 +40,15 @@ def timeit(fn, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=256)
-    ap.add_argument("--engines", default="tcgen05")
+    ap.add_argument("--engines", default="tcgen05", help="comma list of popc, b1, imma, tcgen05, u8")
+    ap.add_argument("--shapes", default="", help="comma list of shape indices (default: all)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--movers", action="store_true", help="also time bit-packing, im2col, elementwise and pooling kernels")
     args = ap.parse_args()
     B = args.batch
     g = torch.Generator(device="cuda").manual_seed(0)
-    for (H, cin, cout, ks, s, p) in SHAPES:
+    shapes = [SHAPES[int(i)] for i in args.shapes.split(",")] if args.shapes else SHAPES
+    for (H, cin, cout, ks, s, p) in shapes:
         x = torch.randint(-2**63, 2**63 - 1, (B, H, H, cin // 64), device="cuda", dtype=torch.int64, generator=g)
         w = torch.randint(-2**63, 2**63 - 1, (cout * ks * ks * cin // 64,), device="cuda", dtype=torch.int64, generator=g)
         oh = (H + 2 * p - ks) // s + 1
@@ -53,6 +57,19 @@ def main():
         bitops = 2.0 * B * oh * oh * cout * ks * ks * cin
         row = {"shape": f"{H}x{H}x{cin}->{cout} k{ks} s{s}", "batch": B}
         for e in args.engines.split(","):
+            if e == "u8":
+                if not ops.bconv_u8_supported(B, H, H, cin, cout, ks, ks, p, p, s, s):
+                    row[e] = None
+                    continue
+                x8 = torch.randint(0, 2, (B, H, H, cin), device="cuda", dtype=torch.uint8, generator=g)
+                we = ops.bconv_u8_expand_weights(w, cout, ks * ks * cin // 64)
+                t_raw = timeit(lambda: ops.bconv_u8_block(x8, we, cout, ks, ks, p, p, s, s), args.iters)
+                t_blk = timeit(lambda: ops.bconv_u8_block(x8, we, cout, ks, ks, p, p, s, s, a, b, sc, True, True, False), args.iters)
+                row[e] = {"raw_ms": round(t_raw, 4), "raw_Tbitop_s": round(bitops / t_raw / 1e9, 1),
+                          "block_ms": round(t_blk, 4), "block_Tbitop_s": round(bitops / t_blk / 1e9, 1),
+                          "block_GB_s": round(B * (H * H * cin / 8 + oh * oh * cout * 8.125) / t_blk / 1e6, 1),
+                          "block_moved_GB_s": round(B * (H * H * cin + oh * oh * cout * 9) / t_blk / 1e6, 1)}
+                continue
             t_raw = timeit(lambda: ops.bconv(x, w, cout, ks, ks, p, p, s, s, e), args.iters)
             t_blk = timeit(lambda: ops.bconv_block(x, w, cout, ks, ks, p, p, s, s, a, b, sc, True, True, e), args.iters)
             row[e] = {"raw_ms": round(t_raw, 4), "raw_Tbitop_s": round(bitops / t_raw / 1e9, 1),

@@ -61,13 +61,14 @@ bool make_f32_tensor_map(CUtensorMap_st* map, float* base, int rank, const unsig
 bool make_u8_tensor_map(CUtensorMap_st* map, const unsigned char* base, int rank, const unsigned long long* dims,
                         const unsigned long long* strides_bytes, const unsigned* box) {
     const TensorMapEncode encode = tensor_map_encoder();
-    if (!encode || !base || rank < 2 || rank > 5 || box[0] != 64) return false;
+    if (!encode || !base || rank < 2 || rank > 5 || (box[0] != 64 && box[0] != 128)) return false;
     cuuint64_t d[5], s[4];
     cuuint32_t b[5], e[5] = {1, 1, 1, 1, 1};
     for (int i = 0; i < rank; i++) { d[i] = dims[i]; b[i] = box[i]; }
     for (int i = 0; i + 1 < rank; i++) s[i] = strides_bytes[i];
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<unsigned char*>(base), d, s, b, e,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, box[0] == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

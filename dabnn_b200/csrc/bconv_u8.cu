@@ -10,7 +10,7 @@ namespace {
 
 struct U8Plan {
     int OH = 0, OW = 0, rows = 0, imgs = 0, tiles_per_img = 0, ntiles = 0, G = 0, stages = 0, wb = 0, nboxes = 0;
-    int smem = 0, resident = 0, stiles = 2;
+    int smem = 0, resident = 0, stiles = 2, wide = 0;
 };
 
 // Shapes the engine takes: whole 64-channel groups, channel counts in 16s, stride 1 or 2 (even H and W), no
@@ -38,6 +38,11 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
     pl.nboxes = kh * kw * (cin / 64);
     pl.wb = u8_weight_rows(cout);
     pl.G = pl.nboxes % 3 == 0 ? 3 : pl.nboxes % 4 == 0 ? 4 : pl.nboxes % 2 == 0 ? 2 : std::min(pl.nboxes, 3);
+    // 128 input channels: one load per tap with rows of 128 bytes, a stage is one tap (a pair of boxes).  With more
+    // channels the stage size decides (the kernel is bound by the bytes an SM can take in plus a fixed cost per
+    // stage), and three 64-byte boxes per stage measured faster than two pairs.
+    pl.wide = cin == 128;
+    if (pl.wide) pl.G = 2;
     const int res_bytes = pl.nboxes * pl.wb * 64;
     pl.resident = res_bytes <= 48 * 1024;   // a channel block's weights stay in shared memory
     // with resident weights the ring carries pixel boxes only and there is room for a third staging tile
@@ -54,7 +59,7 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
 // maps[0] / maps[1]: the input seen from even / odd rows (the same map twice for stride 1)
 bool u8_input_maps(const unsigned char* in, int n, int h, int w, int cin, int stride, const U8Plan& pl, CUtensorMap* maps) {
     const unsigned long long C = cin;
-    const unsigned box[5] = {64u, (unsigned)pl.OW, (unsigned)pl.rows, (unsigned)pl.imgs, 1u};
+    const unsigned box[5] = {pl.wide ? 128u : 64u, (unsigned)pl.OW, (unsigned)pl.rows, (unsigned)pl.imgs, 1u};
     if (stride == 1) {
         const unsigned long long dims[5] = {C, (unsigned long long)w, (unsigned long long)h, (unsigned long long)n, 1ull};
         const unsigned long long strides[4] = {C, C * w, C * w * h, C * w * h * n};
@@ -139,7 +144,7 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     p.B = n; p.OH = pl.OH; p.OW = pl.OW; p.N = cout;
     p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w; p.stride = stride_h; p.cw = cin / 64;
     p.rows = pl.rows; p.imgs = pl.imgs; p.tiles_per_img = pl.tiles_per_img; p.ntiles = pl.ntiles;
-    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles;
+    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles; p.wide = pl.wide;
     const int tiles_n = (cout + TC5_MAX_N - 1) / TC5_MAX_N;
     const int per_n = std::max(1, sm_count() / tiles_n);
     dim3 grid(std::min(pl.ntiles, per_n), tiles_n);

@@ -59,6 +59,7 @@ struct U8Params {
     int G, stages, wb, nboxes;    // K boxes per stage, ring stages, rows of a weight box image, kh*kw*cw
     int resident;                 // the channel block's weights stay in shared memory (loaded once per CTA)
     int stiles;                   // staging tiles (2 or 3): the shortcut is prefetched stiles - 1 blocks ahead
+    int wide;                     // cin % 128 == 0: one TMA load covers two K boxes (128-byte rows, SWIZZLE_128B)
 };
 
 __host__ __device__ inline int u8_weight_rows(int N) { return min(N, TC5_MAX_N) + 16; }
@@ -118,6 +119,11 @@ __global__ void __launch_bounds__(256) binarize_u8_kernel(const float* __restric
 __device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)4 << 61);
+}
+// K-major SWIZZLE_128B: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
 }
 
 __global__ void __launch_bounds__(U8_THREADS, 1)
@@ -200,7 +206,8 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     if (!p.resident)
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                                      ::"r"(sa + a_bytes), "l"(wsrc + (size_t)st * p.G * wbox_bytes), "r"(wbytes), "r"(bar) : "memory");
-                    for (int b = 0; b < nb; b++) {
+                    const int bstep = p.wide ? 2 : 1;   // a wide load fills two K boxes (16 KB: 128 rows of 128 bytes)
+                    for (int b = 0; b < nb; b += bstep) {
                         const int dy = ky - p.pad_h, dx = kx - p.pad_w;
                         int c1 = 0, c2 = dx, c3 = oh0 + dy;
                         const CUtensorMap* map = &in_map0;
@@ -212,7 +219,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                         asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
                                      ::"r"(sa + b * U8_BOX_BYTES), "l"(reinterpret_cast<uint64_t>(map)), "r"(cg * 64), "r"(c2), "r"(c3), "r"(img0),
                                        "r"(c1), "r"(bar) : "memory");
-                        if (++cg == p.cw) { cg = 0; if (++kx == p.kw) { kx = 0; ky++; } }
+                        if ((cg += bstep) == p.cw) { cg = 0; if (++kx == p.kw) { kx = 0; ky++; } }
                     }
                     if (++s == (uint32_t)p.stages) { s = 0; use++; }
                 }
@@ -223,7 +230,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         if (lane == 0) {
             // instruction descriptor: D = s32, A = u8, B = u8, both K-major, N = n_mma, M = 128
             const uint32_t idesc = (2u << 4) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            const uint64_t d_a = umma_desc_sw64(smem_u32(stage0));
+            const uint64_t d_a = p.wide ? umma_desc_sw128(smem_u32(stage0)) : umma_desc_sw64(smem_u32(stage0));
             const uint64_t d_b = p.resident ? umma_desc(smem_u32(wres), 512) : umma_desc(smem_u32(stage0) + a_bytes, 512);
             if (p.resident && !mbar_wait(&bar_w, 0, abort_flag)) {
                 atomicCAS(&g_u8_status, 0, 23);
@@ -253,13 +260,26 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     const int nb = min(p.G, p.nboxes - st * p.G);
                     uint64_t ad = d_a + (uint64_t)(s * (stage_bytes >> 4));
                     uint64_t bd = d_b + (uint64_t)(p.resident ? st * p.G * (wbox_bytes >> 4) : s * (stage_bytes >> 4));
-                    for (int b = 0; b < nb; b++) {
-                        // one MMA per 32 bytes of K: 32 bytes along the swizzled row of A, two 16-byte units (256 bytes) of B
-                        mma_i8_ss(d_tmem, ad, bd, idesc, accum);
-                        mma_i8_ss(d_tmem, ad + 2, bd + 16, idesc, 1u);
-                        accum = 1u;
-                        ad += U8_BOX_BYTES >> 4;
-                        bd += (uint64_t)(wbox_bytes >> 4);
+                    // one MMA per 32 bytes of K: 32 bytes along the swizzled row of A, two 16-byte units (256 bytes) of B
+                    if (p.wide) {
+                        for (int b = 0; b < nb; b += 2) {   // a 128-byte row of A holds the K of two weight boxes
+                            mma_i8_ss(d_tmem, ad, bd, idesc, accum);
+                            mma_i8_ss(d_tmem, ad + 2, bd + 16, idesc, 1u);
+                            bd += (uint64_t)(wbox_bytes >> 4);
+                            mma_i8_ss(d_tmem, ad + 4, bd, idesc, 1u);
+                            mma_i8_ss(d_tmem, ad + 6, bd + 16, idesc, 1u);
+                            bd += (uint64_t)(wbox_bytes >> 4);
+                            accum = 1u;
+                            ad += (2 * U8_BOX_BYTES) >> 4;
+                        }
+                    } else {
+                        for (int b = 0; b < nb; b++) {
+                            mma_i8_ss(d_tmem, ad, bd, idesc, accum);
+                            mma_i8_ss(d_tmem, ad + 2, bd + 16, idesc, 1u);
+                            accum = 1u;
+                            ad += U8_BOX_BYTES >> 4;
+                            bd += (uint64_t)(wbox_bytes >> 4);
+                        }
                     }
                     umma_commit(&bar_empty[s]);
                     if (++s == (uint32_t)p.stages) { s = 0; par ^= 1u; }
@@ -282,43 +302,53 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         for (int t = blockIdx.x; t < p.ntiles; t += gridDim.x) my_tiles++;
         const int total_blocks = my_tiles * nblk;
         // first output pixel of a tile and how many of its pixels exist
-        auto tile_span = [&](int tile, long long& base, int& nvalid) {
+        auto tile_span = [&](int tile, long long& base, int& nvalid, int& img0, int& oh0) {
             const int tq = tile / p.tiles_per_img;
-            const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
+            img0 = tq * p.imgs; oh0 = (tile - tq * p.tiles_per_img) * p.rows;
             base = ((long long)img0 * p.OH + oh0) * p.OW;
             nvalid = p.imgs > 1 ? min(p.imgs, p.B - img0) * ohw : min(p.rows, p.OH - oh0) * p.OW;
         };
-        auto prefetch = [&](int kb) {
-            if (p.shortcut && kb < total_blocks) {
-                const int tile = blockIdx.x + (kb / nblk) * gridDim.x, cb = (kb % nblk) * 64;
-                const int width = min(64, n_this - cb);
-                long long base; int nvalid;
-                tile_span(tile, base, nvalid);
-                const uint32_t sbase = sbuf0_addr + (kb % p.stiles) * U8_STILE_BYTES;
+        // Prefetch cursor: the block whose shortcut is copied next, walked incrementally.  A thread copies 16 bytes of
+        // rows pr0, pr0 + 32, ...: its position inside a staging tile and inside a pixel row never changes.
+        const int pr0 = et >> 4, pc4 = (et & 15) * 4;
+        const uint32_t poff = (pc4 >> 5) * U8_SBOX_BYTES + pr0 * 128 + ((((pc4 & 31) >> 2) ^ (pr0 & 7)) << 4);
+        int pkb = 0, ptile = blockIdx.x, pblk = 0, pst = 0, pnvalid = 0, pdummy0, pdummy1;
+        long long pbase = 0;
+        if (ptile < p.ntiles) tile_span(ptile, pbase, pnvalid, pdummy0, pdummy1);
+        auto prefetch_next = [&]() {
+            if (p.shortcut && pkb < total_blocks) {
+                const int cb = pblk * 64;
+                if (pc4 < n_this - cb) {
+                    const float* src = p.shortcut + (pbase + pr0) * p.N + n0 + cb + pc4;
+                    const uint32_t dst = sbuf0_addr + pst * U8_STILE_BYTES + poff;
 #pragma unroll
-                for (int j = 0; j < 2048 / U8_EPILOGUE; j++) {
-                    const int it = et + j * U8_EPILOGUE, rr = it >> 4, c4 = (it & 15) * 4;
-                    if (rr < nvalid && c4 < width)
-                        cp_async16(sbase + (c4 >> 5) * U8_SBOX_BYTES + rr * 128 + ((((c4 & 31) >> 2) ^ (rr & 7)) << 4),
-                                   p.shortcut + (base + rr) * p.N + n0 + cb + c4, 16);
+                    for (int j = 0; j < 2048 / U8_EPILOGUE; j++)
+                        if (pr0 + j * (U8_EPILOGUE / 16) < pnvalid)
+                            cp_async16(dst + j * (U8_EPILOGUE / 16) * 128, src + (long long)j * (U8_EPILOGUE / 16) * p.N, 16);
                 }
             }
             cp_async_commit();
+            pkb++;
+            if (++pst == p.stiles) pst = 0;
+            if (++pblk == nblk) {
+                pblk = 0;
+                ptile += gridDim.x;
+                if (ptile < p.ntiles) tile_span(ptile, pbase, pnvalid, pdummy0, pdummy1);
+            }
         };
-        for (int d = 0; d + 1 < p.stiles; d++) prefetch(d);
+        for (int d = 0; d + 1 < p.stiles; d++) prefetch_next();
         bool okw = true;
+        int tile = blockIdx.x, blk = 0, st_idx = 0, accbuf = 0, accuse = 0, nvalid = 0, img0 = 0, oh0 = 0;
+        long long base = 0;
         for (int kb = 0; kb < total_blocks; kb++) {
-            const int i = kb / nblk, blk = kb - i * nblk;
-            const int tile = blockIdx.x + i * gridDim.x, cb = blk * 64;
+            if (blk == 0) tile_span(tile, base, nvalid, img0, oh0);
+            const int cb = blk * 64;
             const int width = min(64, n_this - cb);
-            const int accbuf = i % U8_ACCS, accuse = i / U8_ACCS;
-            const uint32_t sb = sbuf0_addr + (kb % p.stiles) * U8_STILE_BYTES;
-            long long base; int nvalid;
-            tile_span(tile, base, nvalid);
+            const uint32_t sb = sbuf0_addr + st_idx * U8_STILE_BYTES;
             if (p.stiles == 3) cp_async_wait<1>(); else cp_async_wait<0>();   // my copies of block kb have landed
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my tensor store of block kb-1 has read its tile
             asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");    // everybody's have: block kb-1's tile is idle
-            prefetch(kb + p.stiles - 1);
+            prefetch_next();
             const bool mine = width > hq * 16;                               // this thread's 16 columns exist
             if (blk == 0 && okw) {
                 okw = __all_sync(0xffffffffu, mbar_wait<200>(&bar_acc_full[accbuf], accuse & 1, abort_flag));
@@ -388,13 +418,17 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             // ---- write-out: one tensor store per 32-channel box; pixels beyond the image / batch and channels beyond N are clipped ----
             if (p.out && (et == 0 || (et == 32 && width > 32))) {
                 const int hb = et >> 5;
-                const int tq = tile / p.tiles_per_img;
-                const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
                              ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + cb + hb * 32), "r"(oh0 * p.OW), "r"(img0),
                                "r"(sb + hb * U8_SBOX_BYTES) : "memory");
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // every thread, every block: group k is block k's store
+            if (++st_idx == p.stiles) st_idx = 0;
+            if (++blk == nblk) {
+                blk = 0;
+                tile += gridDim.x;
+                if (++accbuf == U8_ACCS) { accbuf = 0; accuse++; }
+            }
         }
         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         cp_async_wait<0>();

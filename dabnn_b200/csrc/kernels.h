@@ -16,8 +16,9 @@ namespace dabnn {
 bool make_f32_tensor_map(CUtensorMap_st* map, float* base, int rank, const unsigned long long* dims,
                          const unsigned long long* strides_bytes, const unsigned* box);
 
-// The same for a tensor of bytes, up to five dimensions, inner box 64 bytes, 64-byte-swizzled (the layout a
-// K-major SWIZZLE_64B shared-memory descriptor of tcgen05.mma reads); elements outside the tensor read as zero.
+// The same for a tensor of bytes, up to five dimensions, inner box 64 or 128 bytes, swizzled over that width (the
+// layout a K-major SWIZZLE_64B / SWIZZLE_128B shared-memory descriptor of tcgen05.mma reads); elements outside the
+// tensor read as zero.
 bool make_u8_tensor_map(CUtensorMap_st* map, const unsigned char* base, int rank, const unsigned long long* dims,
                         const unsigned long long* strides_bytes, const unsigned* box);
 
