@@ -266,7 +266,9 @@ def run_ours(args):
                     "traffic": traffic.get(top, {}).get("bytes_per_image", 0) * B or None}
         else:
             gbps = alg[top] / (classes[top] * 1e-3) / 1e9
-            names = {"Bin Conv block": f"bcontract_tc5_kernel / bcontract_kernel<{eng}> (16 fused binary conv blocks)"}
+            blk = ("bconv_u8_kernel (16 fused binary conv blocks: {0,1}-byte activations loaded by TMA into tcgen05.mma kind::i8)"
+                   if eng == "tcgen05" else f"bcontract_kernel<{eng}> (16 fused binary conv blocks)")
+            names = {"Bin Conv block": blk}
             roof = {"bound": "hbm", "kernel": names.get(top, top), "achieved": round(gbps, 1), "peak": hbm_gbs, "unit": "GB/s",
                     "frac": round(gbps / hbm_gbs, 4), "peak_source": peak_src,
                     "traffic": traffic.get(top, {}).get("bytes_per_image", 0) * B or None}
@@ -274,7 +276,7 @@ def run_ours(args):
             "metric": "Bi-Real-18-shape images/s", "value": round(world * B * args.steps / (ms_dev * 1e-3), 1),
             "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_dev / args.steps, 4), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "b1 x b1 -> s32 (tcgen05 kind::i8 on bits expanded in shared memory) + fp32 (3xTF32)",
+            "vs_baseline": None, "dtype": "b1 x b1 -> s32 (tcgen05 kind::i8 on bits held as {0,1} bytes) + fp32 (3xTF32)",
             "data": "synthetic",
             "config": {"workload": f"Bi-Real-Net-18-shaped BNN, 224x224x3 fp32 N(0,1) inputs, random-init, batch {B} per GPU, "
                                    "independent replicas",
