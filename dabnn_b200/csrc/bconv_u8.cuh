@@ -11,10 +11,11 @@
 // layout tcgen05.mma reads.  Zero fill outside the image is the reference's padding (bit 0).  No thread touches
 // the operand: one lane issues the loads, one lane issues the MMAs, the other warps are the epilogue.
 //
-//   cnt[p][n] = popc(x[p]) + popc(w[n]) - 2 * sum_k a[p][k] * b[n][k]
+//   cnt[p][n] = sum_k a_k xor b_k = sum_k a_k * (1 - 2 b_k) + sum_k b_k
 //
-// popc(x[p]) (over the zero-padded window) comes out of the same MMA: the weight image of every channel block
-// carries one extra row of ones, so accumulator column n_this is the row popcount.
+// with a the activation bits as unsigned bytes {0,1} and the weights stored as signed bytes 1 - 2b = {+1,-1}: the
+// MMA (unsigned x signed 8-bit, s32 accumulators) yields the first sum and the epilogue adds the weight row's
+// popcount.  A zero-filled tap contributes b_k, the reference's count for a padded position.
 //
 // Tiles: OW <= 128.  If an image has more than 128 output pixels a tile is `rows` whole output rows of one image
 // (rows * OW <= 128), else `imgs` whole images.  The M = 128 rows of the MMA beyond the tile's pixels hold stale
@@ -35,7 +36,7 @@
 namespace dabnn {
 
 constexpr int U8_BOX_BYTES = 128 * 64;       // one K box of the pixel operand: 128 rows x 64 bytes
-constexpr int U8_ACCS = 3;                   // TMEM accumulators of up to 144 columns
+constexpr int U8_ACCS = 4;                   // TMEM accumulators of up to 128 columns
 constexpr int U8_EPI_WARPS = 16;
 constexpr int U8_EPILOGUE = U8_EPI_WARPS * 32;
 constexpr int U8_THREADS = 64 + U8_EPILOGUE;  // warp 0: loads, warp 1: MMA, then the epilogue warps
@@ -62,7 +63,7 @@ struct U8Params {
     int wide;                     // cin % 128 == 0: one TMA load covers two K boxes (128-byte rows, SWIZZLE_128B)
 };
 
-__host__ __device__ inline int u8_weight_rows(int N) { return min(N, TC5_MAX_N) + 16; }
+__host__ __device__ inline int u8_weight_rows(int N) { return min(N, TC5_MAX_N); }
 __host__ __device__ inline size_t u8_weight_image_bytes(int N, int nboxes) {
     return (size_t)((N + TC5_MAX_N - 1) / TC5_MAX_N) * nboxes * u8_weight_rows(N) * 64;
 }
@@ -71,8 +72,8 @@ __host__ __device__ inline size_t u8_weight_bytes(int N, int nboxes) {
 }
 
 // grid (nboxes, channel blocks): the image of K box q (= packed word q) of one channel block: wb rows x 64 bytes,
-// byte k of row n = bit k of the word, stored as 8-row x 16-byte core matrices ([row / 8][k / 16][row % 8][k % 16]).
-// Row n_this is all ones (it yields the pixel rows' popcounts), the rows after it are zero.
+// byte k of row n = 1 - 2 * bit k of the word (+1 or -1 as a signed byte), stored as 8-row x 16-byte core matrices
+// ([row / 8][k / 16][row % 8][k % 16]); rows beyond the channel block are zero.
 __global__ void __launch_bounds__(256) bconv_u8_expand_weights_kernel(const uint64_t* w, const long long ldw, const int N,
                                                                       const int nboxes, unsigned char* dst) {
     const int q = blockIdx.x, nb = blockIdx.y, wb = u8_weight_rows(N);
@@ -80,14 +81,16 @@ __global__ void __launch_bounds__(256) bconv_u8_expand_weights_kernel(const uint
     unsigned char* img = dst + ((size_t)nb * nboxes + q) * wb * 64;
     for (int idx = threadIdx.x; idx < wb * 4; idx += blockDim.x) {
         const int row = idx >> 2, unit = idx & 3;
-        uint32_t bits = 0;
-        if (row < n_this) bits = (uint32_t)(__ldg(w + (long long)(n0 + row) * ldw + q) >> (unit * 16)) & 0xffffu;
-        else if (row == n_this) bits = 0xffffu;
-        uint4 v;
-        v.x = ((bits & 0xfu) * 0x00204081u) & 0x01010101u;
-        v.y = (((bits >> 4) & 0xfu) * 0x00204081u) & 0x01010101u;
-        v.z = (((bits >> 8) & 0xfu) * 0x00204081u) & 0x01010101u;
-        v.w = (((bits >> 12) & 0xfu) * 0x00204081u) & 0x01010101u;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_this) {
+            const uint32_t bits = (uint32_t)(__ldg(w + (long long)(n0 + row) * ldw + q) >> (unit * 16)) & 0xffffu;
+            auto signed_bytes = [](uint32_t nibble) {   // four bits -> four bytes, 0 -> 0x01, 1 -> 0xff
+                const uint32_t m = (nibble * 0x00204081u) & 0x01010101u;
+                return (m * 0xffu) | (m ^ 0x01010101u);
+            };
+            v.x = signed_bytes(bits & 0xfu); v.y = signed_bytes((bits >> 4) & 0xfu);
+            v.z = signed_bytes((bits >> 8) & 0xfu); v.w = signed_bytes((bits >> 12) & 0xfu);
+        }
         *reinterpret_cast<uint4*>(img + (row >> 3) * 512 + unit * 128 + (row & 7) * 16) = v;
     }
     if (q == 0 && threadIdx.x < TC5_MAX_N) {
@@ -140,7 +143,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.y * TC5_MAX_N;
     const int n_this = min(TC5_MAX_N, p.N - n0);   // multiple of 16 (host-checked)
-    const int n_mma = n_this + 16;                  // + the row of ones
+    const int n_mma = n_this;
     const int a_bytes = p.G * U8_BOX_BYTES, wbox_bytes = p.wb * 64, stage_bytes = a_bytes + (p.resident ? 0 : p.G * wbox_bytes);
     unsigned char* wres = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* stage0 = wres + (p.resident ? p.nboxes * wbox_bytes : 0);   // a multiple of 1024 bytes further
@@ -228,8 +231,8 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     } else if (warp == 1) {
         // =========================== MMA issue: one lane ===========================
         if (lane == 0) {
-            // instruction descriptor: D = s32, A = u8, B = u8, both K-major, N = n_mma, M = 128
-            const uint32_t idesc = (2u << 4) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            // instruction descriptor: D = s32, A = u8, B = s8, both K-major, N = n_mma, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 10) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             const uint64_t d_a = p.wide ? umma_desc_sw128(smem_u32(stage0)) : umma_desc_sw64(smem_u32(stage0));
             const uint64_t d_b = p.resident ? umma_desc(smem_u32(wres), 512) : umma_desc(smem_u32(stage0) + a_bytes, 512);
             if (p.resident && !mbar_wait(&bar_w, 0, abort_flag)) {
@@ -362,14 +365,12 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             if (okw && mine) {
                 const int c0 = cb + hq * 16;
                 const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * n_mma;
-                uint32_t v[16], pxu;
+                uint32_t v[16];
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
                                "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                              : "r"(t_row + c0));
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(pxu) : "r"(t_row + n_this));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int px = (int)pxu;
                 // chunk qq (4 channels) of this pixel's row in box hq / 2: srow + ((qq ^ (r & 7)) << 4)
                 const uint32_t srow = sb + (hq >> 1) * U8_SBOX_BYTES + r * 128;
                 uint32_t signs = 0;   // bit j: channel c0 + j of this pixel is positive
@@ -378,10 +379,10 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     const int cl = c0 + q * 4;
                     const int4 pw = *reinterpret_cast<const int4*>(popw + cl);
                     float o[4];
-                    o[0] = small_int_to_float(px + pw.x - 2 * (int)v[q * 4 + 0]);
-                    o[1] = small_int_to_float(px + pw.y - 2 * (int)v[q * 4 + 1]);
-                    o[2] = small_int_to_float(px + pw.z - 2 * (int)v[q * 4 + 2]);
-                    o[3] = small_int_to_float(px + pw.w - 2 * (int)v[q * 4 + 3]);
+                    o[0] = small_int_to_float(pw.x + (int)v[q * 4 + 0]);
+                    o[1] = small_int_to_float(pw.y + (int)v[q * 4 + 1]);
+                    o[2] = small_int_to_float(pw.z + (int)v[q * 4 + 2]);
+                    o[3] = small_int_to_float(pw.w + (int)v[q * 4 + 3]);
                     if (p.a) {
                         const float4 ca = *reinterpret_cast<const float4*>(chan_a + cl), cbv = *reinterpret_cast<const float4*>(chan_b + cl);
                         o[0] = __fadd_rn(__fmul_rn(ca.x, o[0]), cbv.x); o[1] = __fadd_rn(__fmul_rn(ca.y, o[1]), cbv.y);
