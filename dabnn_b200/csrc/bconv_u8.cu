@@ -10,7 +10,7 @@ namespace {
 
 struct U8Plan {
     int OH = 0, OW = 0, rows = 0, imgs = 0, tiles_per_img = 0, ntiles = 0, G = 0, stages = 0, wb = 0, nboxes = 0;
-    int smem = 0, resident = 0, stiles = 2, wide = 0;
+    int smem = 0, resident = 0, stiles = 2, wide = 0, pair = 0;
 };
 
 // Shapes the engine takes: whole 64-channel groups, channel counts in 16s, stride 1 or 2 (even H and W), no
@@ -49,7 +49,16 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
     pl.stiles = pl.resident ? 3 : 2;
     int avail = U8_MAX_SMEM - 1024 - pl.stiles * U8_STILE_BYTES - 3072 /* static shared memory */;
     if (pl.resident) avail -= res_bytes;
-    const int stage_bytes = pl.G * (U8_BOX_BYTES + (pl.resident ? 0 : pl.wb * 64));
+    // Streamed weights: two pixel tiles per weight stage (a stage is then two boxes of each tile and of the weights),
+    // where handing out tiles in pairs does not lengthen the longest CTA's share (a few per cent per tile; a whole
+    // extra tile would cost more).
+    {
+        const int ctas = std::max(1, sm_count() / ((cout + TC5_MAX_N - 1) / TC5_MAX_N));
+        const int units = (pl.ntiles + 1) / 2;
+        pl.pair = !pl.resident && pl.nboxes % 2 == 0 && 2 * ((units + ctas - 1) / ctas) <= (pl.ntiles + ctas - 1) / ctas;
+    }
+    if (pl.pair) pl.G = 2;
+    const int stage_bytes = pl.G * ((pl.pair ? 2 : 1) * U8_BOX_BYTES + (pl.resident ? 0 : pl.wb * 64));
     pl.stages = std::min(8, avail / stage_bytes);
     if (pl.stages < 2) return false;
     pl.smem = (pl.resident ? res_bytes : 0) + pl.stages * stage_bytes + pl.stiles * U8_STILE_BYTES + 1024;
@@ -127,7 +136,8 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     int dev = 0;
     DABNN_CUDA_OK(cudaGetDevice(&dev));
     if (configured_device != dev) {
-        DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_u8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
+        DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_u8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
+        DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_u8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
         configured_device = dev;
     }
     CUtensorMap in_maps[2], out_map{};
@@ -144,11 +154,13 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     p.B = n; p.OH = pl.OH; p.OW = pl.OW; p.N = cout;
     p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w; p.stride = stride_h; p.cw = cin / 64;
     p.rows = pl.rows; p.imgs = pl.imgs; p.tiles_per_img = pl.tiles_per_img; p.ntiles = pl.ntiles;
-    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles; p.wide = pl.wide;
+    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles; p.wide = pl.wide; p.pair = pl.pair;
     const int tiles_n = (cout + TC5_MAX_N - 1) / TC5_MAX_N;
     const int per_n = std::max(1, sm_count() / tiles_n);
-    dim3 grid(std::min(pl.ntiles, per_n), tiles_n);
-    bconv_u8_kernel<<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
+    const int nunits = pl.pair ? (pl.ntiles + 1) / 2 : pl.ntiles;
+    dim3 grid(std::min(nunits, per_n), tiles_n);
+    if (pl.pair) bconv_u8_kernel<true><<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
+    else bconv_u8_kernel<false><<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
     return check_launch("bconv_u8_kernel");
 }
 

@@ -23,6 +23,9 @@
 // column parity): stride 1 uses parity 0 only; stride 2 views W as (W / 2, parity) and folds the row parity into
 // the base address (two tensor maps), so that a tap is still a dense box.
 //
+// Where the weights are streamed, a unit of work is a pair of pixel tiles (M = 2 x 128) that share every weight
+// stage, each with its own accumulator: half the weight bytes per MMA.
+//
 // Weights: expanded once (bconv_u8_expand_weights_kernel) into per-(channel block, K box) images in the
 // SWIZZLE_NONE K-major core-matrix layout, streamed per stage by one bulk copy - or, when a channel block's
 // weights are small (the 64-channel layers: 45 KB), loaded once per CTA and kept in shared memory, which takes
@@ -61,6 +64,7 @@ struct U8Params {
     int resident;                 // the channel block's weights stay in shared memory (loaded once per CTA)
     int stiles;                   // staging tiles (2 or 3): the shortcut is prefetched stiles - 1 blocks ahead
     int wide;                     // cin % 128 == 0: one TMA load covers two K boxes (128-byte rows, SWIZZLE_128B)
+    int pair;                     // two pixel tiles share every weight stage (streamed weights: halves their bytes)
 };
 
 __host__ __device__ inline int u8_weight_rows(int N) { return min(N, TC5_MAX_N); }
@@ -129,6 +133,7 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
            ((uint64_t)2 << 61);
 }
 
+template <bool PAIR>   // PAIR: a unit of work is two pixel tiles sharing the weight stages (p.pair)
 __global__ void __launch_bounds__(U8_THREADS, 1)
     bconv_u8_kernel(const U8Params p, const __grid_constant__ CUtensorMap in_map0, const __grid_constant__ CUtensorMap in_map1,
                     const __grid_constant__ CUtensorMap out_map) {
@@ -144,7 +149,10 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     const int n0 = blockIdx.y * TC5_MAX_N;
     const int n_this = min(TC5_MAX_N, p.N - n0);   // multiple of 16 (host-checked)
     const int n_mma = n_this;
-    const int a_bytes = p.G * U8_BOX_BYTES, wbox_bytes = p.wb * 64, stage_bytes = a_bytes + (p.resident ? 0 : p.G * wbox_bytes);
+    constexpr int np = PAIR ? 2 : 1;                // pixel tiles per unit of work (they share the unit's weight stages)
+    const int nunits = (p.ntiles + np - 1) / np;
+    const int a_bytes1 = p.G * U8_BOX_BYTES, a_bytes = np * a_bytes1;   // one tile's boxes of a stage, all of them
+    const int wbox_bytes = p.wb * 64, stage_bytes = a_bytes + (p.resident ? 0 : p.G * wbox_bytes);
     unsigned char* wres = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* stage0 = wres + (p.resident ? p.nboxes * wbox_bytes : 0);   // a multiple of 1024 bytes further
     const int nst = (p.nboxes + p.G - 1) / p.G;     // stages per tile
@@ -191,9 +199,12 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(smem_u32(wres)), "l"(wsrc), "r"(bytes), "r"(bar) : "memory");
             }
-            for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
-                const int tq = tile / p.tiles_per_img;
-                const int img0 = tq * p.imgs, oh0 = (tile - tq * p.tiles_per_img) * p.rows;
+            for (int unit = blockIdx.x; unit < nunits && ok; unit += gridDim.x) {
+                int img0[2], oh0[2];   // a tile past the last one lies outside the tensor: its loads deliver zeros
+                for (int t = 0; t < np; t++) {
+                    const int tile = unit * np + t, tq = tile / p.tiles_per_img;
+                    img0[t] = tq * p.imgs; oh0[t] = (tile - tq * p.tiles_per_img) * p.rows;
+                }
                 int cg = 0, ky = 0, kx = 0;
                 for (int st = 0; st < nst; st++) {
                     if (use >= 1 && !mbar_wait<32>(&bar_empty[s], (use - 1) & 1, abort_flag)) {
@@ -205,23 +216,24 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     const int nb = min(p.G, p.nboxes - st * p.G);
                     const uint32_t bar = smem_u32(&bar_full[s]), sa = stage0_addr + s * stage_bytes;
                     const uint32_t wbytes = p.resident ? 0u : (uint32_t)(nb * wbox_bytes);
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(wbytes + nb * box_tx) : "memory");
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(wbytes + np * nb * box_tx) : "memory");
                     if (!p.resident)
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                                      ::"r"(sa + a_bytes), "l"(wsrc + (size_t)st * p.G * wbox_bytes), "r"(wbytes), "r"(bar) : "memory");
                     const int bstep = p.wide ? 2 : 1;   // a wide load fills two K boxes (16 KB: 128 rows of 128 bytes)
                     for (int b = 0; b < nb; b += bstep) {
                         const int dy = ky - p.pad_h, dx = kx - p.pad_w;
-                        int c1 = 0, c2 = dx, c3 = oh0 + dy;
+                        int c1 = 0, c2 = dx, c3 = dy;
                         const CUtensorMap* map = &in_map0;
                         if (p.stride == 2) {
                             const int hp = dy & 1, wp = dx & 1;
-                            c1 = wp; c2 = (dx - wp) >> 1; c3 = oh0 + ((dy - hp) >> 1);
+                            c1 = wp; c2 = (dx - wp) >> 1; c3 = (dy - hp) >> 1;
                             if (hp) map = &in_map1;
                         }
-                        asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-                                     ::"r"(sa + b * U8_BOX_BYTES), "l"(reinterpret_cast<uint64_t>(map)), "r"(cg * 64), "r"(c2), "r"(c3), "r"(img0),
-                                       "r"(c1), "r"(bar) : "memory");
+                        for (int t = 0; t < np; t++)
+                            asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                                         ::"r"(sa + t * a_bytes1 + b * U8_BOX_BYTES), "l"(reinterpret_cast<uint64_t>(map)), "r"(cg * 64), "r"(c2),
+                                           "r"(oh0[t] + c3), "r"(img0[t]), "r"(c1), "r"(bar) : "memory");
                         if ((cg += bstep) == p.cw) { cg = 0; if (++kx == p.kw) { kx = 0; ky++; } }
                     }
                     if (++s == (uint32_t)p.stages) { s = 0; use++; }
@@ -241,16 +253,20 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             }
             uint32_t s = 0, par = 0;
             bool ok = !s_abort;
-            int i = 0;
-            for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, i++) {
-                const int accbuf = i % U8_ACCS, accuse = i / U8_ACCS;
-                if (accuse >= 1 && !mbar_wait(&bar_acc_empty[accbuf], (accuse - 1) & 1, abort_flag)) {
-                    atomicCAS(&g_u8_status, 0, 22);
-                    s_abort = 1;
-                    break;
+            int i = 0;   // tiles so far: tile i accumulates in accumulator i % U8_ACCS
+            for (int unit = blockIdx.x; unit < nunits && ok; unit += gridDim.x, i += np) {
+                for (int t = 0; t < np && ok; t++) {
+                    const int accbuf = (i + t) % U8_ACCS, accuse = (i + t) / U8_ACCS;
+                    if (accuse >= 1 && !mbar_wait(&bar_acc_empty[accbuf], (accuse - 1) & 1, abort_flag)) {
+                        atomicCAS(&g_u8_status, 0, 22);
+                        s_abort = 1;
+                        ok = false;
+                    }
                 }
+                if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_tmem = tmem_base + accbuf * n_mma;
+                const uint32_t d_tmem = tmem_base + (i % U8_ACCS) * n_mma;   // the pair's second accumulator follows the first
+                const uint32_t a_step = (uint32_t)(a_bytes1 >> 4);
                 uint32_t accum = 0;
                 for (int st = 0; st < nst; st++) {
                     if (!mbar_wait(&bar_full[s], par, abort_flag)) {
@@ -266,19 +282,25 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     // one MMA per 32 bytes of K: 32 bytes along the swizzled row of A, two 16-byte units (256 bytes) of B
                     if (p.wide) {
                         for (int b = 0; b < nb; b += 2) {   // a 128-byte row of A holds the K of two weight boxes
-                            mma_i8_ss(d_tmem, ad, bd, idesc, accum);
-                            mma_i8_ss(d_tmem, ad + 2, bd + 16, idesc, 1u);
-                            bd += (uint64_t)(wbox_bytes >> 4);
-                            mma_i8_ss(d_tmem, ad + 4, bd, idesc, 1u);
-                            mma_i8_ss(d_tmem, ad + 6, bd + 16, idesc, 1u);
-                            bd += (uint64_t)(wbox_bytes >> 4);
+                            const uint64_t bd2 = bd + (uint64_t)(wbox_bytes >> 4);
+                            for (int t = 0; t < np; t++) {
+                                const uint64_t at = ad + t * a_step;
+                                mma_i8_ss(d_tmem + t * n_mma, at, bd, idesc, accum);
+                                mma_i8_ss(d_tmem + t * n_mma, at + 2, bd + 16, idesc, 1u);
+                                mma_i8_ss(d_tmem + t * n_mma, at + 4, bd2, idesc, 1u);
+                                mma_i8_ss(d_tmem + t * n_mma, at + 6, bd2 + 16, idesc, 1u);
+                            }
+                            bd = bd2 + (uint64_t)(wbox_bytes >> 4);
                             accum = 1u;
                             ad += (2 * U8_BOX_BYTES) >> 4;
                         }
                     } else {
                         for (int b = 0; b < nb; b++) {
-                            mma_i8_ss(d_tmem, ad, bd, idesc, accum);
-                            mma_i8_ss(d_tmem, ad + 2, bd + 16, idesc, 1u);
+                            for (int t = 0; t < np; t++) {
+                                const uint64_t at = ad + t * a_step;
+                                mma_i8_ss(d_tmem + t * n_mma, at, bd, idesc, accum);
+                                mma_i8_ss(d_tmem + t * n_mma, at + 2, bd + 16, idesc, 1u);
+                            }
                             accum = 1u;
                             ad += U8_BOX_BYTES >> 4;
                             bd += (uint64_t)(wbox_bytes >> 4);
@@ -287,7 +309,8 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     umma_commit(&bar_empty[s]);
                     if (++s == (uint32_t)p.stages) { s = 0; par ^= 1u; }
                 }
-                if (ok) umma_commit(&bar_acc_full[accbuf]);
+                if (ok)
+                    for (int t = 0; t < np; t++) umma_commit(&bar_acc_full[(i + t) % U8_ACCS]);
             }
         }
     } else {
@@ -301,8 +324,13 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         const int r = (warp & 3) * 32 + lane, hq = ew >> 2;   // TMEM lane quarter of a warp = warp % 4; column quarter 0..3
         const uint32_t sbuf0_addr = smem_u32(stage0 + p.stages * stage_bytes);
         const int nblk = (n_this + 63) >> 6;
+        // This CTA's tiles in order: unit u = blockIdx.x + j * gridDim.x holds tiles u * np .. u * np + np - 1.
+        const int first_tile = blockIdx.x * np;
+        auto next_tile = [&](int tile, int index) {   // the tile after `tile`, which is this CTA's tile number `index`
+            return np == 1 ? tile + (int)gridDim.x : ((index & 1) ? tile + 2 * (int)gridDim.x - 1 : tile + 1);
+        };
         int my_tiles = 0;
-        for (int t = blockIdx.x; t < p.ntiles; t += gridDim.x) my_tiles++;
+        for (int t = first_tile, k = 0; t < p.ntiles; t = next_tile(t, k++)) my_tiles++;
         const int total_blocks = my_tiles * nblk;
         // first output pixel of a tile and how many of its pixels exist
         auto tile_span = [&](int tile, long long& base, int& nvalid, int& img0, int& oh0) {
@@ -315,7 +343,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         // rows pr0, pr0 + 32, ...: its position inside a staging tile and inside a pixel row never changes.
         const int pr0 = et >> 4, pc4 = (et & 15) * 4;
         const uint32_t poff = (pc4 >> 5) * U8_SBOX_BYTES + pr0 * 128 + ((((pc4 & 31) >> 2) ^ (pr0 & 7)) << 4);
-        int pkb = 0, ptile = blockIdx.x, pblk = 0, pst = 0, pnvalid = 0, pdummy0, pdummy1;
+        int pkb = 0, ptile = first_tile, pti = 0, pblk = 0, pst = 0, pnvalid = 0, pdummy0, pdummy1;
         long long pbase = 0;
         if (ptile < p.ntiles) tile_span(ptile, pbase, pnvalid, pdummy0, pdummy1);
         auto prefetch_next = [&]() {
@@ -335,13 +363,13 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             if (++pst == p.stiles) pst = 0;
             if (++pblk == nblk) {
                 pblk = 0;
-                ptile += gridDim.x;
+                ptile = next_tile(ptile, pti++);
                 if (ptile < p.ntiles) tile_span(ptile, pbase, pnvalid, pdummy0, pdummy1);
             }
         };
         for (int d = 0; d + 1 < p.stiles; d++) prefetch_next();
         bool okw = true;
-        int tile = blockIdx.x, blk = 0, st_idx = 0, accbuf = 0, accuse = 0, nvalid = 0, img0 = 0, oh0 = 0;
+        int tile = first_tile, ti = 0, blk = 0, st_idx = 0, accbuf = 0, accuse = 0, nvalid = 0, img0 = 0, oh0 = 0;
         long long base = 0;
         for (int kb = 0; kb < total_blocks; kb++) {
             if (blk == 0) tile_span(tile, base, nvalid, img0, oh0);
@@ -427,7 +455,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             if (++st_idx == p.stiles) st_idx = 0;
             if (++blk == nblk) {
                 blk = 0;
-                tile += gridDim.x;
+                tile = next_tile(tile, ti++);
                 if (++accbuf == U8_ACCS) { accbuf = 0; accuse++; }
             }
         }
