@@ -276,6 +276,9 @@ U8_SHAPES = [  # n, H, W, cin, cout, k, pad, stride
     (1, 9, 9, 64, 192, 5, 2, 1),       # 5x5, channel blocks of 128 + 64
     (2, 12, 12, 64, 64, 3, 0, 1),      # no padding
     (2, 16, 16, 64, 64, 2, 0, 2),      # 2x2 stride 2
+    (3, 14, 14, 256, 256, 3, 1, 1),    # the deep layers' shapes: four and eight boxes per tap
+    (5, 7, 7, 512, 80, 3, 1, 1),       # with a 16-channel tail block
+    (3, 14, 14, 256, 512, 3, 1, 2),    # and stride 2
     (148, 14, 14, 128, 128, 3, 1, 1),  # 296 tiles on 148 SMs: tiles handed out in pairs that share the weight stages
     (589, 7, 7, 128, 128, 3, 1, 1),    # 295 tiles: the last pair has one tile
 ]
