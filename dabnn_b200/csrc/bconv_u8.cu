@@ -47,7 +47,8 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
     pl.resident = res_bytes <= 48 * 1024;   // a channel block's weights stay in shared memory
     // with resident weights the ring carries pixel boxes only and there is room for a third staging tile
     pl.stiles = pl.resident ? 3 : 2;
-    int avail = U8_MAX_SMEM - 1024 - pl.stiles * U8_STILE_BYTES - 3072 /* static shared memory */;
+    const int stile_bytes = u8_staging_tile_bytes(pl.rows * pl.OW * pl.imgs);
+    int avail = U8_MAX_SMEM - 1024 - pl.stiles * stile_bytes - 3072 /* static shared memory */;
     if (pl.resident) avail -= res_bytes;
     // Streamed weights: two pixel tiles per weight stage (a stage is then two boxes of each tile and of the weights),
     // where handing out tiles in pairs does not lengthen the longest CTA's share (a few per cent per tile; a whole
@@ -61,7 +62,7 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
     const int stage_bytes = pl.G * ((pl.pair ? 2 : 1) * U8_BOX_BYTES + (pl.resident ? 0 : pl.wb * 64));
     pl.stages = std::min(8, avail / stage_bytes);
     if (pl.stages < 2) return false;
-    pl.smem = (pl.resident ? res_bytes : 0) + pl.stages * stage_bytes + pl.stiles * U8_STILE_BYTES + 1024;
+    pl.smem = (pl.resident ? res_bytes : 0) + pl.stages * stage_bytes + pl.stiles * stile_bytes + 1024;
     return true;
 }
 

@@ -43,8 +43,9 @@ constexpr int U8_ACCS = 4;                   // TMEM accumulators of up to 128 c
 constexpr int U8_EPI_WARPS = 16;
 constexpr int U8_EPILOGUE = U8_EPI_WARPS * 32;
 constexpr int U8_THREADS = 64 + U8_EPILOGUE;  // warp 0: loads, warp 1: MMA, then the epilogue warps
-constexpr int U8_SBOX_BYTES = 128 * 128;     // staging box: 128 pixels x 32 channels of fp32, 128-byte-swizzled
-constexpr int U8_STILE_BYTES = 2 * U8_SBOX_BYTES;   // 128 pixels x 64 channels
+// Staging tile of a 64-channel block: two boxes of (a tile's pixels, rounded up to 8) x 32 channels of fp32, 128-byte-swizzled.
+__host__ __device__ inline int u8_staging_rows(int tile_pixels) { return (tile_pixels + 7) & ~7; }
+__host__ __device__ inline int u8_staging_tile_bytes(int tile_pixels) { return 2 * u8_staging_rows(tile_pixels) * 128; }
 constexpr int U8_MAX_STILES = 3;             // staging tiles: one being drained and stored, the others being prefetched
 constexpr int U8_MAX_SMEM = 227 * 1024;
 
@@ -161,6 +162,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     const volatile int* abort_flag = &s_abort;
     const int ohw = p.OH * p.OW;
     const int box_px = p.rows * p.OW * p.imgs;      // pixels a tile's loads and stores cover
+    const int srows = u8_staging_rows(box_px), sbox_bytes = srows * 128, stile_bytes = 2 * sbox_bytes;
 
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(tmem_cols));
@@ -342,7 +344,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         // Prefetch cursor: the block whose shortcut is copied next, walked incrementally.  A thread copies 16 bytes of
         // rows pr0, pr0 + 32, ...: its position inside a staging tile and inside a pixel row never changes.
         const int pr0 = et >> 4, pc4 = (et & 15) * 4;
-        const uint32_t poff = (pc4 >> 5) * U8_SBOX_BYTES + pr0 * 128 + ((((pc4 & 31) >> 2) ^ (pr0 & 7)) << 4);
+        const uint32_t poff = (pc4 >> 5) * sbox_bytes + pr0 * 128 + ((((pc4 & 31) >> 2) ^ (pr0 & 7)) << 4);
         int pkb = 0, ptile = first_tile, pti = 0, pblk = 0, pst = 0, pnvalid = 0, pdummy0, pdummy1;
         long long pbase = 0;
         if (ptile < p.ntiles) tile_span(ptile, pbase, pnvalid, pdummy0, pdummy1);
@@ -351,7 +353,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                 const int cb = pblk * 64;
                 if (pc4 < n_this - cb) {
                     const float* src = p.shortcut + (pbase + pr0) * p.N + n0 + cb + pc4;
-                    const uint32_t dst = sbuf0_addr + pst * U8_STILE_BYTES + poff;
+                    const uint32_t dst = sbuf0_addr + pst * stile_bytes + poff;
 #pragma unroll
                     for (int j = 0; j < 2048 / U8_EPILOGUE; j++)
                         if (pr0 + j * (U8_EPILOGUE / 16) < pnvalid)
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             if (blk == 0) tile_span(tile, base, nvalid, img0, oh0);
             const int cb = blk * 64;
             const int width = min(64, n_this - cb);
-            const uint32_t sb = sbuf0_addr + st_idx * U8_STILE_BYTES;
+            const uint32_t sb = sbuf0_addr + st_idx * stile_bytes;
             if (p.stiles == 3) cp_async_wait<1>(); else cp_async_wait<0>();   // my copies of block kb have landed
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my tensor store of block kb-1 has read its tile
             asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");    // everybody's have: block kb-1's tile is idle
@@ -400,7 +402,8 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                              : "r"(t_row + c0));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 // chunk qq (4 channels) of this pixel's row in box hq / 2: srow + ((qq ^ (r & 7)) << 4)
-                const uint32_t srow = sb + (hq >> 1) * U8_SBOX_BYTES + r * 128;
+                const uint32_t srow = sb + (hq >> 1) * sbox_bytes + r * 128;
+                const bool staged = r < srows;   // the accumulator rows beyond the tile have no staging row
                 uint32_t signs = 0;   // bit j: channel c0 + j of this pixel is positive
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
@@ -417,12 +420,12 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                         o[2] = __fadd_rn(__fmul_rn(ca.z, o[2]), cbv.z); o[3] = __fadd_rn(__fmul_rn(ca.w, o[3]), cbv.w);
                     }
                     const uint32_t sa = srow + ((((hq & 1) * 4 + q) ^ (r & 7)) << 4);
-                    if (p.shortcut) {
+                    if (p.shortcut && staged) {
                         const float4 ad = lds128f(sa);
                         o[0] = __fadd_rn(ad.x, o[0]); o[1] = __fadd_rn(ad.y, o[1]);
                         o[2] = __fadd_rn(ad.z, o[2]); o[3] = __fadd_rn(ad.w, o[3]);
                     }
-                    sts128f(sa, o[0], o[1], o[2], o[3]);
+                    if (staged) sts128f(sa, o[0], o[1], o[2], o[3]);
                     signs |= ((o[0] > 0.f ? 1u : 0u) | (o[1] > 0.f ? 2u : 0u) | (o[2] > 0.f ? 4u : 0u) | (o[3] > 0.f ? 8u : 0u)) << (q * 4);
                 }
                 if (r < nvalid) {
@@ -449,7 +452,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                 const int hb = et >> 5;
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
                              ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + cb + hb * 32), "r"(oh0 * p.OW), "r"(img0),
-                               "r"(sb + hb * U8_SBOX_BYTES) : "memory");
+                               "r"(sb + hb * sbox_bytes) : "memory");
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // every thread, every block: group k is block k's store
             if (++st_idx == p.stiles) st_idx = 0;
