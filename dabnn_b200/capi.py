@@ -15,7 +15,7 @@ ENGINE_AUTO, ENGINE_POPC, ENGINE_B1, ENGINE_IMMA, ENGINE_TCGEN05 = 0, 1, 2, 3, 4
 BINCONV_STATIC_BYTES = 16 << 20   # DABNN_BINCONV_STATIC_BYTES
 ENGINES = {"auto": ENGINE_AUTO, "popc": ENGINE_POPC, "b1": ENGINE_B1, "imma": ENGINE_IMMA, "tcgen05": ENGINE_TCGEN05}
 ERROR_NAMES = {1: "ARG", 2: "SHAPE", 3: "IO", 4: "FORMAT", 5: "UNSUPPORTED", 6: "NOT_FOUND", 7: "CUDA",
-               8: "OOM", 9: "STATE"}
+               8: "OOM", 9: "STATE", 10: "TIMEOUT"}
 
 
 class DabnnError(RuntimeError):
@@ -62,6 +62,7 @@ _SIGNATURES = {
     "dabnn_net_run": [_p, _p, _i, _i],
     "dabnn_net_sync": [_p],
     "dabnn_net_get_blob": [_p, C.c_char_p, C.POINTER(_i), C.POINTER(_p), _p, _z],
+    "dabnn_net_get_blob_bits": [_p, C.c_char_p, C.POINTER(_i), C.POINTER(_p), _p, _z],
     "dabnn_net_output_name": [_p, _i],
     "dabnn_net_stream": [_p],
     "dabnn_net_stats": [_p, C.POINTER(_i), C.POINTER(_z)],
@@ -73,6 +74,8 @@ _SIGNATURES = {
     "dabnn_measure_engine_peak": [_i, C.POINTER(C.c_double)],
     "dabnn_measure_tf32_peak": [C.POINTER(C.c_double)],
     "dabnn_engine_status": [C.POINTER(_i)],
+    "dabnn_last_engine": [],
+    "dabnn_debug_raise_engine_status": [_i, _i],
     "dabnn_last_error": [],
     "dabnn_version": [],
     "dabnn_device_count": [],

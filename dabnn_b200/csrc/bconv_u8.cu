@@ -15,8 +15,10 @@ struct U8Plan {
 
 // Shapes the engine takes: whole 64-channel groups, channel counts in 16s, stride 1 or 2 (even H and W), no
 // dilation, output rows of at most 128 pixels.
+// force_pair: -1 = pair the pixel tiles where the tile count makes it pay, 0 / 1 = the plan without / with pairing
+// (the choice depends on the batch; a Net decides once whether a layer runs here, for every batch up to its maximum).
 bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
-             U8Plan& pl) {
+             U8Plan& pl, int force_pair = -1) {
     if (n <= 0 || h <= 0 || w <= 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || pad_h < 0 || pad_w < 0) return false;
     if (cin % 64 || cout % 16 || stride_h != stride_w || (stride_h != 1 && stride_h != 2)) return false;
     if (stride_h == 2 && ((h | w) & 1)) return false;
@@ -56,7 +58,9 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
     {
         const int ctas = std::max(1, sm_count() / ((cout + TC5_MAX_N - 1) / TC5_MAX_N));
         const int units = (pl.ntiles + 1) / 2;
-        pl.pair = !pl.resident && pl.nboxes % 2 == 0 && 2 * ((units + ctas - 1) / ctas) <= (pl.ntiles + ctas - 1) / ctas;
+        const bool can_pair = !pl.resident && pl.nboxes % 2 == 0;
+        pl.pair = can_pair && 2 * ((units + ctas - 1) / ctas) <= (pl.ntiles + ctas - 1) / ctas;
+        if (force_pair >= 0) pl.pair = can_pair && force_pair;
     }
     if (pl.pair) pl.G = 2;
     const int stage_bytes = pl.G * ((pl.pair ? 2 : 1) * U8_BOX_BYTES + (pl.resident ? 0 : pl.wb * 64));
@@ -88,8 +92,11 @@ bool u8_input_maps(const unsigned char* in, int n, int h, int w, int cin, int st
 }  // namespace
 
 bool bconv_u8_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w) {
-    U8Plan pl;
-    if (!u8_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, pl)) return false;
+    // Both tilings must fit: which one a launch uses depends on its batch, and a Net that keeps a blob as bytes has
+    // no other engine to fall back to for a smaller batch or a ragged last sub-batch.
+    U8Plan pl, other;
+    if (!u8_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, pl, 0)) return false;
+    if (!u8_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, other, 1)) return false;
     // the encoder only looks at the address's alignment: try the descriptors of this shape once
     CUtensorMap maps[2];
     return u8_input_maps(reinterpret_cast<const unsigned char*>(uintptr_t(1) << 20), n, h, w, cin, stride_h, pl, maps);
@@ -163,6 +170,11 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     if (pl.pair) bconv_u8_kernel<true><<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
     else bconv_u8_kernel<false><<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
     return check_launch("bconv_u8_kernel");
+}
+
+int bconv_u8_status_word(int** addr) {
+    DABNN_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(addr), g_u8_status));
+    return DABNN_OK;
 }
 
 int bconv_u8_status(int* status) {

@@ -7,6 +7,9 @@
 
 namespace dabnn {
 
+// engine of the calling thread's most recent contraction launch (dabnn_last_engine)
+static thread_local int g_last_engine = DABNN_ENGINE_AUTO;
+
 template <int ENGINE, int WM, int WN, bool FAST, class XOp, class WOp>
 static int launch_one(const XOp& xop, const WOp& wop, const EpilogueParams& ep, int M, int N, int kwords,
                       cudaStream_t stream) {
@@ -60,8 +63,10 @@ static int launch_tc5_cw(const XOp& xop, const WOp& wop, const EpilogueParams& e
     CUtensorMap out_map{};
     const unsigned long long dims[2] = {(unsigned long long)N, (unsigned long long)M}, strides[1] = {(unsigned long long)ep.ld_out * sizeof(float)};
     const unsigned box[2] = {32, 128};
-    if (ep.out && !make_f32_tensor_map(&out_map, ep.out, 2, dims, strides, box))
+    if (ep.out && !make_f32_tensor_map(&out_map, ep.out, 2, dims, strides, box)) {
+        g_last_engine = DABNN_ENGINE_IMMA;
         return launch_engine<ENG_IMMA>(xop, wop, ep, M, N, kwords, stream);   // no TMA descriptor: the mma.sync engine
+    }
     kern<<<grid, TC5_THREADS, Tc5Cfg<CW>::TOTAL, stream>>>(xop, wop, ep, M, N, kwords, tiles_m, out_map);
     return check_launch("bcontract_tc5_kernel");
 }
@@ -85,6 +90,7 @@ int launch_bcontract(int engine, const XOp& xop, const WOp& wop, const EpilogueP
     DABNN_REQUIRE(kwords < (1 << 17), DABNN_ERR_SHAPE, "contraction: K must be below 2^23 bits");
     if (engine == DABNN_ENGINE_AUTO) engine = DABNN_ENGINE_TCGEN05;
     if (engine == DABNN_ENGINE_TCGEN05 && !tc5_eligible(ep, N)) engine = DABNN_ENGINE_IMMA;
+    g_last_engine = engine;
     switch (engine) {
         case DABNN_ENGINE_TCGEN05: return launch_tc5(xop, wop, ep, M, N, kwords, stream);
         case DABNN_ENGINE_POPC: return launch_engine<ENG_POPC>(xop, wop, ep, M, N, kwords, stream);
@@ -236,6 +242,22 @@ extern "C" int dabnn_binconv_forward(const float* in, const uint64_t* weight, si
     RowMajorOperand wop{weight, row_words, cout, row_words};
     EpilogueParams ep{out, cout, 0, nullptr, nullptr, nullptr, 0, nullptr, 0};
     return launch_bcontract(engine, xop, wop, ep, n * oh * ow, cout, row_words, static_cast<cudaStream_t>(s));
+}
+
+int dabnn::contraction_status_word(int** addr) {
+    DABNN_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(addr), g_tc5_status));
+    return DABNN_OK;
+}
+
+extern "C" int dabnn_last_engine(void) { return g_last_engine; }
+
+extern "C" int dabnn_debug_raise_engine_status(int which, int code) {
+    DABNN_REQUIRE(which >= 0 && which <= 2, DABNN_ERR_ARG, "raise_engine_status: which must be 0, 1 or 2");
+    int* word = nullptr;
+    const int rc = which == 0 ? contraction_status_word(&word) : which == 1 ? fconv_status_word(&word) : bconv_u8_status_word(&word);
+    if (rc) return rc;
+    DABNN_CUDA_OK(cudaMemcpy(word, &code, sizeof(int), cudaMemcpyHostToDevice));
+    return DABNN_OK;
 }
 
 extern "C" int dabnn_engine_status(int* status) {

@@ -80,8 +80,10 @@ class FbTable {
         const size_t t = indirect(slot);
         if (!t) return out;
         const uint32_t n = b_->read<uint32_t>(t);
+        if (!n) return out;
+        const uint8_t* src = b_->ptr(t + 4, (size_t)n * sizeof(T));   // bounds-checked before anything is allocated
         out.resize(n);
-        if (n) std::memcpy(out.data(), b_->ptr(t + 4, (size_t)n * sizeof(T)), (size_t)n * sizeof(T));
+        std::memcpy(out.data(), src, (size_t)n * sizeof(T));
         return out;
     }
     // raw view of a scalar vector (pointer into the buffer, element count)
@@ -99,6 +101,7 @@ class FbTable {
         const size_t t = indirect(slot);
         if (!t) return out;
         const uint32_t n = b_->read<uint32_t>(t);
+        b_->ptr(t + 4, 4 * (size_t)n);   // the offset array lies inside the buffer
         for (uint32_t i = 0; i < n; i++) {
             const size_t p = t + 4 + 4 * (size_t)i;
             out.emplace_back(b_, p + b_->read<uint32_t>(p));
@@ -110,6 +113,7 @@ class FbTable {
         const size_t t = indirect(slot);
         if (!t) return out;
         const uint32_t n = b_->read<uint32_t>(t);
+        b_->ptr(t + 4, 4 * (size_t)n);
         for (uint32_t i = 0; i < n; i++) {
             const size_t p = t + 4 + 4 * (size_t)i;
             const size_t s = p + b_->read<uint32_t>(p);

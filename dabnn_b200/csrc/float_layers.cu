@@ -555,6 +555,11 @@ int fconv_tc5_status(int* status) {
     return DABNN_OK;
 }
 
+int fconv_status_word(int** addr) {
+    DABNN_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(addr), g_tc5_status));
+    return DABNN_OK;
+}
+
 int fconv_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b, int relu,
                float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w,
                int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream) {

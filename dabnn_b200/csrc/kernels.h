@@ -46,6 +46,12 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
                         cudaStream_t stream);
 int bconv_u8_status(int* status);
 
+// Device addresses (on the current device) of the words in which the tensor-core kernels record the code of a
+// bounded wait that gave up: the packed-bit contraction, the float convolution, the byte-activation engine.
+int contraction_status_word(int** addr);
+int fconv_status_word(int** addr);
+int bconv_u8_status_word(int** addr);
+
 // Elementwise chain on an fp32 NHWC tensor, in one pass:  v = x;  if (a) v = a[c]*v + b[c];
 // if (add) v += add;  if (relu) v = max(v, 0);  optional fp32 store and optional sign-bit store.
 int elementwise_chain(const float* x, const float* a, const float* b, const float* add, int relu,

@@ -31,6 +31,22 @@ namespace dabnn {
 
 namespace {
 
+// Last node of every launch plan: collects the status words the tensor-core kernels raise when one of their
+// bounded waits gives up (one word per translation unit), clears them, and reports the first code to the host
+// through a word of mapped pinned memory that the Net checks after it has synchronised.
+__global__ void status_gather_kernel(int* w0, int* w1, int* w2, volatile int* host_word) {
+    int code = 0;
+    int* words[3] = {w0, w1, w2};
+    for (int i = 0; i < 3; i++) {
+        const int v = words[i] ? atomicExch(words[i], 0) : 0;
+        if (v && !code) code = v;
+    }
+    if (code) {
+        *host_word = code;
+        __threadfence_system();
+    }
+}
+
 struct TensorInfo {
     bool is_bit = false;
     std::vector<uint32_t> shape;
@@ -45,6 +61,7 @@ struct Blob {                // one activation buffer (aliases share a Blob)
     bool need_f32 = true;    // some op reads or exposes the float values
     bool need_bits = false;  // some op reads the sign bits
     bool u8 = false;         // the sign bits are kept as {0,1} bytes (byte-activation engine), not packed words
+    bool keep_bits = false;  // the packed bits are a named output of the model (Binarize layer): they survive the run
     size_t f32_off = (size_t)-1, bits_off = (size_t)-1;
     size_t per_image() const { return (size_t)h * w * c; }
 };
@@ -112,7 +129,14 @@ struct NetImpl {
     std::vector<std::string> time_names;
     std::vector<float> time_ms;
 
+    std::map<std::string, int> bit_names;   // outputs of Binarize layers: blob whose packed sign bits they name
+    int* status_words[3] = {nullptr, nullptr, nullptr};   // device addresses of the kernels' status words
+    volatile int* status_host = nullptr;                  // mapped pinned word written by status_gather_kernel
+    int* status_dev = nullptr;                            // its device-side address
+    int check_status();                                   // after a synchronisation: DABNN_OK or DABNN_ERR_TIMEOUT
+
     ~NetImpl() {
+        if (status_host) cudaFreeHost(const_cast<int*>(status_host));
         for (auto& g : graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
         for (auto e : events) cudaEventDestroy(e);
         for (auto e : tickets) if (e) cudaEventDestroy(e);
@@ -154,7 +178,7 @@ struct NetImpl {
     }
     uint64_t* bits(int blob) const {
         const Blob& b = blobs[blob];
-        return reinterpret_cast<uint64_t*>(arena + b.bits_off) + (b.keep ? out_offset * b.h * b.w * (b.c / 64) : 0);
+        return reinterpret_cast<uint64_t*>(arena + b.bits_off) + ((b.keep || b.keep_bits) ? out_offset * b.h * b.w * (b.c / 64) : 0);
     }
     unsigned char* bytes(int blob) const {   // the same buffer when the blob keeps its signs as bytes
         const Blob& b = blobs[blob];
@@ -176,6 +200,8 @@ int NetImpl::parse(const uint8_t* buf, size_t len) {
         {   // only the first input is used (net.cpp:59-70)
             const auto shape = inputs[0].vec<uint32_t>(0);
             DABNN_REQUIRE(shape.size() == 4, DABNN_ERR_FORMAT, "dab: input shape must be NHWC");
+            DABNN_REQUIRE(shape[1] > 0 && shape[2] > 0 && shape[3] > 0 && shape[1] < (1u << 16) && shape[2] < (1u << 16) &&
+                              shape[3] < (1u << 16), DABNN_ERR_FORMAT, "dab: input dimensions must lie in [1, 65535]");
             in_h = shape[1]; in_w = shape[2]; in_c = shape[3];
             input_name = inputs[0].str(1);
         }
@@ -192,6 +218,7 @@ int NetImpl::parse(const uint8_t* buf, size_t len) {
             const void* src = ti.is_bit ? (const void*)t.vec_view<uint64_t>(1, &count)
                                         : (const void*)t.vec_view<float>(2, &count);
             DABNN_REQUIRE(src && count > 0, DABNN_ERR_FORMAT, "dab: tensor " + name + " has no data");
+            for (uint32_t d : ti.shape) DABNN_REQUIRE(d > 0, DABNN_ERR_FORMAT, "dab: tensor " + name + " has an empty dimension");
             ti.count = count;
             auto& slot = tensors[name];
             slot = ti;
@@ -263,6 +290,8 @@ int NetImpl::parse(const uint8_t* buf, size_t len) {
         }
     } catch (const DabError& e) {
         return fail(DABNN_ERR_FORMAT, e.what());
+    } catch (const std::exception& e) {   // bad_alloc / length_error from a hostile length field
+        return fail(DABNN_ERR_FORMAT, std::string("dab: ") + e.what());
     }
     return DABNN_OK;
 }
@@ -311,8 +340,11 @@ int NetImpl::build() {
                 if ((rc = find_tensor(L.weight, &op.w))) return rc;
                 DABNN_REQUIRE(op.w->shape.size() == 4 && op.w->is_bit == bin, DABNN_ERR_FORMAT,
                               "conv weight " + L.weight + " has the wrong type or rank");
-                if (!L.bias.empty() && !bin)
+                if (!L.bias.empty() && !bin) {
                     if ((rc = find_tensor(L.bias, &op.bias))) return rc;
+                    DABNN_REQUIRE(!op.bias->is_bit && op.bias->count == op.w->shape[0], DABNN_ERR_FORMAT,
+                                  "conv bias " + L.bias + " must hold one float per output channel");
+                }
                 if ((rc = sym2(L.pads, "pads", &op.pad_h, &op.pad_w))) return rc;
                 if ((rc = sym2(L.strides, "strides", &op.stride_h, &op.stride_w))) return rc;
                 DABNN_REQUIRE(op.stride_h > 0 && op.stride_w > 0 && op.pad_h >= 0 && op.pad_w >= 0, DABNN_ERR_SHAPE,
@@ -321,6 +353,8 @@ int NetImpl::build() {
                 const Blob ib = blobs[op.in];
                 const int cout = op.w->shape[0];
                 op.kh = op.w->shape[1]; op.kw = op.w->shape[2];
+                DABNN_REQUIRE(cout > 0 && op.kh > 0 && op.kw > 0 && op.kh < 256 && op.kw < 256, DABNN_ERR_FORMAT,
+                              "conv weight " + L.weight + ": output channels and kernel size must be positive (kernel below 256)");
                 DABNN_REQUIRE((int)op.w->shape[3] == ib.c, DABNN_ERR_SHAPE, "conv: weight channels != input channels");
                 const int oh = conv_out_dim(ib.h, op.pad_h, 1, op.kh, op.stride_h);
                 const int ow = conv_out_dim(ib.w, op.pad_w, 1, op.kw, op.stride_w);
@@ -351,6 +385,7 @@ int NetImpl::build() {
                 if ((rc = find_blob(L.input, &op.in))) return rc;
                 if ((rc = find_tensor(L.a, &op.a))) return rc;
                 if ((rc = find_tensor(L.b, &op.b))) return rc;
+                DABNN_REQUIRE(!op.a->is_bit && !op.b->is_bit, DABNN_ERR_FORMAT, "affine: coefficients must be float tensors");
                 DABNN_REQUIRE((int)op.a->count == blobs[op.in].c && (int)op.b->count == blobs[op.in].c, DABNN_ERR_SHAPE,
                               "affine: coefficient length != channels");
                 blob_of[L.output] = op.in;  // in place (ADD_INPLACE_LAYER)
@@ -375,6 +410,7 @@ int NetImpl::build() {
             case LayerType::PRelu: {
                 if ((rc = find_blob(L.input, &op.in))) return rc;
                 if ((rc = find_tensor(L.slope, &op.slope))) return rc;
+                DABNN_REQUIRE(!op.slope->is_bit, DABNN_ERR_FORMAT, "prelu: slope must be a float tensor");
                 DABNN_REQUIRE(op.slope->count == 1 || (int)op.slope->count == blobs[op.in].c, DABNN_ERR_SHAPE,
                               "slope must have size 1 or input.channels");  // PRelu.cpp:7-9
                 blob_of[L.output] = op.in;
@@ -410,11 +446,15 @@ int NetImpl::build() {
             case LayerType::FC: {  // extension: the reference runtime has no FC handler (net.cpp:263)
                 if ((rc = find_blob(L.input, &op.in))) return rc;
                 if ((rc = find_tensor(L.weight, &op.w))) return rc;
-                if (!L.bias.empty())
-                    if ((rc = find_tensor(L.bias, &op.bias))) return rc;
                 const Blob ib = blobs[op.in];
-                DABNN_REQUIRE(!op.w->is_bit && op.w->shape.size() == 2 && op.w->shape[1] == ib.per_image(), DABNN_ERR_SHAPE,
+                DABNN_REQUIRE(!op.w->is_bit && op.w->shape.size() == 2 && op.w->shape[1] == ib.per_image() &&
+                                  op.w->count == (size_t)op.w->shape[0] * ib.per_image(), DABNN_ERR_SHAPE,
                               "fc: weight must be [units][input_size]");
+                if (!L.bias.empty()) {
+                    if ((rc = find_tensor(L.bias, &op.bias))) return rc;
+                    DABNN_REQUIRE(!op.bias->is_bit && op.bias->count == op.w->shape[0], DABNN_ERR_FORMAT,
+                                  "fc bias " + L.bias + " must hold one float per unit");
+                }
                 op.kh = ib.h; op.kw = ib.w;  // a full-size "valid" convolution
                 op.out = blob_of.count(L.output) ? blob_of[L.output] : new_blob(L.output, 1, 1, op.w->shape[0]);
                 op.kind = OpKind::FConv; op.cls = "FC";
@@ -424,6 +464,8 @@ int NetImpl::build() {
                 if ((rc = find_blob(L.input, &op.in))) return rc;
                 DABNN_REQUIRE(blobs[op.in].c % 64 == 0, DABNN_ERR_SHAPE, "float_mat.c % 64 == 0 is not satisfied!");
                 blob_of[L.output] = op.in;
+                bit_names[L.output] = op.in;
+                blobs[op.in].keep_bits = true;
                 op.out = op.in; op.kind = OpKind::Pack; op.cls = "Binarize";
                 break;
             }
@@ -537,7 +579,7 @@ int NetImpl::build() {
         }
         // sign bits: every blob read by a BConvBlock needs bits; let its producer emit them
         for (auto& o : plan)
-            if (o.kind == OpKind::BConvBlock) blobs[o.in].need_bits = true;
+            if (o.kind == OpKind::BConvBlock || o.kind == OpKind::Pack) blobs[o.in].need_bits = true;
         // A blob keeps its signs as {0,1} bytes when every reader is a binary convolution that the byte-activation
         // engine takes (the Binarize layer exposes packed words, so a blob it reads stays packed).
         if (engine == DABNN_ENGINE_AUTO || engine == DABNN_ENGINE_TCGEN05) {
@@ -561,6 +603,10 @@ int NetImpl::build() {
                 with_packs.push_back(pk);
                 bits_ready[o.in] = 1;
             }
+            if (o.kind == OpKind::Pack) {   // a Binarize layer of the model: skipped when the blob's writer already emitted the bits
+                if (bits_ready[o.in]) continue;
+                bits_ready[o.in] = 1;
+            }
             if (o.out >= 0 && o.kind != OpKind::Pack) {
                 bool emits = false;
                 if (blobs[o.out].need_bits && blobs[o.out].c % 64 == 0 &&
@@ -572,7 +618,7 @@ int NetImpl::build() {
                         if (&q == &o) { seen = true; continue; }
                         if (seen && q.out == o.out && q.kind != OpKind::Pack) later_writer = true;
                     }
-                    emits = !later_writer;
+                    emits = !later_writer && !blobs[o.out].keep_bits;   // a Binarize layer's bits are packed where the layer stands
                     // bytes are written by the byte-activation engine and the max pool; any other producer is followed by a Pack
                     if (blobs[o.out].u8 && !((o.kind == OpKind::BConvBlock && o.u8) || o.kind == OpKind::MaxPool)) emits = false;
                 }
@@ -610,7 +656,7 @@ int NetImpl::build() {
         if (i != input_blob) items.push_back({i, false, fbytes, first, last, 0});
         if (b.need_bits) {
             const size_t bb = ((size_t)max_batch * b.h * b.w * (b.u8 ? b.c : b.c / 64 * 8) + 255) / 256 * 256;
-            items.push_back({i, true, bb, first, last, 0});
+            items.push_back({i, true, bb, b.keep_bits ? 0 : first, b.keep_bits ? (int)plan.size() : last, 0});
         }
     }
     // BinConvIm2col scratch: one shared region sized for the largest user
@@ -694,8 +740,28 @@ int NetImpl::build() {
         events.resize(plan.size() + 1);
         for (auto& e : events) DABNN_CUDA_OK(cudaEventCreate(&e));
     }
+    {   // where the kernels report a wait that gave up, and the host-visible word run_plan's last launch copies it to
+        int rc;
+        if ((rc = contraction_status_word(&status_words[0]))) return rc;
+        if ((rc = fconv_status_word(&status_words[1]))) return rc;
+        if ((rc = bconv_u8_status_word(&status_words[2]))) return rc;
+        int* host = nullptr;
+        DABNN_CUDA_OK(cudaHostAlloc(&host, 64, cudaHostAllocMapped));
+        *host = 0;
+        status_host = host;
+        DABNN_CUDA_OK(cudaHostGetDevicePointer(&status_dev, host, 0));
+    }
     loaded = true;
     return DABNN_OK;
+}
+
+int NetImpl::check_status() {
+    if (!status_host) return DABNN_OK;
+    const int code = *status_host;
+    if (!code) return DABNN_OK;
+    *status_host = 0;
+    return fail(DABNN_ERR_TIMEOUT, "a bounded wait inside a tensor-core kernel gave up (code " + std::to_string(code) +
+                                       "): the results of the runs in flight are incomplete");
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -863,6 +929,10 @@ int NetImpl::run_plan(int batch) {
         }
     }
     if (profiling && !events.empty()) cudaEventRecord(events[plan.size()], stream);
+    if (rc == DABNN_OK && status_dev) {
+        status_gather_kernel<<<1, 1, 0, stream>>>(status_words[0], status_words[1], status_words[2], status_dev);
+        rc = check_launch("status_gather_kernel");
+    }
     return rc;
 }
 
@@ -911,9 +981,13 @@ extern "C" int dabnn_net_read_buf(dabnn_net* net, const void* buf, size_t len) {
     DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
     DABNN_REQUIRE(!net->impl.loaded, DABNN_ERR_STATE, "a model has already been read into this net");
     DABNN_CUDA_OK(cudaSetDevice(net->impl.device));
-    int rc = net->impl.parse(static_cast<const uint8_t*>(buf), len);
-    if (rc) return rc;
-    return net->impl.build();
+    try {
+        int rc = net->impl.parse(static_cast<const uint8_t*>(buf), len);
+        if (rc) return rc;
+        return net->impl.build();
+    } catch (const std::exception& e) {   // nothing may unwind through the C boundary
+        return fail(DABNN_ERR_FORMAT, std::string("read_buf: ") + e.what());
+    }
 }
 extern "C" int dabnn_net_read_file(dabnn_net* net, const char* path) {
     DABNN_REQUIRE(net && path, DABNN_ERR_ARG, "null argument");
@@ -938,7 +1012,7 @@ extern "C" int dabnn_net_run(dabnn_net* net, const float* input, int batch, int 
 extern "C" int dabnn_net_sync(dabnn_net* net) {
     DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
     DABNN_CUDA_OK(cudaStreamSynchronize(net->impl.stream));
-    return DABNN_OK;
+    return net->impl.check_status();
 }
 extern "C" int dabnn_net_submit(dabnn_net* net, const float* host_input, int batch, const char* blob, float* host_out,
                                 size_t host_floats, int* ticket) {
@@ -963,7 +1037,7 @@ extern "C" int dabnn_net_submit(dabnn_net* net, const float* host_input, int bat
 extern "C" int dabnn_net_wait(dabnn_net* net, int ticket) {
     DABNN_REQUIRE(net && ticket >= 0 && ticket < NetImpl::kTickets && net->impl.tickets[ticket], DABNN_ERR_ARG, "wait: unknown ticket");
     DABNN_CUDA_OK(cudaEventSynchronize(net->impl.tickets[ticket]));
-    return DABNN_OK;
+    return net->impl.check_status();
 }
 extern "C" int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4], const float** device_ptr,
                                   float* to_host, size_t host_floats) {
@@ -973,6 +1047,8 @@ extern "C" int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4],
     auto it = n.blob_of.find(name);
     if (it == n.blob_of.end()) return fail(DABNN_ERR_NOT_FOUND, std::string("Key ") + name + " not found.");
     const Blob& b = n.blobs[it->second];
+    if (n.bit_names.count(name))
+        return fail(DABNN_ERR_NOT_FOUND, std::string("blob ") + name + " holds packed sign bits (a Binarize output): fetch it with dabnn_net_get_blob_bits");
     if (it->second == n.input_blob)
         return fail(DABNN_ERR_NOT_FOUND, std::string("blob ") + name + " is the caller's input; it is read in place and not kept");
     if (!b.keep)
@@ -985,6 +1061,30 @@ extern "C" int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4],
         DABNN_REQUIRE(host_floats >= cnt, DABNN_ERR_ARG, "get_blob: host buffer too small");
         DABNN_CUDA_OK(cudaMemcpyAsync(to_host, n.f32(it->second), cnt * 4, cudaMemcpyDeviceToHost, n.stream));
         DABNN_CUDA_OK(cudaStreamSynchronize(n.stream));
+        return n.check_status();
+    }
+    return DABNN_OK;
+}
+extern "C" int dabnn_net_get_blob_bits(dabnn_net* net, const char* name, int dims[4], const uint64_t** device_ptr,
+                                       uint64_t* to_host, size_t host_words) {
+    DABNN_REQUIRE(net && name, DABNN_ERR_ARG, "null argument");
+    NetImpl& n = net->impl;
+    DABNN_REQUIRE(n.loaded, DABNN_ERR_STATE, "get_blob_bits: no model has been read");
+    auto it = n.bit_names.find(name);
+    if (it == n.bit_names.end())
+        return fail(DABNN_ERR_NOT_FOUND, std::string("Key ") + name + " not found among the outputs of Binarize layers.");
+    const Blob& b = n.blobs[it->second];
+    if (!b.keep_bits || !b.need_bits || b.u8 || b.bits_off == (size_t)-1)
+        return fail(DABNN_ERR_NOT_FOUND, std::string("blob ") + name + " is consumed inside the fused plan; read the model with optimize = 0 to keep every blob");
+    const int batch = n.cur_batch > 0 ? n.cur_batch : 1;
+    if (dims) { dims[0] = batch; dims[1] = b.h; dims[2] = b.w; dims[3] = b.c / 64; }
+    if (device_ptr) *device_ptr = n.bits(it->second);
+    if (to_host) {
+        const size_t cnt = (size_t)batch * b.h * b.w * (b.c / 64);
+        DABNN_REQUIRE(host_words >= cnt, DABNN_ERR_ARG, "get_blob_bits: host buffer too small");
+        DABNN_CUDA_OK(cudaMemcpyAsync(to_host, n.bits(it->second), cnt * 8, cudaMemcpyDeviceToHost, n.stream));
+        DABNN_CUDA_OK(cudaStreamSynchronize(n.stream));
+        return n.check_status();
     }
     return DABNN_OK;
 }
@@ -997,6 +1097,7 @@ extern "C" int dabnn_net_stats(dabnn_net* net, int* kernels_per_run, size_t* are
     DABNN_REQUIRE(net, DABNN_ERR_ARG, "null net");
     int k = 0;
     for (const auto& o : net->impl.plan) k += o.kind == OpKind::BinConvIm2col ? 2 : 1;
+    if (net->impl.status_dev) k += 1;   // the status collector that ends every plan
     if (kernels_per_run) *kernels_per_run = k;
     if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes + net->impl.arena_bytes_extra + net->impl.expanded_bytes;
     return DABNN_OK;

@@ -114,6 +114,19 @@ class Net:
                                              out.size))
         return out
 
+    def get_blob_bits(self, name: str) -> np.ndarray:
+        """Packed sign bits written by a Binarize layer (reference dabnn/layers/Binarize.cpp:9): uint64 words
+        [batch][h][w][c / 64]."""
+        dims = (C.c_int * 4)()
+        lib = capi.load()
+        rc = lib.dabnn_net_get_blob_bits(self._h, name.encode(), dims, None, None, 0)
+        if rc == 6:
+            raise KeyError(lib.dabnn_last_error().decode())
+        check(rc)
+        out = np.empty(tuple(dims), dtype=np.uint64)
+        check(lib.dabnn_net_get_blob_bits(self._h, name.encode(), None, None, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
     def get_blob_to_ptr(self, name: str, ptr: int, floats: int):
         check(capi.load().dabnn_net_get_blob(self._h, name.encode(), None, None, C.c_void_p(ptr), floats))
 

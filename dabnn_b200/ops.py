@@ -279,3 +279,10 @@ def engine_status():
     v = C.c_int()
     check(capi.load().dabnn_engine_status(C.byref(v)))
     return v.value
+
+
+def last_engine():
+    """Name of the engine the most recent bgemm / bconv / bconv_block / binconv_forward call of this thread launched
+    (a "tcgen05" request falls back to "imma" for shapes the tensor-memory kernel does not take)."""
+    code = capi.load().dabnn_last_engine()
+    return next(k for k, v in ENGINES.items() if v == code)

@@ -38,7 +38,8 @@ enum {
     DABNN_ERR_NOT_FOUND = 6,    /* blob name unknown (reference: std::out_of_range "Key ... not found.") */
     DABNN_ERR_CUDA = 7,         /* a CUDA call failed */
     DABNN_ERR_OOM = 8,          /* device arena cannot be allocated */
-    DABNN_ERR_STATE = 9         /* call order violated (run before read, ...) */
+    DABNN_ERR_STATE = 9,        /* call order violated (run before read, ...) */
+    DABNN_ERR_TIMEOUT = 10      /* a bounded wait inside a tensor-core kernel gave up: results are incomplete */
 };
 
 /* Which contraction engine computes the XOR-popcount sums.  All give identical integers. */
@@ -236,6 +237,11 @@ int dabnn_net_get_blob(dabnn_net* net, const char* name, int dims[4], const floa
 int dabnn_net_submit(dabnn_net* net, const float* host_input, int batch, const char* blob, float* host_out,
                      size_t host_floats, int* ticket);
 int dabnn_net_wait(dabnn_net* net, int ticket);
+/* The packed sign bits that a Binarize layer produced (reference dabnn/layers/Binarize.cpp:9: pack_mat of the
+ * input into a Bit mat, bitpack.h:277; the reference's caller casts get_blob()'s Mat to uint64_t*).  `name` is
+ * the layer's output; dims = {batch, h, w, c / 64} words.  Same conventions as dabnn_net_get_blob. */
+int dabnn_net_get_blob_bits(dabnn_net* net, const char* name, int dims[4], const uint64_t** device_ptr,
+                            uint64_t* to_host, size_t host_words);
 /* Name of the i-th blob that no layer consumes (network outputs); NULL when i is out of range. */
 const char* dabnn_net_output_name(dabnn_net* net, int i);
 /* The CUDA stream (cudaStream_t) the net enqueues on. */
@@ -262,11 +268,25 @@ int dabnn_measure_engine_peak(int engine, double* bitops_per_second);
  * fp32 product (hi*hi + hi*lo + lo*hi), so its fp32-equivalent ceiling is a third of this. */
 int dabnn_measure_tf32_peak(double* flops_per_second);
 
-/* Diagnostic: synchronises the device and returns, through *status, 0 or the code of the first
- * bounded wait that gave up inside a TCGEN05-engine kernel since the library was loaded (1 = an
- * operand buffer was never released by the tensor core, 2 = an accumulator never completed).
- * Such a kernel stops issuing work, frees its tensor memory and returns instead of hanging. */
+/* Diagnostic for the kernel-level entry points: synchronises the device and returns, through *status, 0 or the
+ * code of the first bounded wait that gave up inside a tensor-core kernel and has not been collected yet.  Such
+ * a kernel stops issuing work, frees its tensor memory and returns instead of hanging.  Codes: packed-bit
+ * contraction 1 producers (a ring stage was never released), 2 epilogue (an accumulator never completed),
+ * 3 / 4 MMA thread (accumulator never released / stage never filled); float convolution 11 producers, 12 epilogue, 13 / 14 MMA thread (accumulator /
+ * stage), 15 / 16 row loader and its consumers; byte-activation engine 21 loader, 22 / 23 MMA thread
+ * (accumulator / stage or resident weights), 24 epilogue.  A Net collects (and clears) the words itself at the
+ * end of every run and reports them as DABNN_ERR_TIMEOUT from dabnn_net_wait / _sync / _get_blob. */
 int dabnn_engine_status(int* status);
+
+/* Which engine (DABNN_ENGINE_POPC ... DABNN_ENGINE_TCGEN05) the calling thread's most recent dabnn_bgemm /
+ * dabnn_bconv / dabnn_bconv_block / dabnn_binconv_forward call actually launched: DABNN_ENGINE_TCGEN05 requests
+ * fall back to IMMA for channel counts and alignments the tensor-memory kernel does not take. */
+int dabnn_last_engine(void);
+
+/* Test hook: stores `code` in status word `which` (0 packed-bit contraction, 1 float convolution, 2 byte-activation
+ * engine) exactly as a kernel whose bounded wait gave up would, so that the reporting path can be exercised
+ * without stalling a GPU. */
+int dabnn_debug_raise_engine_status(int which, int code);
 
 #ifdef __cplusplus
 }

@@ -4,6 +4,7 @@
 // tests/net_test.cpp) only needs to include this header instead of <dabnn/net.h>.
 #pragma once
 #include <cstddef>
+#include <cstdint>
 #include <memory>
 #include <stdexcept>
 #include <string>
@@ -69,6 +70,15 @@ class Net : public std::enable_shared_from_this<Net> {
         m->data = m->storage.data();
         check(dabnn_net_get_blob(handle_, name.c_str(), nullptr, nullptr, m->storage.data(), m->storage.size()));
         return m;
+    }
+    // Output of a Binarize layer (dabnn/layers/Binarize.cpp:9): the packed words, dims {n, h, w, c / 64}.
+    std::vector<uint64_t> get_blob_bits(const std::string& name, int dims[4]) {
+        int rc = dabnn_net_get_blob_bits(handle_, name.c_str(), dims, nullptr, nullptr, 0);
+        if (rc == DABNN_ERR_NOT_FOUND) throw std::out_of_range(dabnn_last_error());
+        check(rc);
+        std::vector<uint64_t> words(static_cast<size_t>(dims[0]) * dims[1] * dims[2] * dims[3]);
+        check(dabnn_net_get_blob_bits(handle_, name.c_str(), nullptr, nullptr, words.data(), words.size()));
+        return words;
     }
     dabnn_net* handle() const { return handle_; }
 

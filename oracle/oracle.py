@@ -22,7 +22,8 @@ HERE = Path(__file__).resolve().parent
 PORT_SO = HERE / "_build" / "liboracle_port.so"
 REF_SO = HERE / "_ref" / "libdabnn_ref.so"
 REF_NATIVE_SO = HERE / "_ref" / "libdabnn_ref_native.so"
-REFERENCE_ROOT = Path(os.environ.get("DABNN_REFERENCE", "/root/reference"))
+# where the reference checkout lies: only needed to (re)build oracle/_ref, never at test or bench time
+REFERENCE_ROOT = Path(os.environ["DABNN_REFERENCE"]) if os.environ.get("DABNN_REFERENCE") else None
 
 # numeric values of flatbnn::LayerType (reference common/dab.fbs:4-5)
 LAYER_TYPE = {
@@ -36,11 +37,11 @@ def build(port: bool = True, ref: bool = True) -> None:
     targets = []
     if port:
         targets.append("port")
-    if ref and (REFERENCE_ROOT / "dabnn" / "bgemm.h").exists():
+    if ref and REFERENCE_ROOT is not None and (REFERENCE_ROOT / "dabnn" / "bgemm.h").exists():
         targets.append("ref")
     if targets:
-        subprocess.run(["make", "-s", "-C", str(HERE), f"DABNN_REFERENCE={REFERENCE_ROOT}", *targets],
-                       check=True)
+        env = [f"DABNN_REFERENCE={REFERENCE_ROOT}"] if "ref" in targets else []
+        subprocess.run(["make", "-s", "-C", str(HERE), *env, *targets], check=True)
 
 
 def out_dim(i, pad, dil, k, stride):
@@ -263,6 +264,17 @@ class Port:
                                         f["pads"][0], f["pads"][1], f["strides"][0], f["strides"][1])
             elif l.type == "Concat":
                 blobs[f["output"]] = self.concat(blobs[f["inputs"][0]], blobs[f["inputs"][1]])
+            elif l.type == "Binarize":
+                # dabnn/layers/Binarize.cpp:9: pack_mat(input, output), the output a Bit mat of c / 64 words
+                blobs[f["output"]] = self.pack_mat(blobs[f["input"]])
+            elif l.type == "FC":
+                # The reference runtime has no FC handler (dabnn/net.cpp:263-266); the converter emits the layer
+                # for Gemm (tools/onnx2bnn/OnnxConverter.cpp:429-489) with weight [units][input_size] and a bias.
+                # Over an NHWC blob that is dabnn/fconv.h:14-76 with a kernel as large as the input and no padding.
+                x = blobs[f["input"]]
+                ws = t[f["weight"]]
+                bias = t[f["bias"]].data if f.get("bias") else None
+                blobs[f["output"]] = self.fconv(x, ws.data.reshape(ws.shape[0], *x.shape), bias, 0, 0, 1, 1)
             else:
                 raise RuntimeError(f"Not supported op {l.type}")
         return blobs

@@ -14,9 +14,13 @@ int main(int argc, char** argv) {
             std::vector<float> ones(224 * 224 * 3, 1.f);
             net->run(ones.data());
             auto blob = net->get_blob(argc > 2 ? argv[2] : "fc_out");
-            std::printf("%g %g %g\n", (*blob)[0], (*blob)[1], (*blob)[2]);
+            for (size_t i = 0; i < blob->total(); i++) std::printf("%.9g ", (*blob)[static_cast<int>(i)]);
+            std::printf("\n");
         }
         std::puts("created");
+    } catch (const std::invalid_argument& e) {   // reference net.cpp:35: the model file cannot be opened
+        std::printf("invalid_argument: %s\n", e.what());
+        return 4;
     } catch (const std::runtime_error& e) {
         std::printf("runtime_error: %s\n", e.what());
         return 3;

@@ -137,18 +137,22 @@ def test_bitpack_bgemm_config(ops, port, M, N, K):
     g = torch.Generator(device="cuda").manual_seed(K)
     xbig = torch.randint(-2**63, 2**63 - 1, (Mb, kw), device="cuda", dtype=torch.int64, generator=g)
     res = {}
-    for eng in ("imma", "popc"):
+    for eng in ("imma", "popc", "tcgen05", "auto"):   # the tensor-memory kernel with many pixel tiles per CTA
         c = torch.zeros(Mb * N, device="cuda")
         ops.bgemm(N, Mb, kw, wt, N, xbig, kw, c, N, eng)
+        assert ops.last_engine() == ("tcgen05" if eng == "auto" else eng)
         res[eng] = c
-    assert torch.equal(res["imma"], res["popc"])
+    for eng in ("popc", "tcgen05", "auto"):
+        assert torch.equal(res["imma"], res[eng]), eng
+    assert ops.engine_status() == 0
     c = torch.zeros(Mb * N, device="cuda")
-    ops.bgemm(N, Mb, kw, wt, N, ~xbig, kw, c, N, "imma")
-    assert torch.equal(c, K - res["imma"])
-    idx = [0, Mb // 2 + 1, Mb - 1]                               # spot rows against the oracle
+    ops.bgemm(N, Mb, kw, wt, N, ~xbig, kw, c, N, "tcgen05")
+    assert torch.equal(c, K - res["tcgen05"])
+    idx = [0, 127, 128, Mb // 2 + 1, min(148 * 128 * 4 + 5, Mb - 2), Mb - 129, Mb - 1]   # spot rows against the oracle, several per-CTA tile rounds apart
     sub = host_bits(xbig[idx].contiguous())
-    exp = port.bgemm(N, 3, kw, host_bits(wt), N, sub, kw, np.zeros(3 * N, np.float32), N)
-    assert same_bits(host(res["imma"].view(Mb, N)[idx].contiguous()).ravel(), exp)
+    exp = port.bgemm(N, len(idx), kw, host_bits(wt), N, sub, kw, np.zeros(len(idx) * N, np.float32), N)
+    for eng in ("imma", "tcgen05"):
+        assert same_bits(host(res[eng].view(Mb, N)[idx].contiguous()).ravel(), exp), eng
 
 
 # ------------------------------------------------------------------------------------ bconv
@@ -184,6 +188,13 @@ def test_bconv_sweep_batched(ops, port, H, cin, cout, ks, stride, pad):
     o_imma = ops.bconv(xb, wd, cout, ks, ks, pad, pad, stride, stride, "imma")
     o_popc = ops.bconv(xb, wd, cout, ks, ks, pad, pad, stride, stride, "popc")
     assert torch.equal(o_imma, o_popc)
+    for eng in ("tcgen05", "auto"):   # what dabnn_bconv runs by default: the tensor-memory kernel, several tiles per CTA
+        o = ops.bconv(xb, wd, cout, ks, ks, pad, pad, stride, stride, eng)
+        assert ops.last_engine() == "tcgen05"
+        assert torch.equal(o, o_imma), eng
+    o16 = host(ops.bconv(dev_bits(x), dev_bits(w), cout, ks, ks, pad, pad, stride, stride, "tcgen05"))
+    assert same_bits(o16, out)
+    assert ops.engine_status() == 0
     for i in (0, 255):
         assert same_bits(host(o_imma[i]), port.baseline_bconv(host_bits(xb[i]), w, cout, ks, ks, pad, pad, stride, stride))
 
@@ -408,3 +419,69 @@ def test_engine_peaks_are_measurable(ops):
     peaks = {e: ops.measure_engine_peak(e) for e in ["popc", "b1", "imma", "tcgen05"]}
     peaks["tf32"] = ops.measure_tf32_peak()
     assert all(v > 1e13 for v in peaks.values()), peaks
+
+
+def test_last_engine_names_the_kernel_that_ran(ops, port):
+    """A tcgen05 request is served by the mma.sync int8 kernel for channel counts and alignments the tensor-memory
+    kernel does not take; dabnn_last_engine tells which one ran, so a test that names an engine cannot pass on another."""
+    rng = np.random.default_rng(1)
+    for (m, n, kk, pad_ld, expected) in [(128, 300, 9, 0, "tcgen05"), (64, 1000, 18, 4, "tcgen05"), (159, 253, 68, 0, "imma"),
+                                         (128, 300, 9, 3, "imma"), (3, 50, 2, 0, "imma")]:
+        lda, ldb, ldc = m + pad_ld, kk, m + pad_ld
+        a, b = rand_bits(rng, kk * lda), rand_bits(rng, n * ldb)
+        c0 = rng.integers(0, 5, n * ldc).astype(np.float32)
+        exp = port.bgemm(m, n, kk, a, lda, b, ldb, c0.copy(), ldc)
+        for req in ("tcgen05", "auto"):
+            c = dev_f32(c0)
+            ops.bgemm(m, n, kk, dev_bits(a), lda, dev_bits(b), ldb, c, ldc, req)
+            assert ops.last_engine() == expected, (m, n, kk, pad_ld, req)
+            assert same_bits(host(c), exp)
+    for req in ("popc", "b1", "imma"):
+        c = dev_f32(np.zeros(64 * 64, np.float32))
+        ops.bgemm(64, 64, 1, dev_bits(rand_bits(rng, 64)), 64, dev_bits(rand_bits(rng, 64)), 1, c, 64, req)
+        assert ops.last_engine() == req
+
+
+@pytest.mark.parametrize("h,cin,cout,ks,stride,pad,dil", [(16, 5, 7, 3, 1, 2, 2), (20, 16, 32, 3, 1, 2, 2), (23, 3, 16, 3, 2, 2, 2),
+                                                         (12, 64, 64, 1, 1, 0, 2)])
+def test_fconv_dilation(ops, port, h, cin, cout, ks, stride, pad, dil):
+    """Dilated windows (the reference's tests/fconv_test.cpp runs dilation 2) on every route: the mma.sync kernel
+    (Cout % 16 != 0), staged rows, and a 1x1 kernel for which dilation must change nothing."""
+    rng = np.random.default_rng(h * cin)
+    x = rng.normal(0, 1, (2, h, h, cin)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (cin * ks * ks)), (cout, ks, ks, cin)).astype(np.float32)
+    bv = rng.normal(0, 1, cout).astype(np.float32)
+    out = host(ops.fconv(dev_f32(x), dev_f32(w), dev_f32(bv), pad, pad, stride, stride, dil, dil))
+    for i in range(2):
+        exp = port.fconv(x[i], w, bv, pad, pad, stride, stride, dil, dil)
+        assert out[i].shape == exp.shape
+        np.testing.assert_allclose(out[i], exp, rtol=1e-4, atol=1e-4 * np.abs(exp).max())
+    assert ops.engine_status() == 0
+
+
+@pytest.mark.parametrize("cin,cout,ks", [(64, 64, 3), (128, 32, 3), (64, 128, 1), (256, 64, 3)])
+def test_batchnorm_fold_identity(ops, port, cin, cout, ks):
+    """The converter's BatchNorm fold for a binary convolution (reference tools/onnx2bnn/OnnxConverter.cpp:583-639:
+    b += K*a, then a *= -2) exists so that Affine(mismatch count) equals BatchNorm applied to the +-1 dot product
+    (reference docs/onnx2bnn.md:9-13).  Checked against that product computed in float64, without padding (the
+    reference pads with -1, a float convolution with 0).  Tolerance 1e-5 relative to the largest output."""
+    from dabnn_b200.convert import batchnorm_to_affine, bitpack_weight
+    rng = np.random.default_rng(cin + cout)
+    x = rng.normal(0, 1, (2, 9, 9, cin)).astype(np.float32)
+    wf = np.where(rng.random((cout, ks, ks, cin)) < 0.5, -1.0, 1.0).astype(np.float32)
+    scale, beta = rng.uniform(0.5, 1.5, cout).astype(np.float32), rng.normal(0, 0.1, cout).astype(np.float32)
+    mean, var = rng.normal(0, 3.0, cout).astype(np.float32), rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    K = ks * ks * cin
+    a, b = batchnorm_to_affine(scale, beta, mean, var, 1e-5, binary_k=K)
+    wb, _ = bitpack_weight(wf)
+    cnt = ops.binconv_forward(dev_f32(x), dev_bits(wb), cout, ks, ks, 0, 0, 1, 1)
+    got = host(ops.affine_(cnt.clone(), dev_f32(a), dev_f32(b)))       # Affine works in place
+    xs = np.where(x > 0, 1.0, -1.0)
+    oh = 9 - ks + 1
+    dot = np.zeros((2, oh, oh, cout))
+    for ky in range(ks):
+        for kx in range(ks):
+            dot += np.einsum("nhwc,oc->nhwo", xs[:, ky:ky + oh, kx:kx + oh, :], wf[:, ky, kx, :].astype(np.float64))
+    bn = (dot - mean.astype(np.float64)) / np.sqrt(var.astype(np.float64) + 1e-5) * scale + beta
+    np.testing.assert_allclose(got, bn, rtol=0, atol=1e-5 * np.abs(bn).max())
+    assert same_bits(host(cnt)[0], ((K - dot[0]) / 2).astype(np.float32))   # count = (K - dot) / 2, exactly

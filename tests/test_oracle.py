@@ -184,3 +184,57 @@ def test_live_net_optimize_flag(ref):
     a = ref.run_model(spec, img, optimize=True)["fc_out"]
     b = ref.run_model(spec, img, optimize=False)["fc_out"]
     assert same_bits(a, b)
+
+
+# ------------------------------------------------------------------ converter transforms and the layers beyond the reference runtime
+@pytest.mark.parametrize("cin,cout,ks", [(64, 16, 3), (128, 8, 1), (32, 8, 3)])
+def test_batchnorm_fold_is_batchnorm_of_the_signed_dot_product(port, cin, cout, ks):
+    """tools/onnx2bnn/OnnxConverter.cpp:583-639 (b += K*a; a *= -2) is correct iff Affine(BinConv mismatch count)
+    equals BatchNorm of the +-1 dot product (docs/onnx2bnn.md:9-13).  That identity pins the restated fold without
+    the converter binary: dot product in float64, no padding (the reference pads with -1), 1e-5 of the largest output."""
+    from dabnn_b200.convert import batchnorm_to_affine, bitpack_weight
+    rng = np.random.default_rng(cin * 3 + cout)
+    x = rng.normal(0, 1, (7, 7, cin)).astype(np.float32)
+    wf = np.where(rng.random((cout, ks, ks, cin)) < 0.5, -1.0, 1.0).astype(np.float32)
+    scale, beta = rng.uniform(0.5, 1.5, cout).astype(np.float32), rng.normal(0, 0.1, cout).astype(np.float32)
+    mean, var = rng.normal(0, 3.0, cout).astype(np.float32), rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    K = ks * ks * cin
+    a, b = batchnorm_to_affine(scale, beta, mean, var, 1e-5, binary_k=K)
+    pa, pb = port.bn_to_affine(scale, beta, mean, var, 1e-5, binary_k=K)
+    assert a.tobytes() == pa.tobytes() and b.tobytes() == pb.tobytes()
+    wb, _ = bitpack_weight(wf)
+    assert wb.tobytes() == port.pack_weight(wf).tobytes()
+    cnt = port.binconv_forward(x, wb, cout, ks, ks, 0, 0, 1, 1)
+    got = port.affine(cnt, a, b)
+    xs = np.where(x > 0, 1.0, -1.0)
+    oh = 7 - ks + 1
+    dot = np.zeros((oh, oh, cout))
+    for ky in range(ks):
+        for kx in range(ks):
+            dot += np.einsum("hwc,oc->hwo", xs[ky:ky + oh, kx:kx + oh, :], wf[:, ky, kx, :].astype(np.float64))
+    assert np.array_equal(cnt, ((K - dot) / 2).astype(np.float32))            # Q3: the layer's output is the mismatch count
+    bn = (dot - mean.astype(np.float64)) / np.sqrt(var.astype(np.float64) + 1e-5) * scale + beta
+    np.testing.assert_allclose(got, bn, rtol=0, atol=1e-5 * np.abs(bn).max())
+    # with a convolution bias folded in (OnnxConverter.cpp:617-623): BatchNorm sees dot + bias
+    bias = rng.normal(0, 2.0, cout).astype(np.float32)
+    a2, b2 = batchnorm_to_affine(scale, beta, mean, var, 1e-5, binary_k=K, conv_bias=bias)
+    bn2 = (dot + bias - mean.astype(np.float64)) / np.sqrt(var.astype(np.float64) + 1e-5) * scale + beta
+    np.testing.assert_allclose(port.affine(cnt, a2, b2), bn2, rtol=0, atol=1e-5 * np.abs(bn2).max())
+
+
+def test_run_model_fc_and_binarize(port):
+    """The checker's FC (a full-size valid fconv, dabnn/fconv.h:14-76) is a matrix product over the NHWC-flattened
+    blob plus bias; its Binarize (dabnn/layers/Binarize.cpp:9) is pack_mat."""
+    from dabnn_b200.model_spec import LayerSpec, ModelSpec, TensorSpec
+    rng = np.random.default_rng(8)
+    w = rng.normal(0, 0.1, (6, 4 * 4 * 64)).astype(np.float32)
+    bias = rng.normal(0, 1, 6).astype(np.float32)
+    spec = ModelSpec("data", (1, 4, 4, 64), [TensorSpec("w", "f32", w.shape, w), TensorSpec("b", "f32", (6,), bias)],
+                     [LayerSpec("Binarize", "bin", dict(input="data", output="bits")),
+                      LayerSpec("FC", "fc", dict(input="data", weight="w", bias="b", output="fc"))])
+    x = rng.normal(0, 1, (4, 4, 64)).astype(np.float32)
+    out = port.run_model(spec, x)
+    np.testing.assert_allclose(out["fc"].ravel(), w.astype(np.float64) @ x.ravel().astype(np.float64) + bias, rtol=1e-5, atol=1e-5)
+    assert out["bits"].shape == (4, 4, 1) and out["bits"].tobytes() == port.pack_mat(x).tobytes()
+    word = int(out["bits"][1, 2, 0])
+    assert [(word >> i) & 1 for i in range(64)] == [int(v > 0) for v in x[1, 2]]

@@ -33,6 +33,25 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
         second = ops.binconv_forward_static(x, w, cout, 3, 3, 1, 1, stride, stride)
         assert torch.equal(first, expected)
         assert torch.equal(second, expected)
+        if cin % 64 == 0 and n <= 3:   # and against the CPU checker, not only against the library's other entry
+            from oracle.oracle import Port
+            cnt = Port().binconv_forward(x[0].cpu().numpy(), w.cpu().numpy().view(np.uint64), cout, 3, 3, 1, 1, stride, stride)
+            assert first[0].cpu().numpy().tobytes() == cnt.tobytes()
+    # after the first call on the device (which loads the array's module and looks its address up) a call neither
+    # takes nor returns device memory: the free-byte count of the device does not move
+    n, hw, cin, cout, stride = cases[0]
+    x = torch.rand((n, hw, hw, cin), device="cuda", generator=g) * 2 - 1
+    w = torch.randint(-2**63, 2**63 - 1, (cout * 9,), device="cuda", dtype=torch.int64, generator=g)
+    out = torch.empty((n, hw, hw, cout), device="cuda")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        capi.check(lib.dabnn_binconv_forward_static(C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), w.numel(),
+                                                    C.c_void_p(out.data_ptr()), n, hw, hw, cin, cout, 3, 3, 1, 1, stride, stride, 0,
+                                                    C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
     # a problem whose packed input exceeds the built-in buffer is refused, nothing is launched
     n_big = cap // (56 * 56 * 8) + 1
     dummy = torch.empty(8, device="cuda")
