@@ -494,8 +494,47 @@ __global__ void __launch_bounds__(FNT, 2) fconv_kernel(const FconvParams p) {
 }  // namespace dabnn
 
 #include "fconv_tc5.cuh"
+#include "fconv_stem.cuh"
 
 namespace dabnn {
+
+// The window-reading kernel (fconv_stem.cuh) takes thin inputs with horizontal stride 2 whose output rows fill
+// most of a 128-row tile: the stem of a ResNet.  Returns false for every other shape.
+static bool fconv_stem_plan(const FconvParams& p, FsGeom& g) {
+    if (p.cin > 4 || p.stride_w != 2 || p.dil_h != 1 || p.dil_w != 1 || (p.cout % 16) != 0) return false;
+    if (p.ow < 64 || p.ow > 128 || p.w > FS_MAX_W || p.kh > 16 || p.kw > 8) return false;
+    if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (reinterpret_cast<uintptr_t>(p.in) & 3) != 0) return false;
+    g.kxp = (p.kw + 1) & ~1;
+    g.kpad = p.kh * g.kxp * 4;
+    const int entries = std::max(p.w + 2 * p.pad_w, 2 * (p.ow - 1) + g.kxp);
+    g.plane_bytes = entries * 16;
+    g.slot_bytes = 2 * g.plane_bytes;
+    g.ahead = 2;
+    g.slots = p.kh + 2 * std::min(p.stride_h, p.kh);
+    g.srows = (p.ow + 7) & ~7;
+    g.rows_total = p.n * p.oh;
+    static thread_local int budget_device = -1, budget = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    if (dev != budget_device) {
+        int optin = 0;
+        cudaFuncAttributes fa;
+        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return false;
+        if (cudaFuncGetAttributes(&fa, fconv_stem_kernel<4>) != cudaSuccess) return false;
+        budget = optin - (int)fa.sharedSizeBytes;
+        if (cudaFuncSetAttribute(fconv_stem_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess)
+            return false;
+        budget_device = dev;
+    }
+    if (fs_smem_bytes(g) > budget) {   // a shorter ring: one tile of look-ahead
+        g.ahead = 1;
+        g.slots = p.kh + std::min(p.stride_h, p.kh);
+    }
+    return fs_smem_bytes(g) <= budget;
+}
 
 // The tcgen05 kernel takes a convolution whose padded K fits the resident weight block, whose taps
 // fit the 32-bit validity masks and whose channel blocks are MMA-sized; everything else runs on the
@@ -575,6 +614,25 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     dim3 grid((n * oh * ow + FTM - 1) / FTM, (cout + FTN - 1) / FTN);
     const FconvParams prm{in, weight, bias, a, b, out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w,
                           stride_h, stride_w, dil_h, dil_w, oh, ow};
+    FsGeom geom;
+    if (fconv_stem_plan(prm, geom)) {
+        const int ny = (cout + FS_N - 1) / FS_N;
+        CUtensorMap out_map{};
+        const unsigned long long dims[3] = {(unsigned long long)cout, (unsigned long long)ow, (unsigned long long)n * oh};
+        const unsigned long long strides[2] = {(unsigned long long)cout * 4, (unsigned long long)ow * cout * 4};
+        const unsigned box[3] = {32, (unsigned)geom.srows, 1};
+        if (make_f32_tensor_map(&out_map, out, 3, dims, strides, box)) {
+            dim3 sgrid(std::min(geom.rows_total, std::max(1, sm_count() / ny)), ny);
+            const int smem = fs_smem_bytes(geom);
+            switch (geom.kxp / 2) {
+                case 1: fconv_stem_kernel<1><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
+                case 2: fconv_stem_kernel<2><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
+                case 3: fconv_stem_kernel<3><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
+                default: fconv_stem_kernel<4><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
+            }
+            return check_launch("fconv_stem_kernel");
+        }
+    }
     const int M = n * oh * ow, K = kh * kw * cin, kpad = (K + 7) / 8 * 8;
     const FconvTc5Plan plan = fconv_tc5_plan(prm, kpad);
     if (plan.mode >= 0) {

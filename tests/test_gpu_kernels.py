@@ -485,3 +485,26 @@ def test_batchnorm_fold_identity(ops, port, cin, cout, ks):
     bn = (dot - mean.astype(np.float64)) / np.sqrt(var.astype(np.float64) + 1e-5) * scale + beta
     np.testing.assert_allclose(got, bn, rtol=0, atol=1e-5 * np.abs(bn).max())
     assert same_bits(host(cnt)[0], ((K - dot[0]) / 2).astype(np.float32))   # count = (K - dot) / 2, exactly
+
+
+@pytest.mark.parametrize("n,h,cin,cout,ks,pad,bias,spots", [
+    (2, 224, 3, 64, 7, 3, True, None),        # the stem itself
+    (37, 224, 3, 64, 7, 3, False, None),      # 4144 output rows on 148 CTAs: 28 per CTA, windows rolling through the slot ring, image changes inside a CTA
+    (300, 130, 3, 32, 5, 2, True, (0, 1, 149, 298, 299)),   # 65-pixel output rows, one 32-channel box
+    (3, 256, 4, 64, 3, 1, True, None),        # 128-pixel output rows, four real channels, 256 converter threads busy
+    (2, 200, 1, 16, 7, 3, False, None),       # one channel, one 16-channel box (the three-instruction form)
+    (2, 224, 3, 128, 7, 3, True, None),       # two channel blocks
+    (5, 160, 2, 48, 4, 1, True, None),        # even kernel width (no dummy tap), 48 channels
+])
+def test_fconv_window_reading_kernel(ops, port, n, h, cin, cout, ks, pad, bias, spots):
+    """Thin inputs with stride 2 (dabnn/fconv.h:14-76 on the shapes of a ResNet stem) run on the kernel whose tensor
+    core reads the convolution windows straight out of the staged input rows; against the oracle at 1e-4."""
+    rng = np.random.default_rng(n * h + cout)
+    x = rng.normal(0, 1, (n, h, h, cin)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (cin * ks * ks)), (cout, ks, ks, cin)).astype(np.float32)
+    bv = rng.normal(0, 1, cout).astype(np.float32) if bias else None
+    out = host(ops.fconv(dev_f32(x), dev_f32(w), dev_f32(bv) if bias else None, pad, pad, 2, 2))
+    assert ops.engine_status() == 0
+    for i in (spots or range(n)):
+        exp = port.fconv(x[i], w, bv, pad, pad, 2, 2)
+        np.testing.assert_allclose(out[i], exp, rtol=1e-4, atol=1e-4 * np.abs(exp).max(), err_msg=f"image {i}")
