@@ -76,6 +76,7 @@ _SIGNATURES = {
     "dabnn_engine_status": [C.POINTER(_i)],
     "dabnn_last_engine": [],
     "dabnn_debug_raise_engine_status": [_i, _i],
+    "dabnn_debug_set_halo": [_i],
     "dabnn_last_error": [],
     "dabnn_version": [],
     "dabnn_device_count": [],

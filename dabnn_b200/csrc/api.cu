@@ -35,6 +35,7 @@ static TensorMapEncode tensor_map_encoder() {
     static TensorMapEncode encode = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
+        cudaFree(nullptr);   // the encoder needs an initialised driver and a current context
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult st;
         if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &st) == cudaSuccess &&

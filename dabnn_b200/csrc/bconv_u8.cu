@@ -1,7 +1,7 @@
 // Host side of the byte-activation binary convolution (bconv_u8.cuh): geometry, tensor maps, launches, C ABI.
 #include <algorithm>
 
-#include "bconv_u8.cuh"
+#include "bconv_halo.cuh"
 #include "kernels.h"
 
 namespace dabnn {
@@ -89,6 +89,67 @@ bool u8_input_maps(const unsigned char* in, int n, int h, int w, int cin, int st
     return true;
 }
 
+// ---- the halo kernel (bconv_halo.cuh): 3x3, stride 1, padding 1 --------------------------------------------------
+struct HaloPlan {
+    int OH = 0, OW = 0, P = 0, rows = 0, tiles_per_img = 0, ntiles = 0, hslots = 0, halo_stride = 0, wstages = 0, wb = 0;
+    int resident = 0, stiles = 2, pair = 0, smem = 0;
+};
+
+int g_halo_mode = 1;   // 0: never, 1: wherever the shape allows (dabnn_debug_set_halo)
+
+bool halo_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
+               HaloPlan& pl, int force_pair = -1) {
+    if (!g_halo_mode || kh != 3 || kw != 3 || pad_h != 1 || pad_w != 1 || stride_h != 1 || stride_w != 1) return false;
+    if (n <= 0 || h <= 0 || w <= 0 || cin % 64 || cout % 16 || cin <= 0 || cout <= 0 || w + 2 > 128) return false;
+    if ((long long)n * h * w >= (1ll << 31)) return false;
+    pl.OH = h; pl.OW = w; pl.P = w + 2;
+    const int rmax = 128 / pl.P;
+    pl.tiles_per_img = (h + rmax - 1) / rmax;
+    pl.rows = (h + pl.tiles_per_img - 1) / pl.tiles_per_img;
+    pl.ntiles = n * pl.tiles_per_img;
+    // an image smaller than half a tile (7x7: 63 halo pixels of the MMA's 128 rows) is better served by the per-tap kernel,
+    // which packs two images into a tile
+    if (pl.rows * pl.P < 96) return false;
+    const int cw = cin / 64;
+    pl.wb = u8_weight_rows(cout);
+    const int wbox = pl.wb * 64, res_bytes = 9 * cw * wbox;
+    pl.resident = res_bytes <= 48 * 1024;
+    pl.stiles = pl.resident ? 3 : 2;
+    pl.halo_stride = ((pl.rows + 2) * pl.P * 64 + 1023) & ~1023;
+    const int stile_bytes = u8_staging_tile_bytes(pl.rows * pl.OW);
+    int avail = U8_MAX_SMEM - 1024 - pl.stiles * stile_bytes - 3072 /* static shared memory */;
+    {
+        const int ctas = std::max(1, sm_count() / ((cout + TC5_MAX_N - 1) / TC5_MAX_N));
+        const int units = (pl.ntiles + 1) / 2;
+        pl.pair = !pl.resident && 2 * ((units + ctas - 1) / ctas) <= (pl.ntiles + ctas - 1) / ctas;
+        if (force_pair >= 0) pl.pair = !pl.resident && force_pair;
+    }
+    const int np = pl.pair ? 2 : 1;
+    if (pl.resident) {
+        avail -= res_bytes;
+        pl.wstages = 0;
+    } else {
+        // weight ring first (two to four stages of three boxes), the halo ring gets the rest
+        pl.wstages = 0;
+        for (int ws = HL_MAX_WSTAGES; ws >= 2 && !pl.wstages; ws--)
+            if ((avail - ws * 3 * wbox) / pl.halo_stride >= std::min(HL_MAX_HSLOTS, 2 * np * std::min(cw, 2))) pl.wstages = ws;
+        if (!pl.wstages) pl.wstages = 2;
+        avail -= pl.wstages * 3 * wbox;
+    }
+    pl.hslots = std::min(HL_MAX_HSLOTS, avail / pl.halo_stride);
+    if (pl.hslots < 2 * np) return false;
+    pl.smem = 1024 + pl.hslots * pl.halo_stride + (pl.resident ? res_bytes : pl.wstages * 3 * wbox) + pl.stiles * stile_bytes;
+    return true;
+}
+
+bool halo_input_map(const unsigned char* in, int n, int h, int w, int cin, const HaloPlan& pl, CUtensorMap* map) {
+    const unsigned long long C = cin;
+    const unsigned box[5] = {64u, (unsigned)pl.P, (unsigned)(pl.rows + 2), 1u, 1u};
+    const unsigned long long dims[5] = {C, (unsigned long long)w, (unsigned long long)h, (unsigned long long)n, 1ull};
+    const unsigned long long strides[4] = {C, C * w, C * w * h, C * w * h * n};
+    return make_u8_tensor_map(map, in, 5, dims, strides, box);
+}
+
 }  // namespace
 
 bool bconv_u8_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w) {
@@ -146,7 +207,34 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     if (configured_device != dev) {
         DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_u8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
         DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_u8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
+        DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_halo_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
+        DABNN_CUDA_OK(cudaFuncSetAttribute(bconv_halo_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, U8_MAX_SMEM - 3072));
         configured_device = dev;
+    }
+    HaloPlan hp;
+    if (halo_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, hp)) {   // 3x3 stride 1: every input byte enters the SM once per tile
+        CUtensorMap in_map, out_map{};
+        DABNN_REQUIRE(halo_input_map(in_u8, n, h, w, cin, hp, &in_map), DABNN_ERR_CUDA, "bconv_u8: cannot encode the halo's tensor map");
+        if (out_f32) {
+            const unsigned long long dims[3] = {(unsigned long long)cout, (unsigned long long)hp.OH * hp.OW, (unsigned long long)n};
+            const unsigned long long strides[2] = {(unsigned long long)cout * 4, (unsigned long long)cout * 4 * hp.OH * hp.OW};
+            const unsigned box[3] = {32u, (unsigned)(hp.rows * hp.OW), 1u};
+            DABNN_REQUIRE(make_f32_tensor_map(&out_map, out_f32, 3, dims, strides, box), DABNN_ERR_CUDA,
+                          "bconv_u8: cannot encode the output's tensor map");
+        }
+        HaloParams q{};
+        q.w_img = w_img; q.a = a; q.b = b; q.shortcut = shortcut; q.out = out_f32; q.out_u8 = out_u8; q.out_bits = out_bits;
+        q.B = n; q.OH = hp.OH; q.OW = hp.OW; q.N = cout; q.cw = cin / 64; q.P = hp.P;
+        q.rows = hp.rows; q.tiles_per_img = hp.tiles_per_img; q.ntiles = hp.ntiles;
+        q.hslots = hp.hslots; q.halo_stride = hp.halo_stride; q.wstages = hp.wstages; q.wb = hp.wb;
+        q.resident = hp.resident; q.stiles = hp.stiles; q.pair = hp.pair;
+        const int tiles_n = (cout + TC5_MAX_N - 1) / TC5_MAX_N;
+        const int per_n = std::max(1, sm_count() / tiles_n);
+        const int nunits = hp.pair ? (hp.ntiles + 1) / 2 : hp.ntiles;
+        dim3 grid(std::min(nunits, per_n), tiles_n);
+        if (hp.pair) bconv_halo_kernel<true><<<grid, HL_THREADS, hp.smem, stream>>>(q, in_map, out_map);
+        else bconv_halo_kernel<false><<<grid, HL_THREADS, hp.smem, stream>>>(q, in_map, out_map);
+        return check_launch("bconv_halo_kernel");
     }
     CUtensorMap in_maps[2], out_map{};
     DABNN_REQUIRE(u8_input_maps(in_u8, n, h, w, cin, stride_h, pl, in_maps), DABNN_ERR_CUDA, "bconv_u8: cannot encode the input's tensor map");
@@ -185,6 +273,11 @@ int bconv_u8_status(int* status) {
 }  // namespace dabnn
 
 using namespace dabnn;
+
+extern "C" int dabnn_debug_set_halo(int mode) {
+    g_halo_mode = mode != 0;
+    return DABNN_OK;
+}
 
 extern "C" int dabnn_binarize_u8(const float* in, unsigned char* out, size_t count, dabnn_stream_t s) {
     return binarize_u8_impl(in, out, count, static_cast<cudaStream_t>(s));

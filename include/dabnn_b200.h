@@ -283,6 +283,10 @@ int dabnn_engine_status(int* status);
  * fall back to IMMA for channel counts and alignments the tensor-memory kernel does not take. */
 int dabnn_last_engine(void);
 
+/* Tuning hook: mode 0 keeps 3x3 stride-1 blocks of dabnn_bconv_u8_block on the kernel that loads one box per tap;
+ * the default (1) runs them on the kernel that loads a tile's halo once.  Both give identical results. */
+int dabnn_debug_set_halo(int mode);
+
 /* Test hook: stores `code` in status word `which` (0 packed-bit contraction, 1 float convolution, 2 byte-activation
  * engine) exactly as a kernel whose bounded wait gave up would, so that the reporting path can be exercised
  * without stalling a GPU. */
