@@ -495,6 +495,7 @@ __global__ void __launch_bounds__(FNT, 2) fconv_kernel(const FconvParams p) {
 
 #include "fconv_tc5.cuh"
 #include "fconv_stem.cuh"
+#include "fconv_gemm.cuh"
 
 namespace dabnn {
 
@@ -614,6 +615,37 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     dim3 grid((n * oh * ow + FTM - 1) / FTM, (cout + FTN - 1) / FTN);
     const FconvParams prm{in, weight, bias, a, b, out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w,
                           stride_h, stride_w, dil_h, dil_w, oh, ow};
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (kh == 1 && kw == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 && cin % FG_CHUNK == 0 && cout % 16 == 0 &&
+        al16(in) && al16(weight) && al16(out)) {
+        // a 1x1 convolution is a GEMM over [pixels][cin]: TMA-fed (fconv_gemm.cuh)
+        static thread_local int gemm_device = -1, gemm_stages = 0;
+        int dev = 0;
+        DABNN_CUDA_OK(cudaGetDevice(&dev));
+        if (dev != gemm_device) {
+            int optin = 0;
+            cudaFuncAttributes fa;
+            DABNN_CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+            DABNN_CUDA_OK(cudaFuncGetAttributes(&fa, fconv_gemm_kernel));
+            gemm_stages = FG_MAX_STAGES;
+            while (gemm_stages >= 2 && fg_smem_bytes(gemm_stages) > optin - (int)fa.sharedSizeBytes) gemm_stages--;
+            if (gemm_stages >= 2)
+                DABNN_CUDA_OK(cudaFuncSetAttribute(fconv_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fg_smem_bytes(gemm_stages)));
+            gemm_device = dev;
+        }
+        const int Mpx = n * oh * ow;
+        CUtensorMap a_map, w_map, o_map;
+        const unsigned box[2] = {32, 128};
+        const unsigned long long adims[2] = {(unsigned long long)cin, (unsigned long long)Mpx}, astr[1] = {(unsigned long long)cin * 4};
+        const unsigned long long wdims[2] = {(unsigned long long)cin, (unsigned long long)cout};
+        const unsigned long long odims[2] = {(unsigned long long)cout, (unsigned long long)Mpx}, ostr[1] = {(unsigned long long)cout * 4};
+        if (gemm_stages >= 2 && make_f32_tensor_map(&a_map, const_cast<float*>(in), 2, adims, astr, box) &&
+            make_f32_tensor_map(&w_map, const_cast<float*>(weight), 2, wdims, astr, box) && make_f32_tensor_map(&o_map, out, 2, odims, ostr, box)) {
+            const int items = ((Mpx + 127) / 128) * ((cout + FG_N - 1) / FG_N);
+            fconv_gemm_kernel<<<std::min(items, sm_count()), FG_THREADS, fg_smem_bytes(gemm_stages), stream>>>(prm, Mpx, gemm_stages, a_map, w_map, o_map);
+            return check_launch("fconv_gemm_kernel");
+        }
+    }
     FsGeom geom;
     if (fconv_stem_plan(prm, geom)) {
         const int ny = (cout + FS_N - 1) / FS_N;

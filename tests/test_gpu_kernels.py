@@ -515,3 +515,25 @@ def test_fconv_window_reading_kernel(ops, port, n, h, cin, cout, ks, pad, bias, 
     for i in (spots or range(n)):
         exp = port.fconv(x[i], w, bv, pad, pad, 2, 2)
         np.testing.assert_allclose(out[i], exp, rtol=1e-4, atol=1e-4 * np.abs(exp).max(), err_msg=f"image {i}")
+
+
+@pytest.mark.parametrize("n,h,cin,cout,bias", [
+    (2, 28, 64, 128, True),       # one channel block, two K chunks
+    (70, 28, 64, 128, False),     # 429 pixel tiles on 148 CTAs: every ring wraps, a partial last tile
+    (33, 14, 128, 256, True),     # two channel blocks per pixel tile
+    (150, 7, 256, 512, True),     # four channel blocks, eight K chunks
+    (3, 9, 32, 48, True),         # one K chunk, a 48-channel block (a 16-channel tail box)
+    (2, 11, 96, 208, False),      # 208 = 128 + 80 channels
+])
+def test_fconv_1x1_gemm_kernel(ops, port, n, h, cin, cout, bias):
+    """1x1 float convolutions (the downsample branches: dabnn/fconv.h:14-76 with a 1x1 kernel) run on the TMA-fed GEMM
+    kernel; against the oracle at 1e-4 on spot images."""
+    rng = np.random.default_rng(n + cin + cout)
+    x = rng.normal(0, 1, (n, h, h, cin)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / cin), (cout, 1, 1, cin)).astype(np.float32)
+    bv = rng.normal(0, 1, cout).astype(np.float32) if bias else None
+    out = host(ops.fconv(dev_f32(x), dev_f32(w), dev_f32(bv) if bias else None, 0, 0, 1, 1))
+    assert ops.engine_status() == 0
+    for i in sorted({0, 1, n // 2, n - 1}):
+        exp = port.fconv(x[i], w, bv, 0, 0, 1, 1)
+        np.testing.assert_allclose(out[i], exp, rtol=1e-4, atol=1e-4 * np.abs(exp).max(), err_msg=f"image {i}")
