@@ -53,6 +53,8 @@ _SIGNATURES = {
     "dabnn_avepool": [_p, _p] + [_i] * 10 + [_p],
     "dabnn_concat": [_p, _i, _p, _i, _p, _z, _p],
     "dabnn_fconv": [_p, _p, _p, _p] + [_i] * 13 + [_p],
+    "dabnn_fconv_maxpool_supported": [_i] * 11,
+    "dabnn_fconv_maxpool": [_p, _p, _p, _p, _p, _i, _p, _p] + [_i] * 11 + [_p],
     "dabnn_net_create": [C.POINTER(_p)],
     "dabnn_net_destroy": [_p],
     "dabnn_net_set_flags": [_p, _i, _i, _i],

@@ -26,6 +26,12 @@
 //   * 16 epilogue warps, thread (pixel, 16-channel quarter), in two groups of eight, one per 32-channel box:
 //     tcgen05.ld, add the two column halves, bias, affine, relu, park the row in the group's 128-byte-swizzled
 //     staging box, one TMA tensor store per box.
+// With POOL the 3x3 stride-2 pad-1 max pooling that follows a ResNet stem happens in the same kernel and the stem's own
+// output never leaves the SM: a CTA's share is a run of POOLED rows, the stem rows under them arrive in order (the
+// first one computed again by the neighbour that shares it), and after parking a stem row in the staging boxes the
+// epilogue folds it - three columns, in the reference's tap order and with its `acc < t ? t : acc` rule - into a running
+// row of column maxima in shared memory; every second stem row completes a pooled row, which is written out as fp32
+// and as {0,1} sign bytes.  Results are bit-identical to the two layers run one after the other.
 // Every wait is bounded; a wait that gives up records a code (31 converters, 32 / 33 MMA thread waiting for rows /
 // for an accumulator, 34 epilogue), raises the CTA's abort flag, and the CTA frees its tensor memory and returns.
 // Inputs must be finite: a non-finite pixel also poisons the output pixel whose zero-weight odd tap covers it.
@@ -50,12 +56,17 @@ struct FsGeom {
     int slots;                    // ring of input-row slots: kh + ahead * stride_h
     int ahead;                    // tiles whose windows may be converted beyond the one being multiplied (1 or 2)
     int srows;                    // rows of a staging box (ow rounded up to 8)
-    int rows_total;               // n * oh output rows
+    int rows_total;               // rows shared out among the CTAs: n * oh output rows, n * ph pooled rows with POOL
+    int ph, pw;                   // POOL: pooled rows and columns per image
 };
 
 __host__ __device__ inline int fs_weight_bytes(int kpad) { return 2 * (FS_N / 8) * (kpad / 4) * 128; }
-__host__ __device__ inline int fs_smem_bytes(const FsGeom& g) {
-    return 1024 + g.slots * g.slot_bytes + fs_weight_bytes(g.kpad) + 1024 + 2 * g.srows * 128;
+__host__ __device__ inline int fs_smem_bytes(const FsGeom& g) {   // with POOL: + a running row of column maxima per 32-channel box
+    return 1024 + g.slots * g.slot_bytes + fs_weight_bytes(g.kpad) + 1024 + 2 * g.srows * 128 + 2 * g.pw * 128;
+}
+// the reference's max-pool fold (MaxPool.cpp:209-246): keeps the earlier value on ties, never picks a NaN
+__device__ __forceinline__ float4 fs_sel(const float4 a, const float4 t) {
+    return make_float4(a.x < t.x ? t.x : a.x, a.y < t.y ? t.y : a.y, a.z < t.z ? t.z : a.z, a.w < t.w ? t.w : a.w);
 }
 
 // K-major SWIZZLE_32B shared-memory descriptor: rows of 32 bytes, 8-row groups 256 bytes apart
@@ -90,9 +101,12 @@ struct FsTileIter {
     __device__ __forceinline__ int first_new() const { return fresh ? q0 : next_q; }
 };
 
-template <int SLICES>   // tap pairs per window row (kxp / 2): a compile-time count lets the issue loop unroll
+// SLICES: tap pairs per window row (kxp / 2), a compile-time count lets the issue loop unroll.  POOL: see above; the
+// result goes to pool_out (fp32 [n][ph][pw][cout]) and, if not null, pool_u8 (its signs as bytes) instead of p.out.
+template <int SLICES, bool POOL>
 __global__ void __launch_bounds__(FS_THREADS, 1)
-    fconv_stem_kernel(const FconvParams p, const FsGeom g, const __grid_constant__ CUtensorMap out_map) {
+    fconv_stem_kernel(const FconvParams p, const FsGeom g, const __grid_constant__ CUtensorMap out_map, float* __restrict__ pool_out,
+                      unsigned char* __restrict__ pool_u8) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t rows_ready[4], tile_done[FS_ACCS], acc_empty[FS_ACCS];
     __shared__ uint32_t tmem_base_s;
@@ -110,10 +124,20 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
     const volatile int* abort_flag = &s_abort;
     constexpr int ACC_COLS = 2 * FS_N, TMEM_COLS = FS_ACCS * ACC_COLS;   // 512 columns: all of the tensor memory
 
-    // this CTA's output rows: an even share of n * oh
+    // this CTA's rows: an even share of n * oh output rows - or of n * ph pooled rows, and then the output rows under them
+    // (pooled row py covers output rows 2 py - 1 .. 2 py + 1: consecutive pooled rows share one, so the run of output rows
+    // is contiguous and starts one row early)
     const int per = g.rows_total / gridDim.x, extra = g.rows_total - per * gridDim.x;
-    const int g_begin = blockIdx.x * per + min((int)blockIdx.x, extra);
-    const int ntiles = per + ((int)blockIdx.x < extra ? 1 : 0);
+    const int share_begin = blockIdx.x * per + min((int)blockIdx.x, extra);
+    const int share = per + ((int)blockIdx.x < extra ? 1 : 0);
+    int g_begin = share_begin, ntiles = share;
+    if (POOL && share > 0) {
+        const int i0 = share_begin / g.ph, py0 = share_begin - i0 * g.ph;
+        const int last = share_begin + share - 1, i1 = last / g.ph, py1 = last - i1 * g.ph;
+        g_begin = i0 * p.oh + max(0, 2 * py0 - 1);
+        ntiles = i1 * p.oh + min(p.oh - 1, 2 * py1 + 1) - g_begin + 1;
+    }
+    float* accrow = reinterpret_cast<float*>(stile + 2 * sbox_bytes);   // POOL: [box][pw][32 channels] running column maxima
 
     // ---- set-up ----
     if (warp == FS_MMA_WARP) {
@@ -348,8 +372,8 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[accbuf]);
             }
-            if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's store has read the box
-            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+            if (!POOL && elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's store has read the box
+            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");   // (POOL: everybody has folded the previous row)
             if (epi_abort[h2]) break;
             if (staged && ncol > 0) {
 #pragma unroll
@@ -360,6 +384,39 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor store below reads what was just written
             }
             asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+            if (POOL) {
+                // Fold the parked output row into the running row of column maxima of this group's box.  Output row oy is
+                // the middle row of pooled row oy / 2 when even, and when odd the last row of pooled row (oy - 1) / 2 and
+                // the first of the next: an odd row completes a pooled row (unless it is the CTA's first: that pooled row
+                // is the neighbour's), and so does an image's last row.
+                const int g_row = g_begin + t, img = g_row / p.oh, oy = g_row - img * p.oh;
+                const bool odd = (oy & 1) != 0, prelude = odd && t == 0;
+                const bool emit = (odd && !prelude) || (!odd && oy == p.oh - 1);
+                const bool init = prelude || oy == 0;
+                const uint32_t acc0 = smem_u32(accrow) + (uint32_t)(h2 * g.pw * 128);
+                for (int k = et & 255; k < g.pw * 8; k += 256) {   // task: pooled column px, four channels
+                    const int px = k >> 3, q = k & 7;
+                    if (h2 * 32 + q * 4 >= n_this) continue;
+                    float4 h = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+#pragma unroll
+                    for (int dx = -1; dx <= 1; dx++) {   // the reference skips taps outside the image
+                        const int ox = 2 * px + dx;
+                        if ((unsigned)ox < (unsigned)p.ow) h = fs_sel(h, lds128f(sbox + ox * 128 + ((q ^ (ox & 7)) << 4)));
+                    }
+                    const uint32_t aaddr = acc0 + px * 128 + q * 16;
+                    float4 a = init ? h : fs_sel(lds128f(aaddr), h);
+                    if (emit) {
+                        const size_t e = (((size_t)img * g.ph + (oy >> 1)) * g.pw + px) * p.cout + n0 + h2 * 32 + q * 4;
+                        *reinterpret_cast<float4*>(pool_out + e) = a;
+                        if (pool_u8)
+                            *reinterpret_cast<uint32_t*>(pool_u8 + e) =
+                                (a.x > 0.f ? 1u : 0u) | (a.y > 0.f ? 0x100u : 0u) | (a.z > 0.f ? 0x10000u : 0u) | (a.w > 0.f ? 0x1000000u : 0u);
+                        a = h;   // the row also opens the next pooled row
+                    }
+                    sts128f(aaddr, a.x, a.y, a.z, a.w);
+                }
+                continue;
+            }
             // one tensor store per box; the descriptor is [output row of the batch][pixel][channel]: pixels beyond the row
             // and channels beyond Cout are clipped
             if (elected && n_this > h2 * 32) {

@@ -501,7 +501,7 @@ namespace dabnn {
 
 // The window-reading kernel (fconv_stem.cuh) takes thin inputs with horizontal stride 2 whose output rows fill
 // most of a 128-row tile: the stem of a ResNet.  Returns false for every other shape.
-static bool fconv_stem_plan(const FconvParams& p, FsGeom& g) {
+static bool fconv_stem_plan(const FconvParams& p, FsGeom& g, bool pool = false) {
     if (p.cin > 4 || p.stride_w != 2 || p.dil_h != 1 || p.dil_w != 1 || (p.cout % 16) != 0) return false;
     if (p.ow < 64 || p.ow > 128 || p.w > FS_MAX_W || p.kh > 16 || p.kw > 8) return false;
     if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (reinterpret_cast<uintptr_t>(p.in) & 3) != 0) return false;
@@ -513,7 +513,9 @@ static bool fconv_stem_plan(const FconvParams& p, FsGeom& g) {
     g.ahead = 2;
     g.slots = p.kh + 2 * std::min(p.stride_h, p.kh);
     g.srows = (p.ow + 7) & ~7;
-    g.rows_total = p.n * p.oh;
+    g.ph = pool ? (p.oh - 1) / 2 + 1 : 0;     // 3x3 stride 2 pad 1
+    g.pw = pool ? (p.ow - 1) / 2 + 1 : 0;
+    g.rows_total = pool ? p.n * g.ph : p.n * p.oh;
     static thread_local int budget_device = -1, budget = 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return false;
@@ -521,12 +523,16 @@ static bool fconv_stem_plan(const FconvParams& p, FsGeom& g) {
         int optin = 0;
         cudaFuncAttributes fa;
         if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return false;
-        if (cudaFuncGetAttributes(&fa, fconv_stem_kernel<4>) != cudaSuccess) return false;
+        if (cudaFuncGetAttributes(&fa, fconv_stem_kernel<4, true>) != cudaSuccess) return false;
         budget = optin - (int)fa.sharedSizeBytes;
-        if (cudaFuncSetAttribute(fconv_stem_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
-            cudaFuncSetAttribute(fconv_stem_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
-            cudaFuncSetAttribute(fconv_stem_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
-            cudaFuncSetAttribute(fconv_stem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess)
+        if (cudaFuncSetAttribute(fconv_stem_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess ||
+            cudaFuncSetAttribute(fconv_stem_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess)
             return false;
         budget_device = dev;
     }
@@ -595,6 +601,44 @@ int fconv_tc5_status(int* status) {
     return DABNN_OK;
 }
 
+// Float convolution + (bias, affine, relu) + 3x3 stride-2 pad-1 max pooling in one kernel (fconv_stem.cuh with POOL):
+// whether the shape is taken, and the launch.  The pooled result is fp32 [n][ph][pw][cout] (+ its signs as bytes).
+bool fconv_pool_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w) {
+    if (n <= 0 || h <= 0 || w <= 0 || cin <= 0 || cout <= 0 || kh <= 0 || kw <= 0 || stride_h <= 0 || stride_w <= 0 || pad_h < 0 || pad_w < 0) return false;
+    const int oh = conv_out_dim(h, pad_h, 1, kh, stride_h), ow = conv_out_dim(w, pad_w, 1, kw, stride_w);
+    if (oh < 2 || ow < 2 || (long long)n * oh * ow >= (1ll << 31)) return false;
+    const FconvParams prm{reinterpret_cast<const float*>(uintptr_t(1) << 20), nullptr, nullptr, nullptr, nullptr, reinterpret_cast<float*>(uintptr_t(1) << 20),
+                          0, n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, 1, 1, oh, ow};
+    FsGeom g;
+    return fconv_stem_plan(prm, g, true);
+}
+
+int fconv_pool_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b, int relu, float* pool_out,
+                    unsigned char* pool_u8, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                    int stride_w, cudaStream_t stream) {
+    DABNN_REQUIRE(in && weight && pool_out, DABNN_ERR_ARG, "fconv_pool: null pointer");
+    DABNN_REQUIRE((a == nullptr) == (b == nullptr), DABNN_ERR_ARG, "fconv_pool: a and b go together");
+    DABNN_REQUIRE(fconv_pool_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w), DABNN_ERR_SHAPE,
+                  "fconv_pool: shape not taken by the fused convolution + pooling kernel");
+    DABNN_REQUIRE(((reinterpret_cast<uintptr_t>(pool_out) | reinterpret_cast<uintptr_t>(pool_u8)) & 15) == 0 && (reinterpret_cast<uintptr_t>(in) & 3) == 0,
+                  DABNN_ERR_ARG, "fconv_pool: outputs must be 16-byte aligned");
+    const int oh = conv_out_dim(h, pad_h, 1, kh, stride_h), ow = conv_out_dim(w, pad_w, 1, kw, stride_w);
+    const FconvParams prm{in, weight, bias, a, b, pool_out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, 1, 1, oh, ow};
+    FsGeom geom;
+    DABNN_REQUIRE(fconv_stem_plan(prm, geom, true), DABNN_ERR_SHAPE, "fconv_pool: shape not taken by the fused convolution + pooling kernel");
+    const int ny = (cout + FS_N - 1) / FS_N;
+    dim3 sgrid(std::min(geom.rows_total, std::max(1, sm_count() / ny)), ny);
+    const int smem = fs_smem_bytes(geom);
+    const CUtensorMap no_map{};
+    switch (geom.kxp / 2) {
+        case 1: fconv_stem_kernel<1, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
+        case 2: fconv_stem_kernel<2, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
+        case 3: fconv_stem_kernel<3, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
+        default: fconv_stem_kernel<4, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
+    }
+    return check_launch("fconv_stem_kernel (pooled)");
+}
+
 int fconv_status_word(int** addr) {
     DABNN_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(addr), g_tc5_status));
     return DABNN_OK;
@@ -657,10 +701,10 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
             dim3 sgrid(std::min(geom.rows_total, std::max(1, sm_count() / ny)), ny);
             const int smem = fs_smem_bytes(geom);
             switch (geom.kxp / 2) {
-                case 1: fconv_stem_kernel<1><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
-                case 2: fconv_stem_kernel<2><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
-                case 3: fconv_stem_kernel<3><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
-                default: fconv_stem_kernel<4><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map); break;
+                case 1: fconv_stem_kernel<1, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
+                case 2: fconv_stem_kernel<2, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
+                case 3: fconv_stem_kernel<3, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
+                default: fconv_stem_kernel<4, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
             }
             return check_launch("fconv_stem_kernel");
         }
@@ -732,6 +776,16 @@ extern "C" int dabnn_concat(const float* x1, int c1, const float* x2, int c2, fl
     if (pixels == 0) return DABNN_OK;
     concat_kernel<<<grid_for(pixels * (c1 + c2), 256 * 4), 256, 0, static_cast<cudaStream_t>(s)>>>(x1, c1, x2, c2, out, pixels);
     return check_launch("concat_kernel");
+}
+extern "C" int dabnn_fconv_maxpool_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                                             int stride_w) {
+    return fconv_pool_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w) ? 1 : 0;
+}
+extern "C" int dabnn_fconv_maxpool(const float* in, const float* weight, const float* bias, const float* a, const float* b, int relu,
+                                   float* out, unsigned char* out_u8, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
+                                   int pad_w, int stride_h, int stride_w, dabnn_stream_t s) {
+    return fconv_pool_impl(in, weight, bias, a, b, relu, out, out_u8, n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w,
+                           static_cast<cudaStream_t>(s));
 }
 extern "C" int dabnn_fconv(const float* in, const float* weight, const float* bias, float* out, int n, int h,
                            int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,

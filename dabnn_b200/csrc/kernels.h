@@ -64,6 +64,13 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
                int relu, float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
                int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream);
 
+// The same followed by a 3x3 stride-2 pad-1 max pooling, in one kernel, for the shapes fconv_pool_supported accepts (thin
+// inputs with horizontal stride 2: a ResNet stem); the convolution's own output is never written.
+bool fconv_pool_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w);
+int fconv_pool_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b, int relu, float* pool_out,
+                    unsigned char* pool_u8, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                    int stride_w, cudaStream_t stream);
+
 // Max pooling that also emits the signs of its output (the first binary conv's input), packed and / or as bytes.
 int maxpool_impl(const float* in, float* out, uint64_t* out_bits, int n, int h, int w, int c, int kh, int kw,
                  int pad_h, int pad_w, int stride_h, int stride_w, cudaStream_t stream, unsigned char* out_u8 = nullptr);

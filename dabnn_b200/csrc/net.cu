@@ -66,7 +66,7 @@ struct Blob {                // one activation buffer (aliases share a Blob)
     size_t per_image() const { return (size_t)h * w * c; }
 };
 
-enum class OpKind { FConv, BConvBlock, BinConvIm2col, Pack, Chain, PRelu, MaxPool, AvePool, Concat };
+enum class OpKind { FConv, FConvPool, BConvBlock, BinConvIm2col, Pack, Chain, PRelu, MaxPool, AvePool, Concat };
 
 struct Op {
     OpKind kind;
@@ -560,6 +560,21 @@ int NetImpl::build() {
             } else if (o.kind == OpKind::FConv && lops[i].type == LayerType::FpConv2D) {
                 if (next_is(LayerType::Affine)) { o.a = lops[j].op.a; o.b = lops[j].op.b; used[j++] = 1; }
                 if (next_is(LayerType::Relu)) { o.relu = 1; used[j++] = 1; }
+                // A ResNet stem: the 3x3 stride-2 pad-1 max pooling that is the convolution's only reader happens in the
+                // convolution's epilogue, and the convolution's own output is never materialised.
+                if (j < nl && !used[j] && lops[j].type == LayerType::MaxPool && lops[j].op.in == o.out && !blobs[o.out].keep) {
+                    const Op& mp = lops[j].op;
+                    int readers = 0;
+                    for (int k = i + 1; k < nl; k++)
+                        if (!used[k] && (lops[k].op.in == o.out || lops[k].op.in2 == o.out || (k != j && lops[k].op.out == o.out))) readers++;
+                    const Blob& ib = blobs[o.in];
+                    if (readers == 1 && mp.kh == 3 && mp.kw == 3 && mp.stride_h == 2 && mp.stride_w == 2 && mp.pad_h == 1 && mp.pad_w == 1 &&
+                        fconv_pool_supported(max_batch, ib.h, ib.w, ib.c, blobs[o.out].c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w)) {
+                        o.kind = OpKind::FConvPool;
+                        o.out = mp.out;
+                        used[j++] = 1;
+                    }
+                }
             } else if (o.kind == OpKind::Chain) {
                 // merge a run of in-place elementwise layers on the same blob, in reference order:
                 // affine -> add -> relu is the only order one pass can express
@@ -610,7 +625,7 @@ int NetImpl::build() {
             if (o.out >= 0 && o.kind != OpKind::Pack) {
                 bool emits = false;
                 if (blobs[o.out].need_bits && blobs[o.out].c % 64 == 0 &&
-                    (o.kind == OpKind::BConvBlock || o.kind == OpKind::Chain || o.kind == OpKind::MaxPool)) {
+                    (o.kind == OpKind::BConvBlock || o.kind == OpKind::Chain || o.kind == OpKind::MaxPool || o.kind == OpKind::FConvPool)) {
                     // only the blob's last writer emits the bits: an in-place writer later in the
                     // plan would change the values
                     bool later_writer = false, seen = false;
@@ -620,7 +635,8 @@ int NetImpl::build() {
                     }
                     emits = !later_writer && !blobs[o.out].keep_bits;   // a Binarize layer's bits are packed where the layer stands
                     // bytes are written by the byte-activation engine and the max pool; any other producer is followed by a Pack
-                    if (blobs[o.out].u8 && !((o.kind == OpKind::BConvBlock && o.u8) || o.kind == OpKind::MaxPool)) emits = false;
+                    if (blobs[o.out].u8 && !((o.kind == OpKind::BConvBlock && o.u8) || o.kind == OpKind::MaxPool || o.kind == OpKind::FConvPool)) emits = false;
+                    if (o.kind == OpKind::FConvPool && !blobs[o.out].u8) emits = false;   // the fused kernel writes sign bytes, not packed words
                 }
                 o.write_bits = emits;
                 bits_ready[o.out] = emits;
@@ -902,6 +918,16 @@ int NetImpl::run_plan(int batch) {
                                 o.a ? static_cast<const float*>(o.a->dev) : nullptr,
                                 o.b ? static_cast<const float*>(o.b->dev) : nullptr, o.relu, f32(o.out), batch, ib.h,
                                 ib.w, ib.c, ob.c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, 1, 1, stream);
+                break;
+            }
+            case OpKind::FConvPool: {
+                const Blob& ob = blobs[o.out];
+                rc = fconv_pool_impl(f32(o.in), static_cast<const float*>(o.w->dev),
+                                     o.bias ? static_cast<const float*>(o.bias->dev) : nullptr,
+                                     o.a ? static_cast<const float*>(o.a->dev) : nullptr,
+                                     o.b ? static_cast<const float*>(o.b->dev) : nullptr, o.relu, f32(o.out),
+                                     o.write_bits && ob.u8 ? bytes(o.out) : nullptr, batch, ib.h, ib.w, ib.c, ob.c, o.kh, o.kw,
+                                     o.pad_h, o.pad_w, o.stride_h, o.stride_w, stream);
                 break;
             }
             case OpKind::Chain:

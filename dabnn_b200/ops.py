@@ -260,6 +260,26 @@ def fconv(x, weight, bias, pad_h, pad_w, stride_h, stride_w, dil_h=1, dil_w=1):
     return out if x.dim() == 4 else out[0]
 
 
+def fconv_maxpool_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w):
+    return bool(capi.load().dabnn_fconv_maxpool_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w))
+
+
+def fconv_maxpool(x, weight, bias, pad_h, pad_w, stride_h, stride_w, a=None, b=None, relu=False, want_u8=False):
+    """Float convolution (+ bias, affine, relu) followed by a 3x3 stride-2 pad-1 max pooling, in one kernel (the stem of
+    a ResNet: reference dabnn/fconv.h:14 -> Affine.cpp:10 -> Relu.cpp:21 -> MaxPool.cpp:209).  Returns (pooled fp32,
+    sign bytes or None)."""
+    x4 = _b4(_cuda(x, torch.float32))
+    n, h, w, c = x4.shape
+    cout, kh, kw, _ = weight.shape
+    oh, ow = out_dim(h, pad_h, 1, kh, stride_h), out_dim(w, pad_w, 1, kw, stride_w)
+    ph, pw = (oh - 1) // 2 + 1, (ow - 1) // 2 + 1
+    out = torch.empty((n, ph, pw, cout), dtype=torch.float32, device=x.device)
+    o8 = torch.empty((n, ph, pw, cout), dtype=torch.uint8, device=x.device) if want_u8 else None
+    check(capi.load().dabnn_fconv_maxpool(_ptr(x4), _ptr(_cuda(weight, torch.float32)), _ptr(bias), _ptr(a), _ptr(b), int(relu), _ptr(out),
+                                          _ptr(o8), n, h, w, c, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, _stream()))
+    return out, o8
+
+
 def measure_engine_peak(engine):
     """Register-resident peak of one contraction instruction in bit-op/s."""
     v = C.c_double()

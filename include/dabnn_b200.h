@@ -190,6 +190,19 @@ int dabnn_fconv(const float* in, const float* weight, const float* bias, float* 
                 int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
                 int stride_w, int dil_h, int dil_w, dabnn_stream_t s);
 
+/* The stem of a ResNet-shaped network in one kernel, the sequence the reference runs as four layers
+ * (dabnn/fconv.h:14 -> layers/Affine.cpp:10 -> layers/Relu.cpp:21 -> layers/MaxPool.cpp:209 with a 3x3 window, stride 2,
+ * padding 1):  y = conv(in, weight) (+ bias);  if (a) y = a[c]*y + b[c];  if (relu) y = max(y, 0);  out = maxpool3x3s2p1(y).
+ * y itself is never written.  out fp32 [n][ph][pw][cout] with ph = (oh - 1) / 2 + 1; out_u8 (optional) = its signs as
+ * {0,1} bytes.  The result is bit-identical to dabnn_fconv + dabnn_affine + dabnn_relu + dabnn_maxpool.  Shapes taken:
+ * cin <= 4, horizontal stride 2, no dilation, kw <= 8, output rows of 64 .. 128 pixels, cout % 16 == 0
+ * (dabnn_fconv_maxpool_supported tells); anything else returns DABNN_ERR_SHAPE. */
+int dabnn_fconv_maxpool_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                                  int stride_w);
+int dabnn_fconv_maxpool(const float* in, const float* weight, const float* bias, const float* a, const float* b, int relu,
+                        float* out, unsigned char* out_u8, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
+                        int pad_w, int stride_h, int stride_w, dabnn_stream_t s);
+
 /* ---------------------------------------------------------------------------------------------
  * Net level: reference dabnn/net.h:22-66 class bnn::Net.
  * ------------------------------------------------------------------------------------------- */

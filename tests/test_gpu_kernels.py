@@ -537,3 +537,47 @@ def test_fconv_1x1_gemm_kernel(ops, port, n, h, cin, cout, bias):
     for i in sorted({0, 1, n // 2, n - 1}):
         exp = port.fconv(x[i], w, bv, 0, 0, 1, 1)
         np.testing.assert_allclose(out[i], exp, rtol=1e-4, atol=1e-4 * np.abs(exp).max(), err_msg=f"image {i}")
+
+
+@pytest.mark.parametrize("n,h,cin,cout,ks,pad,relu", [
+    (2, 224, 3, 64, 7, 3, True),        # the stem and its pool
+    (37, 224, 3, 64, 7, 3, True),       # 2072 pooled rows on 148 CTAs: shares that start and end inside images
+    (149, 130, 3, 32, 5, 2, False),     # 65-pixel rows (odd: the last column has a two-tap window), 33 pooled rows, no relu (negative maxima)
+    (3, 255, 4, 64, 3, 1, True),        # 128 x 128 outputs from an odd-sized image
+    (5, 226, 1, 16, 7, 3, True),        # 113 output rows: an image's last pooled row ends on an even row
+    (2, 224, 3, 128, 7, 3, True),       # two channel blocks
+])
+def test_fconv_maxpool_fused_is_bit_identical(ops, port, n, h, cin, cout, ks, pad, relu):
+    """The fused stem kernel (convolution + bias + affine + relu + 3x3 / 2 max pooling, the convolution's output never
+    written) against the same four steps run one after the other on the same kernels: bit for bit, sign bytes included;
+    and against the oracle's FloatConv -> Affine -> Relu -> MaxPool at 1e-4 on spot images."""
+    rng = np.random.default_rng(n * h + cout)
+    x = rng.normal(0, 1, (n, h, h, cin)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (cin * ks * ks)), (cout, ks, ks, cin)).astype(np.float32)
+    bv = rng.normal(0, 1, cout).astype(np.float32)
+    a, b = rng.uniform(0.5, 1.5, cout).astype(np.float32), rng.normal(0, 0.5, cout).astype(np.float32)
+    assert ops.fconv_maxpool_supported(n, h, h, cin, cout, ks, ks, pad, pad, 2, 2)
+    xd, wd = dev_f32(x), dev_f32(w)
+    fused, f8 = ops.fconv_maxpool(xd, wd, dev_f32(bv), pad, pad, 2, 2, dev_f32(a), dev_f32(b), relu, want_u8=True)
+    y = ops.affine_(ops.fconv(xd, wd, dev_f32(bv), pad, pad, 2, 2), dev_f32(a), dev_f32(b))
+    if relu:
+        y = ops.relu_(y)
+    steps = ops.maxpool(y, 3, 3, 1, 1, 2, 2)
+    assert ops.engine_status() == 0
+    assert torch.equal(fused, steps)
+    assert torch.equal(f8, (steps > 0).to(torch.uint8))
+    for i in sorted({0, n // 2, n - 1}):
+        e = port.affine(port.fconv(x[i], w, bv, pad, pad, 2, 2), a, b)
+        if relu:
+            e = port.relu(e)
+        e = port.maxpool(e, 3, 3, 1, 1, 2, 2)
+        np.testing.assert_allclose(host(fused[i]), e, rtol=1e-4, atol=1e-4 * np.abs(e).max(), err_msg=f"image {i}")
+
+
+def test_fconv_maxpool_refuses_other_shapes(ops):
+    assert not ops.fconv_maxpool_supported(1, 64, 64, 3, 64, 7, 7, 3, 3, 2, 2)      # 32-pixel output rows: too short for the kernel
+    assert not ops.fconv_maxpool_supported(1, 224, 224, 8, 64, 7, 7, 3, 3, 2, 2)    # more than four channels
+    assert not ops.fconv_maxpool_supported(1, 224, 224, 3, 64, 7, 7, 3, 3, 1, 1)    # stride 1
+    x, w = torch.zeros((1, 64, 64, 3), device="cuda"), torch.zeros((64, 7, 7, 3), device="cuda")
+    with pytest.raises(Exception):
+        ops.fconv_maxpool(x, w, None, 3, 3, 2, 2)
