@@ -17,7 +17,7 @@
 
 namespace dabnn {
 
-constexpr int FG_N = 128;                      // channel block
+constexpr int FG_N = 128;                      // largest channel block (the accumulators lie FG_N columns apart)
 constexpr int FG_CHUNK = 32;                   // floats of K per stage: one 128-byte row
 constexpr int FG_CONVERTERS = 128, FG_EPILOGUE = 512;
 constexpr int FG_THREADS = 32 + FG_CONVERTERS + 32 + FG_EPILOGUE;
@@ -37,7 +37,7 @@ __device__ __forceinline__ uint64_t fg_desc_sw128(uint32_t saddr) {
 __host__ __device__ inline int fg_smem_bytes(int stages) { return 1024 + stages * FG_STAGE_BYTES + 2 * FG_TILE_BYTES; }
 
 __global__ void __launch_bounds__(FG_THREADS, 1)
-    fconv_gemm_kernel(const FconvParams p, const int M, const int stages, const __grid_constant__ CUtensorMap a_map,
+    fconv_gemm_kernel(const FconvParams p, const int M, const int stages, const int n_blk, const __grid_constant__ CUtensorMap a_map,
                       const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap out_map) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bar_loaded[FG_MAX_STAGES], bar_ready[FG_MAX_STAGES], bar_empty[FG_MAX_STAGES];
@@ -50,7 +50,9 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
     unsigned char* stile = stage0 + stages * FG_STAGE_BYTES;
     const volatile int* abort_flag = &s_abort;
     const int K = p.cin, nchunks = K / FG_CHUNK;
-    const int tiles_m = (M + 127) / 128, nblocks = (p.cout + FG_N - 1) / FG_N;
+    // n_blk: channels per work item (32, 64 or 128: small when there are few pixel tiles, so that every SM gets work)
+    const int tiles_m = (M + 127) / 128, nblocks = (p.cout + n_blk - 1) / n_blk;
+    const uint32_t w_bytes = (uint32_t)n_blk * 128u;   // a weight tile of a stage
     const int nitems = tiles_m * nblocks;
     constexpr int TMEM_COLS = FG_ACCS * FG_N;
 
@@ -86,12 +88,12 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
                         break;
                     }
                     const uint32_t bar = smem_u32(&bar_loaded[s]), sa = stage0_addr + s * FG_STAGE_BYTES;
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * FG_TILE_BYTES) : "memory");
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(FG_TILE_BYTES + w_bytes) : "memory");
                     // rows beyond M / beyond Cout read as zeros; a load always delivers its whole box
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                                  ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&a_map)), "r"(c * FG_CHUNK), "r"(tile * 128), "r"(bar) : "memory");
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                 ::"r"(sa + 2 * FG_TILE_BYTES), "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(c * FG_CHUNK), "r"(nb * FG_N), "r"(bar) : "memory");
+                                 ::"r"(sa + 2 * FG_TILE_BYTES), "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(c * FG_CHUNK), "r"(nb * n_blk), "r"(bar) : "memory");
                     if (++s == (uint32_t)stages) { s = 0; use++; }
                 }
             }
@@ -117,6 +119,7 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
                     const uint32_t hi0 = sa + half * 2 * FG_TILE_BYTES + ct * 16, lo0 = hi0 + FG_TILE_BYTES;
 #pragma unroll
                     for (int j = 0; j < FG_TILE_BYTES / 16 / FG_CONVERTERS; j++) {
+                        if (half == 1 && (uint32_t)(j * FG_CONVERTERS * 16) >= w_bytes) break;   // a weight tile has n_blk rows
                         const float4 v = lds128f(hi0 + j * FG_CONVERTERS * 16);
                         uint32_t h, l0, l1, l2, l3;
                         split_tf32(v.x, h, l0); split_tf32(v.y, h, l1); split_tf32(v.z, h, l2); split_tf32(v.w, h, l3);
@@ -139,8 +142,8 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
             int i = 0;
             for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x, i++) {
                 const int nb = item % nblocks;
-                const int n_this = min(FG_N, p.cout - nb * FG_N);
-                const uint32_t idesc = idesc_m | ((uint32_t)(n_this >> 3) << 17);
+                const int n_mma = (min(n_blk, p.cout - nb * n_blk) + 15) & ~15;   // weight rows beyond Cout read as zeros
+                const uint32_t idesc = idesc_m | ((uint32_t)(n_mma >> 3) << 17);
                 const int accbuf = i % FG_ACCS, accuse = i / FG_ACCS;
                 if (accuse >= 1 && !mbar_wait(&bar_acc_empty[accbuf], (accuse - 1) & 1, abort_flag)) {
                     atomicCAS(&g_tc5_status, 0, 43);
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
         bool alive = true;
         for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x, i++) {
             const int tile = item / nblocks, nb = item - tile * nblocks;
-            const int n0 = nb * FG_N, n_this = min(FG_N, p.cout - n0);
+            const int n0 = nb * n_blk, n_this = min(n_blk, p.cout - n0);
             const int accbuf = i % FG_ACCS, accuse = i / FG_ACCS;
             const bool okw = __all_sync(0xffffffffu, mbar_wait<200>(&bar_acc_full[accbuf], accuse & 1, abort_flag));   // warp-uniform
             if (!okw) {
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int e = 0; e < 16; e++) {
-                        const int ch = n0 + c0 + e;
+                        const int ch = min(n0 + c0 + e, p.cout - 1);   // columns beyond Cout are clipped by the store
                         float f = __uint_as_float(v[e]);
                         if (p.bias) f = __fadd_rn(f, __ldg(p.bias + ch));
                         if (p.a) f = __fadd_rn(__fmul_rn(__ldg(p.a + ch), f), __ldg(p.b + ch));

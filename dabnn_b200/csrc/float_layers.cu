@@ -118,7 +118,9 @@ int elementwise_chain(const float* x, const float* a, const float* b, const floa
 // IDX is the type of the flat output index: 32-bit whenever the tensor allows it, because the four
 // divisions that turn it into (image, y, x, channel group) cost several times more in 64 bits than the
 // nine loads they lead to.
-template <int VEC, bool IS_MAX, typename IDX>
+// WIDE: the taps of a window row are loaded eight at a time before they are folded (a separate instantiation: its
+// registers would cost the small windows their occupancy).
+template <int VEC, bool IS_MAX, typename IDX, bool WIDE = false>
 __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                    uint64_t* __restrict__ bits, int n, int h, int w, int c_vec,
                                                    int kh, int kw, int pad_h, int pad_w, int stride_h,
@@ -142,20 +144,50 @@ __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in,
             for (int ky = 0; ky < kh; ky++) {
                 const int y = oy * stride_h - pad_h + ky;
                 if (y < 0 || y >= h) continue;
-                for (int kx = 0; kx < kw; kx++) {
-                    const int x = ox * stride_w - pad_w + kx;
-                    if (x < 0 || x >= w) continue;
-                    const float* src = in + ((((size_t)img * h + y) * w + x) * c_vec + cc) * VEC;
-                    float t[VEC];
-                    if (VEC == 4) {
-                        const float4 f = __ldg(reinterpret_cast<const float4*>(src));
-                        t[0] = f.x; t[1 % VEC] = f.y; t[2 % VEC] = f.z; t[3 % VEC] = f.w;
-                    } else {
-                        t[0] = __ldg(src);
+                if (!WIDE) {   // small windows: tap by tap
+                    for (int kx = 0; kx < kw; kx++) {
+                        const int x = ox * stride_w - pad_w + kx;
+                        if (x < 0 || x >= w) continue;
+                        const float* src = in + ((((size_t)img * h + y) * w + x) * c_vec + cc) * VEC;
+                        float t[VEC];
+                        if (VEC == 4) {
+                            const float4 f = __ldg(reinterpret_cast<const float4*>(src));
+                            t[0] = f.x; t[1 % VEC] = f.y; t[2 % VEC] = f.z; t[3 % VEC] = f.w;
+                        } else {
+                            t[0] = __ldg(src);
+                        }
+#pragma unroll
+                        for (int q = 0; q < VEC; q++) acc[q] = IS_MAX ? (acc[q] < t[q] ? t[q] : acc[q]) : __fadd_rn(acc[q], t[q]);
+                        cnt++;
+                    }
+                    continue;
+                }
+                // the taps of a wide window row are loaded eight at a time before they are folded (in the reference's order):
+                // the 7x7 head pool would otherwise wait for one load per tap
+                for (int kx0 = 0; kx0 < kw; kx0 += 8) {
+                    float t[8][VEC];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int x = ox * stride_w - pad_w + kx0 + u;
+                        if (kx0 + u < kw && x >= 0 && x < w) {
+                            const float* src = in + ((((size_t)img * h + y) * w + x) * c_vec + cc) * VEC;
+                            if (VEC == 4) {
+                                const float4 f = __ldg(reinterpret_cast<const float4*>(src));
+                                t[u][0] = f.x; t[u][1 % VEC] = f.y; t[u][2 % VEC] = f.z; t[u][3 % VEC] = f.w;
+                            } else {
+                                t[u][0] = __ldg(src);
+                            }
+                        }
                     }
 #pragma unroll
-                    for (int q = 0; q < VEC; q++) acc[q] = IS_MAX ? (acc[q] < t[q] ? t[q] : acc[q]) : __fadd_rn(acc[q], t[q]);
-                    cnt++;
+                    for (int u = 0; u < 8; u++) {
+                        const int x = ox * stride_w - pad_w + kx0 + u;
+                        if (kx0 + u < kw && x >= 0 && x < w) {
+#pragma unroll
+                            for (int q = 0; q < VEC; q++) acc[q] = IS_MAX ? (acc[q] < t[u][q] ? t[u][q] : acc[q]) : __fadd_rn(acc[q], t[u][q]);
+                            cnt++;
+                        }
+                    }
                 }
             }
             if (!IS_MAX) {
@@ -262,7 +294,10 @@ static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h
     }
     if (vec) {
         const size_t total = (size_t)n * oh * ow * (c / 4);
-        if (total + (size_t)grid_for(total, 256) * 256 + 32 < (1ull << 32))   // the grid-stride loop must not wrap either
+        if (kw > 4 && total < (1ull << 31))   // wide windows (the 7x7 head pool): a window row's loads in flight together
+            pool_kernel<4, IS_MAX, uint32_t, true><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
+                                                                                             pad_w, stride_h, stride_w, oh, ow);
+        else if (total + (size_t)grid_for(total, 256) * 256 + 32 < (1ull << 32))   // the grid-stride loop must not wrap either
             pool_kernel<4, IS_MAX, uint32_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
                                                                                        pad_w, stride_h, stride_w, oh, ow);
         else
@@ -660,7 +695,7 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     const FconvParams prm{in, weight, bias, a, b, out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w,
                           stride_h, stride_w, dil_h, dil_w, oh, ow};
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    if (kh == 1 && kw == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 && cin % FG_CHUNK == 0 && cout % 16 == 0 &&
+    if (kh == 1 && kw == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 && cin % FG_CHUNK == 0 && cout % 4 == 0 &&
         al16(in) && al16(weight) && al16(out)) {
         // a 1x1 convolution is a GEMM over [pixels][cin]: TMA-fed (fconv_gemm.cuh)
         static thread_local int gemm_device = -1, gemm_stages = 0;
@@ -677,16 +712,19 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
                 DABNN_CUDA_OK(cudaFuncSetAttribute(fconv_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fg_smem_bytes(gemm_stages)));
             gemm_device = dev;
         }
-        const int Mpx = n * oh * ow;
+        const int Mpx = n * oh * ow, tiles_m = (Mpx + 127) / 128;
+        // channels per work item: as large as leaves every SM a work item
+        int n_blk = FG_N;
+        while (n_blk > 32 && tiles_m * ((cout + n_blk - 1) / n_blk) < sm_count()) n_blk >>= 1;
         CUtensorMap a_map, w_map, o_map;
-        const unsigned box[2] = {32, 128};
+        const unsigned box[2] = {32, 128}, wbox[2] = {32, (unsigned)n_blk};
         const unsigned long long adims[2] = {(unsigned long long)cin, (unsigned long long)Mpx}, astr[1] = {(unsigned long long)cin * 4};
         const unsigned long long wdims[2] = {(unsigned long long)cin, (unsigned long long)cout};
         const unsigned long long odims[2] = {(unsigned long long)cout, (unsigned long long)Mpx}, ostr[1] = {(unsigned long long)cout * 4};
         if (gemm_stages >= 2 && make_f32_tensor_map(&a_map, const_cast<float*>(in), 2, adims, astr, box) &&
-            make_f32_tensor_map(&w_map, const_cast<float*>(weight), 2, wdims, astr, box) && make_f32_tensor_map(&o_map, out, 2, odims, ostr, box)) {
-            const int items = ((Mpx + 127) / 128) * ((cout + FG_N - 1) / FG_N);
-            fconv_gemm_kernel<<<std::min(items, sm_count()), FG_THREADS, fg_smem_bytes(gemm_stages), stream>>>(prm, Mpx, gemm_stages, a_map, w_map, o_map);
+            make_f32_tensor_map(&w_map, const_cast<float*>(weight), 2, wdims, astr, wbox) && make_f32_tensor_map(&o_map, out, 2, odims, ostr, box)) {
+            const int items = tiles_m * ((cout + n_blk - 1) / n_blk);
+            fconv_gemm_kernel<<<std::min(items, sm_count()), FG_THREADS, fg_smem_bytes(gemm_stages), stream>>>(prm, Mpx, gemm_stages, n_blk, a_map, w_map, o_map);
             return check_launch("fconv_gemm_kernel");
         }
     }

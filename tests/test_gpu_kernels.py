@@ -524,6 +524,9 @@ def test_fconv_window_reading_kernel(ops, port, n, h, cin, cout, ks, pad, bias, 
     (150, 7, 256, 512, True),     # four channel blocks, eight K chunks
     (3, 9, 32, 48, True),         # one K chunk, a 48-channel block (a 16-channel tail box)
     (2, 11, 96, 208, False),      # 208 = 128 + 80 channels
+    (128, 1, 512, 1000, True),    # the classifier: one pixel tile, 32-channel work items, a last block of 8 channels
+    (5, 3, 64, 20, True),         # a channel count that is no multiple of 16
+    (1024, 1, 512, 1000, False),
 ])
 def test_fconv_1x1_gemm_kernel(ops, port, n, h, cin, cout, bias):
     """1x1 float convolutions (the downsample branches: dabnn/fconv.h:14-76 with a 1x1 kernel) run on the TMA-fed GEMM
