@@ -79,6 +79,7 @@ _SIGNATURES = {
     "dabnn_last_engine": [],
     "dabnn_debug_raise_engine_status": [_i, _i],
     "dabnn_debug_set_halo": [_i],
+    "dabnn_debug_set_launch_overlap": [_i],
     "dabnn_last_error": [],
     "dabnn_version": [],
     "dabnn_device_count": [],

@@ -8,6 +8,7 @@
 
 namespace dabnn {
 
+int g_overlap_launches = 1;
 static thread_local std::string g_last_error;
 
 void set_error(const std::string& msg) { g_last_error = msg; }
@@ -76,6 +77,10 @@ bool make_u8_tensor_map(CUtensorMap_st* map, const unsigned char* base, int rank
 }  // namespace dabnn
 
 extern "C" const char* dabnn_last_error(void) { return dabnn::g_last_error.c_str(); }
+extern "C" int dabnn_debug_set_launch_overlap(int on) {
+    dabnn::g_overlap_launches = on != 0;
+    return DABNN_OK;
+}
 extern "C" const char* dabnn_version(void) { return "dabnn_b200 0.1 (sm_100a)"; }
 extern "C" int dabnn_device_count(void) {
     int n = 0;

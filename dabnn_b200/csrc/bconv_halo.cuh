@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
     const unsigned char* wsrc = p.w_img + (size_t)blockIdx.y * nboxes * wbox_bytes;   // this channel block's box images
+    if (warp != 1) grid_dependency_wait();   // the weight loader reads constants only and may run ahead of the previous kernel's end
 
     if (warp == 0) {
         // =========================== halo loads: one lane ===========================

@@ -232,8 +232,8 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         const int per_n = std::max(1, sm_count() / tiles_n);
         const int nunits = hp.pair ? (hp.ntiles + 1) / 2 : hp.ntiles;
         dim3 grid(std::min(nunits, per_n), tiles_n);
-        if (hp.pair) bconv_halo_kernel<true><<<grid, HL_THREADS, hp.smem, stream>>>(q, in_map, out_map);
-        else bconv_halo_kernel<false><<<grid, HL_THREADS, hp.smem, stream>>>(q, in_map, out_map);
+        if (hp.pair) launch_overlapped(bconv_halo_kernel<true>, grid, HL_THREADS, hp.smem, stream, q, in_map, out_map);
+        else launch_overlapped(bconv_halo_kernel<false>, grid, HL_THREADS, hp.smem, stream, q, in_map, out_map);
         return check_launch("bconv_halo_kernel");
     }
     CUtensorMap in_maps[2], out_map{};
@@ -255,8 +255,8 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     const int per_n = std::max(1, sm_count() / tiles_n);
     const int nunits = pl.pair ? (pl.ntiles + 1) / 2 : pl.ntiles;
     dim3 grid(std::min(nunits, per_n), tiles_n);
-    if (pl.pair) bconv_u8_kernel<true><<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
-    else bconv_u8_kernel<false><<<grid, U8_THREADS, pl.smem, stream>>>(p, in_maps[0], in_maps[1], out_map);
+    if (pl.pair) launch_overlapped(bconv_u8_kernel<true>, grid, U8_THREADS, pl.smem, stream, p, in_maps[0], in_maps[1], out_map);
+    else launch_overlapped(bconv_u8_kernel<false>, grid, U8_THREADS, pl.smem, stream, p, in_maps[0], in_maps[1], out_map);
     return check_launch("bconv_u8_kernel");
 }
 

@@ -5,6 +5,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <utility>
 
 #include "../../include/dabnn_b200.h"
 
@@ -34,6 +35,24 @@ inline int check_launch(const char* what) {
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+
+// Launches of consecutive layers overlap at their seams: a kernel launched with launch_overlapped may begin while the
+// kernel before it in the stream is still draining, runs its set-up (shared memory, tensor memory, barriers, constant
+// weights) and then calls grid_dependency_wait(), which returns once everything launched before it has completed and is
+// visible.  Only kernels that make that call before they touch activations may be launched this way.
+extern int g_overlap_launches;   // 1 (default): on; dabnn_debug_set_launch_overlap
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <class... KArgs, class... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_overlap_launches ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 inline int conv_out_dim(int in, int pad, int dil, int k, int stride) {
     return (in + 2 * pad - (dil * (k - 1) + 1)) / stride + 1;

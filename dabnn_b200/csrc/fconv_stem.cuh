@@ -162,21 +162,33 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
         chan_b[tid] = (in && p.a) ? __ldg(p.b + n0 + tid) : 0.f;
     }
     // resident weights, K order (ky, kx < kxp, c < 4): element (n, k) -> (n / 8) * w_sbo + (k / 4) * 128 + (n % 8) * 16 + (k % 4) * 4
-    for (int idx = tid; idx < FS_N * g.kpad; idx += FS_THREADS) {
-        const int n = idx / g.kpad, k = idx - n * g.kpad;
-        const int c = k & 3, tap = k >> 2, ky = tap / g.kxp, kx = tap - ky * g.kxp;
-        const float v = (n < n_this && kx < p.kw && c < p.cin) ? __ldg(p.wgt + ((size_t)(n0 + n) * p.kh * p.kw + ky * p.kw + kx) * p.cin + c) : 0.f;
-        uint32_t hi, lo;
-        split_tf32(v, hi, lo);
-        const int off = (n >> 3) * w_sbo + (k >> 2) * 128 + (n & 7) * 16 + (k & 3) * 4;
-        *reinterpret_cast<uint32_t*>(wbase + off) = hi;
-        *reinterpret_cast<uint32_t*>(wbase + w_half + off) = lo;
+    // (four elements per thread and step, their loads issued together: the set-up is a fixed cost of every launch)
+    for (int idx0 = tid; idx0 < FS_N * g.kpad; idx0 += 4 * FS_THREADS) {
+        float v[4];
+        int off[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int idx = idx0 + u * FS_THREADS;
+            const int n = idx / g.kpad, k = idx - n * g.kpad;
+            const int c = k & 3, tap = k >> 2, ky = tap / g.kxp, kx = tap - ky * g.kxp;
+            v[u] = (idx < FS_N * g.kpad && n < n_this && kx < p.kw && c < p.cin) ? __ldg(p.wgt + ((size_t)(n0 + n) * p.kh * p.kw + ky * p.kw + kx) * p.cin + c) : 0.f;
+            off[u] = idx < FS_N * g.kpad ? (n >> 3) * w_sbo + (k >> 2) * 128 + (n & 7) * 16 + (k & 3) * 4 : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (off[u] < 0) continue;
+            uint32_t hi, lo;
+            split_tf32(v[u], hi, lo);
+            *reinterpret_cast<uint32_t*>(wbase + off[u]) = hi;
+            *reinterpret_cast<uint32_t*>(wbase + w_half + off[u]) = lo;
+        }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    grid_dependency_wait();   // everything above touched constants only; the images and the output buffers come next
 
     if (tid < FS_CONVERTERS) {
         // =========================== converters: thread = pixel x of an input row ===========================

@@ -128,6 +128,7 @@ __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in,
     const IDX total = (IDX)n * oh * ow * c_vec;
     const IDX stride = (IDX)gridDim.x * blockDim.x;
     const IDX bound = bits ? (total + 31) / 32 * 32 : total;
+    grid_dependency_wait();
     for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < bound; i += stride) {
         const bool valid = i < total;
         unsigned nib = 0;
@@ -295,11 +296,11 @@ static int launch_pool(const float* in, float* out, uint64_t* bits, int n, int h
     if (vec) {
         const size_t total = (size_t)n * oh * ow * (c / 4);
         if (kw > 4 && total < (1ull << 31))   // wide windows (the 7x7 head pool): a window row's loads in flight together
-            pool_kernel<4, IS_MAX, uint32_t, true><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
-                                                                                             pad_w, stride_h, stride_w, oh, ow);
+            launch_overlapped(pool_kernel<4, IS_MAX, uint32_t, true>, grid_for(total, 256), 256, 0, stream, in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
+                              pad_w, stride_h, stride_w, oh, ow);
         else if (total + (size_t)grid_for(total, 256) * 256 + 32 < (1ull << 32))   // the grid-stride loop must not wrap either
-            pool_kernel<4, IS_MAX, uint32_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
-                                                                                       pad_w, stride_h, stride_w, oh, ow);
+            launch_overlapped(pool_kernel<4, IS_MAX, uint32_t>, grid_for(total, 256), 256, 0, stream, in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
+                              pad_w, stride_h, stride_w, oh, ow);
         else
             pool_kernel<4, IS_MAX, size_t><<<grid_for(total, 256), 256, 0, stream>>>(in, out, bits, n, h, w, c / 4, kh, kw, pad_h,
                                                                                      pad_w, stride_h, stride_w, oh, ow);
@@ -666,10 +667,10 @@ int fconv_pool_impl(const float* in, const float* weight, const float* bias, con
     const int smem = fs_smem_bytes(geom);
     const CUtensorMap no_map{};
     switch (geom.kxp / 2) {
-        case 1: fconv_stem_kernel<1, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
-        case 2: fconv_stem_kernel<2, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
-        case 3: fconv_stem_kernel<3, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
-        default: fconv_stem_kernel<4, true><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, no_map, pool_out, pool_u8); break;
+        case 1: launch_overlapped(fconv_stem_kernel<1, true>, sgrid, FS_THREADS, smem, stream, prm, geom, no_map, pool_out, pool_u8); break;
+        case 2: launch_overlapped(fconv_stem_kernel<2, true>, sgrid, FS_THREADS, smem, stream, prm, geom, no_map, pool_out, pool_u8); break;
+        case 3: launch_overlapped(fconv_stem_kernel<3, true>, sgrid, FS_THREADS, smem, stream, prm, geom, no_map, pool_out, pool_u8); break;
+        default: launch_overlapped(fconv_stem_kernel<4, true>, sgrid, FS_THREADS, smem, stream, prm, geom, no_map, pool_out, pool_u8); break;
     }
     return check_launch("fconv_stem_kernel (pooled)");
 }
@@ -724,7 +725,8 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
         if (gemm_stages >= 2 && make_f32_tensor_map(&a_map, const_cast<float*>(in), 2, adims, astr, box) &&
             make_f32_tensor_map(&w_map, const_cast<float*>(weight), 2, wdims, astr, wbox) && make_f32_tensor_map(&o_map, out, 2, odims, ostr, box)) {
             const int items = tiles_m * ((cout + n_blk - 1) / n_blk);
-            fconv_gemm_kernel<<<std::min(items, sm_count()), FG_THREADS, fg_smem_bytes(gemm_stages), stream>>>(prm, Mpx, gemm_stages, n_blk, a_map, w_map, o_map);
+            launch_overlapped(fconv_gemm_kernel, std::min(items, sm_count()), FG_THREADS, fg_smem_bytes(gemm_stages), stream, prm, Mpx, gemm_stages, n_blk, a_map,
+                              w_map, o_map);
             return check_launch("fconv_gemm_kernel");
         }
     }
@@ -739,10 +741,10 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
             dim3 sgrid(std::min(geom.rows_total, std::max(1, sm_count() / ny)), ny);
             const int smem = fs_smem_bytes(geom);
             switch (geom.kxp / 2) {
-                case 1: fconv_stem_kernel<1, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
-                case 2: fconv_stem_kernel<2, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
-                case 3: fconv_stem_kernel<3, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
-                default: fconv_stem_kernel<4, false><<<sgrid, FS_THREADS, smem, stream>>>(prm, geom, out_map, nullptr, nullptr); break;
+                case 1: launch_overlapped(fconv_stem_kernel<1, false>, sgrid, FS_THREADS, smem, stream, prm, geom, out_map, nullptr, nullptr); break;
+                case 2: launch_overlapped(fconv_stem_kernel<2, false>, sgrid, FS_THREADS, smem, stream, prm, geom, out_map, nullptr, nullptr); break;
+                case 3: launch_overlapped(fconv_stem_kernel<3, false>, sgrid, FS_THREADS, smem, stream, prm, geom, out_map, nullptr, nullptr); break;
+                default: launch_overlapped(fconv_stem_kernel<4, false>, sgrid, FS_THREADS, smem, stream, prm, geom, out_map, nullptr, nullptr); break;
             }
             return check_launch("fconv_stem_kernel");
         }

@@ -300,6 +300,10 @@ int dabnn_last_engine(void);
  * the default (1) runs them on the kernel that loads a tile's halo once.  Both give identical results. */
 int dabnn_debug_set_halo(int mode);
 
+/* Tuning hook: 0 launches every kernel strictly after the one before it; the default (1) lets the hot kernels of a Net
+ * begin their set-up while the previous kernel drains (programmatic dependent launch).  Results are identical. */
+int dabnn_debug_set_launch_overlap(int on);
+
 /* Test hook: stores `code` in status word `which` (0 packed-bit contraction, 1 float convolution, 2 byte-activation
  * engine) exactly as a kernel whose bounded wait gave up would, so that the reporting path can be exercised
  * without stalling a GPU. */
