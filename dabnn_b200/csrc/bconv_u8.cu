@@ -213,14 +213,16 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     }
     HaloPlan hp;
     if (halo_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, hp)) {   // 3x3 stride 1: every input byte enters the SM once per tile
-        CUtensorMap in_map, out_map{};
+        CUtensorMap in_map, out_map{}, sc_map{};
         DABNN_REQUIRE(halo_input_map(in_u8, n, h, w, cin, hp, &in_map), DABNN_ERR_CUDA, "bconv_u8: cannot encode the halo's tensor map");
-        if (out_f32) {
+        {
             const unsigned long long dims[3] = {(unsigned long long)cout, (unsigned long long)hp.OH * hp.OW, (unsigned long long)n};
             const unsigned long long strides[2] = {(unsigned long long)cout * 4, (unsigned long long)cout * 4 * hp.OH * hp.OW};
             const unsigned box[3] = {32u, (unsigned)(hp.rows * hp.OW), 1u};
-            DABNN_REQUIRE(make_f32_tensor_map(&out_map, out_f32, 3, dims, strides, box), DABNN_ERR_CUDA,
+            DABNN_REQUIRE(!out_f32 || make_f32_tensor_map(&out_map, out_f32, 3, dims, strides, box), DABNN_ERR_CUDA,
                           "bconv_u8: cannot encode the output's tensor map");
+            DABNN_REQUIRE(!shortcut || make_f32_tensor_map(&sc_map, const_cast<float*>(shortcut), 3, dims, strides, box), DABNN_ERR_CUDA,
+                          "bconv_u8: cannot encode the shortcut's tensor map");
         }
         HaloParams q{};
         q.w_img = w_img; q.a = a; q.b = b; q.shortcut = shortcut; q.out = out_f32; q.out_u8 = out_u8; q.out_bits = out_bits;
@@ -232,8 +234,8 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         const int per_n = std::max(1, sm_count() / tiles_n);
         const int nunits = hp.pair ? (hp.ntiles + 1) / 2 : hp.ntiles;
         dim3 grid(std::min(nunits, per_n), tiles_n);
-        if (hp.pair) launch_overlapped(bconv_halo_kernel<true>, grid, HL_THREADS, hp.smem, stream, q, in_map, out_map);
-        else launch_overlapped(bconv_halo_kernel<false>, grid, HL_THREADS, hp.smem, stream, q, in_map, out_map);
+        if (hp.pair) launch_overlapped(bconv_halo_kernel<true>, grid, HL_THREADS, hp.smem, stream, q, in_map, out_map, sc_map);
+        else launch_overlapped(bconv_halo_kernel<false>, grid, HL_THREADS, hp.smem, stream, q, in_map, out_map, sc_map);
         return check_launch("bconv_halo_kernel");
     }
     CUtensorMap in_maps[2], out_map{};
