@@ -238,14 +238,16 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         else launch_overlapped(bconv_halo_kernel<false>, grid, HL_THREADS, hp.smem, stream, q, in_map, out_map, sc_map);
         return check_launch("bconv_halo_kernel");
     }
-    CUtensorMap in_maps[2], out_map{};
+    CUtensorMap in_maps[2], out_map{}, sc_map{};
     DABNN_REQUIRE(u8_input_maps(in_u8, n, h, w, cin, stride_h, pl, in_maps), DABNN_ERR_CUDA, "bconv_u8: cannot encode the input's tensor map");
-    if (out_f32) {
+    {
         const unsigned long long dims[3] = {(unsigned long long)cout, (unsigned long long)pl.OH * pl.OW, (unsigned long long)n};
         const unsigned long long strides[2] = {(unsigned long long)cout * 4, (unsigned long long)cout * 4 * pl.OH * pl.OW};
         const unsigned box[3] = {32u, (unsigned)(pl.rows * pl.OW), (unsigned)pl.imgs};
-        DABNN_REQUIRE(make_f32_tensor_map(&out_map, out_f32, 3, dims, strides, box), DABNN_ERR_CUDA,
+        DABNN_REQUIRE(!out_f32 || make_f32_tensor_map(&out_map, out_f32, 3, dims, strides, box), DABNN_ERR_CUDA,
                       "bconv_u8: cannot encode the output's tensor map");
+        DABNN_REQUIRE(!shortcut || make_f32_tensor_map(&sc_map, const_cast<float*>(shortcut), 3, dims, strides, box), DABNN_ERR_CUDA,
+                      "bconv_u8: cannot encode the shortcut's tensor map");
     }
     U8Params p{};
     p.w_img = w_img; p.a = a; p.b = b; p.shortcut = shortcut; p.out = out_f32; p.out_u8 = out_u8; p.out_bits = out_bits;
@@ -257,8 +259,8 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     const int per_n = std::max(1, sm_count() / tiles_n);
     const int nunits = pl.pair ? (pl.ntiles + 1) / 2 : pl.ntiles;
     dim3 grid(std::min(nunits, per_n), tiles_n);
-    if (pl.pair) launch_overlapped(bconv_u8_kernel<true>, grid, U8_THREADS, pl.smem, stream, p, in_maps[0], in_maps[1], out_map);
-    else launch_overlapped(bconv_u8_kernel<false>, grid, U8_THREADS, pl.smem, stream, p, in_maps[0], in_maps[1], out_map);
+    if (pl.pair) launch_overlapped(bconv_u8_kernel<true>, grid, U8_THREADS, pl.smem, stream, p, in_maps[0], in_maps[1], out_map, sc_map);
+    else launch_overlapped(bconv_u8_kernel<false>, grid, U8_THREADS, pl.smem, stream, p, in_maps[0], in_maps[1], out_map, sc_map);
     return check_launch("bconv_u8_kernel");
 }
 

@@ -137,9 +137,9 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
 template <bool PAIR>   // PAIR: a unit of work is two pixel tiles sharing the weight stages (p.pair)
 __global__ void __launch_bounds__(U8_THREADS, 1)
     bconv_u8_kernel(const U8Params p, const __grid_constant__ CUtensorMap in_map0, const __grid_constant__ CUtensorMap in_map1,
-                    const __grid_constant__ CUtensorMap out_map) {
+                    const __grid_constant__ CUtensorMap out_map, const __grid_constant__ CUtensorMap sc_map) {
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_acc_full[U8_ACCS], bar_acc_empty[U8_ACCS], bar_w;
+    __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_acc_full[U8_ACCS], bar_acc_empty[U8_ACCS], bar_w, sc_full[U8_MAX_STILES];
     __shared__ uint32_t tmem_base_s;
     __shared__ int s_abort, epi_abort;
     __shared__ __align__(16) int popw[TC5_MAX_N];
@@ -172,6 +172,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         for (int i = 0; i < p.stages; i++) { mbar_init(&bar_full[i], 1); mbar_init(&bar_empty[i], 1); }
         for (int i = 0; i < U8_ACCS; i++) { mbar_init(&bar_acc_full[i], 1); mbar_init(&bar_acc_empty[i], U8_EPI_WARPS); }
         mbar_init(&bar_w, 1);
+        for (int i = 0; i < U8_MAX_STILES; i++) mbar_init(&sc_full[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::);
         s_abort = 0;
         epi_abort = 0;
@@ -342,36 +343,32 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             base = ((long long)img0 * p.OH + oh0) * p.OW;
             nvalid = p.imgs > 1 ? min(p.imgs, p.B - img0) * ohw : min(p.rows, p.OH - oh0) * p.OW;
         };
-        // Prefetch cursor: the block whose shortcut is copied next, walked incrementally.  A thread copies 16 bytes of
-        // rows pr0, pr0 + 32, ...: its position inside a staging tile and inside a pixel row never changes.
-        const int pr0 = et >> 4, pc4 = (et & 15) * 4;
-        const uint32_t poff = (pc4 >> 5) * sbox_bytes + pr0 * 128 + ((((pc4 & 31) >> 2) ^ (pr0 & 7)) << 4);
-        int pkb = 0, ptile = first_tile, pti = 0, pblk = 0, pst = 0, pnvalid = 0, pdummy0, pdummy1;
-        long long pbase = 0;
-        if (ptile < p.ntiles) tile_span(ptile, pbase, pnvalid, pdummy0, pdummy1);
-        auto prefetch_next = [&]() {
+        // The shortcut of block kb + stiles - 1 is fetched into the staging tile that block kb - 1 has left, by one thread and
+        // two tiled TMA loads (the tile's layout is the one the tensor store reads, so the sum happens in place).
+        int pkb = 0, ptile = first_tile, pti = 0, pblk = 0, pst = 0;
+        auto prefetch_next = [&]() {   // thread et == 0 only
             if (p.shortcut && pkb < total_blocks) {
-                const int cb = pblk * 64;
-                if (pc4 < n_this - cb) {
-                    const float* src = p.shortcut + (pbase + pr0) * p.N + n0 + cb + pc4;
-                    const uint32_t dst = sbuf0_addr + pst * stile_bytes + poff;
-#pragma unroll
-                    for (int j = 0; j < 2048 / U8_EPILOGUE; j++)
-                        if (pr0 + j * (U8_EPILOGUE / 16) < pnvalid)
-                            cp_async16(dst + j * (U8_EPILOGUE / 16) * 128, src + (long long)j * (U8_EPILOGUE / 16) * p.N, 16);
-                }
+                const int tq = ptile / p.tiles_per_img;
+                const int pimg = tq * p.imgs, poh0 = (ptile - tq * p.tiles_per_img) * p.rows;
+                const int cb = pblk * 64, boxes = n_this - cb > 32 ? 2 : 1;
+                const uint32_t bar = smem_u32(&sc_full[pst]), dst = sbuf0_addr + pst * stile_bytes;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(boxes * box_px * 128)) : "memory");
+                for (int hb = 0; hb < boxes; hb++)
+                    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                                 ::"r"(dst + hb * sbox_bytes), "l"(reinterpret_cast<uint64_t>(&sc_map)), "r"(n0 + cb + hb * 32), "r"(poh0 * p.OW), "r"(pimg),
+                                   "r"(bar) : "memory");
             }
-            cp_async_commit();
             pkb++;
             if (++pst == p.stiles) pst = 0;
             if (++pblk == nblk) {
                 pblk = 0;
                 ptile = next_tile(ptile, pti++);
-                if (ptile < p.ntiles) tile_span(ptile, pbase, pnvalid, pdummy0, pdummy1);
             }
         };
-        for (int d = 0; d + 1 < p.stiles; d++) prefetch_next();
+        if (et == 0)
+            for (int d = 0; d + 1 < p.stiles; d++) prefetch_next();
         bool okw = true;
+        uint32_t sc_par = 0;
         int tile = first_tile, ti = 0, blk = 0, st_idx = 0, accbuf = 0, accuse = 0, nvalid = 0, img0 = 0, oh0 = 0;
         long long base = 0;
         for (int kb = 0; kb < total_blocks; kb++) {
@@ -379,10 +376,18 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             const int cb = blk * 64;
             const int width = min(64, n_this - cb);
             const uint32_t sb = sbuf0_addr + st_idx * stile_bytes;
-            if (p.stiles == 3) cp_async_wait<1>(); else cp_async_wait<0>();   // my copies of block kb have landed
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // my tensor store of block kb-1 has read its tile
-            asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");    // everybody's have: block kb-1's tile is idle
-            prefetch_next();
+            if (et == 0) {
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the tensor stores of block kb - 1 have read its tile: it is idle
+                prefetch_next();
+            }
+            if (p.shortcut && okw) {   // the shortcut of block kb has landed in its tile
+                okw = __all_sync(0xffffffffu, mbar_wait<100>(&sc_full[st_idx], sc_par, abort_flag));
+                if (!okw) {
+                    atomicCAS(&g_u8_status, 0, 24);
+                    s_abort = 1;
+                    epi_abort = 1;
+                }
+            }
             const bool mine = width > hq * 16;                               // this thread's 16 columns exist
             if (blk == 0 && okw) {
                 okw = __all_sync(0xffffffffu, mbar_wait<200>(&bar_acc_full[accbuf], accuse & 1, abort_flag));
@@ -449,14 +454,15 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
             if (epi_abort) break;
             // ---- write-out: one tensor store per 32-channel box; pixels beyond the image / batch and channels beyond N are clipped ----
-            if (p.out && (et == 0 || (et == 32 && width > 32))) {
-                const int hb = et >> 5;
-                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
-                             ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + cb + hb * 32), "r"(oh0 * p.OW), "r"(img0),
-                               "r"(sb + hb * sbox_bytes) : "memory");
+            if (et == 0) {
+                if (p.out)
+                    for (int hb = 0; hb < (width > 32 ? 2 : 1); hb++)
+                        asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                                     ::"l"(reinterpret_cast<uint64_t>(&out_map)), "r"(n0 + cb + hb * 32), "r"(oh0 * p.OW), "r"(img0),
+                                       "r"(sb + hb * sbox_bytes) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");   // every thread, every block: group k is block k's store
-            if (++st_idx == p.stiles) st_idx = 0;
+            if (++st_idx == p.stiles) { st_idx = 0; sc_par ^= 1u; }
             if (++blk == nblk) {
                 blk = 0;
                 tile = next_tile(tile, ti++);
@@ -464,7 +470,6 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             }
         }
         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-        cp_async_wait<0>();
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
