@@ -45,6 +45,8 @@ _SIGNATURES = {
     "dabnn_bconv_u8_weight_bytes": [_i, _i],
     "dabnn_bconv_u8_expand_weights": [_p, _z, _i, _i, _p, _p],
     "dabnn_bconv_u8_block": [_p, _p, _p, _p, _p, _p, _p, _p] + [_i] * 11 + [_p],
+    "dabnn_bconv_u8_block_pooled_supported": [_i] * 11,
+    "dabnn_bconv_u8_block_pooled": [_p, _p, _p, _p, _p, _p, _p, _p, _p] + [_i] * 11 + [_p],
     "dabnn_affine": [_p, _p, _p, _z, _i, _p],
     "dabnn_add": [_p, _p, _z, _p],
     "dabnn_relu": [_p, _z, _p],

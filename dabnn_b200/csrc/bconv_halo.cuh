@@ -16,6 +16,11 @@
 // row, tile, tap, so a halo buffer is released after its 18 (36 with two tiles: each its own) MMAs and the ring refills
 // while the other groups compute.
 //
+// A block whose result also feeds a 2x2 stride-2 average pooling (the downsample shortcut of the next stage: reference
+// layers/AvePool.cpp:84) can write the pooled tensor as well: tiles are then an even number of output rows, and after a
+// block of 64 channels is staged every thread folds one pooled pixel x four channels out of the staging tile, in the
+// reference's tap order, sum first, then the division.
+//
 // Warps: 0 halo loads, 1 weight loads, 2 MMA issue (one lane each), 3 .. 18 epilogue (as in bconv_u8.cuh, with the
 // accumulator row -> pixel mapping above).  Every wait is bounded; a wait that gives up records a code in the
 // byte-activation engine's status word (21 halo loader, 25 weight loader, 22 / 23 / 26 MMA thread waiting for an
@@ -36,6 +41,7 @@ struct HaloParams {
     float* out;
     unsigned char* out_u8;
     uint64_t* out_bits;
+    float* pool_out;              // or null: fp32 [B][OH / 2][OW / 2][N], the 2x2 stride-2 average pooling of `out` (OH, OW, rows even)
     int B, OH, OW, N;
     int cw;                       // 64-channel groups of the input
     int P;                        // halo pitch in pixels: OW + 2
@@ -378,6 +384,25 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
             asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");   // results of block kb are staged (or abort decided)
             if (epi_abort) break;
             // ---- write-out: one tensor store per 32-channel box; pixels beyond the image and channels beyond N are clipped ----
+            if (p.pool_out) {
+                // 2x2 average pooling of the staged block: task = pooled pixel (prow, pcol) x four channels
+                const int pw = p.OW >> 1, q = et & 15, pp = et >> 4;
+                const int prow = pp / pw, pcol = pp - prow * pw;
+                if (prow < (p.rows >> 1) && (2 * prow + 1) * p.OW < nvalid && q * 4 < width) {
+                    const uint32_t box = sb + (q >> 3) * sbox_bytes;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int tap = 0; tap < 4; tap++) {   // the reference's order: (0,0), (0,1), (1,0), (1,1)
+                        const int mm = (2 * prow + (tap >> 1)) * p.OW + 2 * pcol + (tap & 1);
+                        const float4 t = lds128f(box + mm * 128 + (((q & 7) ^ (mm & 7)) << 4));
+                        acc.x = __fadd_rn(acc.x, t.x); acc.y = __fadd_rn(acc.y, t.y); acc.z = __fadd_rn(acc.z, t.z); acc.w = __fadd_rn(acc.w, t.w);
+                    }
+                    const size_t e = ((((size_t)img0 * (p.OH >> 1) + (oh0 >> 1) + prow) * pw) + pcol) * p.N + n0 + cb + q * 4;
+                    *reinterpret_cast<float4*>(p.pool_out + e) =
+                        make_float4(__fdiv_rn(acc.x, 4.f), __fdiv_rn(acc.y, 4.f), __fdiv_rn(acc.z, 4.f), __fdiv_rn(acc.w, 4.f));
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(U8_EPILOGUE) : "memory");   // the tile has been read: it may be given back
+            }
             if (et == 0) {
                 if (p.out)
                     for (int hb = 0; hb < (width > 32 ? 2 : 1); hb++)

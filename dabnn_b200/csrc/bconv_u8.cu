@@ -97,15 +97,21 @@ struct HaloPlan {
 
 int g_halo_mode = 1;   // 0: never, 1: wherever the shape allows (dabnn_debug_set_halo)
 
+// even_rows: tiles of an even number of output rows (the block also writes its 2x2 average pooling)
 bool halo_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
-               HaloPlan& pl, int force_pair = -1) {
+               HaloPlan& pl, int force_pair = -1, bool even_rows = false) {
     if (!g_halo_mode || kh != 3 || kw != 3 || pad_h != 1 || pad_w != 1 || stride_h != 1 || stride_w != 1) return false;
     if (n <= 0 || h <= 0 || w <= 0 || cin % 64 || cout % 16 || cin <= 0 || cout <= 0 || w + 2 > 128) return false;
     if ((long long)n * h * w >= (1ll << 31)) return false;
     pl.OH = h; pl.OW = w; pl.P = w + 2;
-    const int rmax = 128 / pl.P;
+    int rmax = 128 / pl.P;
+    if (even_rows) {
+        rmax &= ~1;
+        if (rmax < 2 || (h & 1) || (w & 1) || (rmax / 2) * (w / 2) * 16 > U8_EPILOGUE) return false;
+    }
     pl.tiles_per_img = (h + rmax - 1) / rmax;
     pl.rows = (h + pl.tiles_per_img - 1) / pl.tiles_per_img;
+    if (even_rows) pl.rows = (pl.rows + 1) & ~1;   // still at most rmax, and every tile starts on an even row
     pl.ntiles = n * pl.tiles_per_img;
     // an image smaller than half a tile (7x7: 63 halo pixels of the MMA's 128 rows) is better served by the per-tap kernel,
     // which packs two images into a tile
@@ -187,10 +193,16 @@ int binarize_u8_impl(const float* in, unsigned char* out, size_t count, cudaStre
     return check_launch("binarize_u8_kernel");
 }
 
+bool bconv_u8_pool_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w) {
+    HaloPlan a, b;
+    return halo_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, a, 0, true) &&
+           halo_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, b, 1, true);
+}
+
 int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, const float* a, const float* b,
                         const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, int n, int h, int w,
                         int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, float* pool_out) {
     DABNN_REQUIRE(in_u8 && w_img, DABNN_ERR_ARG, "bconv_u8: null pointer");
     DABNN_REQUIRE((a == nullptr) == (b == nullptr), DABNN_ERR_ARG, "bconv_u8: a and b go together");
     DABNN_REQUIRE(out_f32 || out_u8 || out_bits, DABNN_ERR_ARG, "bconv_u8: no output requested");
@@ -212,7 +224,9 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         configured_device = dev;
     }
     HaloPlan hp;
-    if (halo_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, hp)) {   // 3x3 stride 1: every input byte enters the SM once per tile
+    DABNN_REQUIRE(!pool_out || (al16(pool_out) && halo_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, hp, -1, true)), DABNN_ERR_SHAPE,
+                  "bconv_u8: the pooled output needs a 3x3 stride-1 block with even height and width that the halo kernel takes");
+    if (halo_plan(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, hp, -1, pool_out != nullptr)) {   // 3x3 stride 1: every input byte enters the SM once per tile
         CUtensorMap in_map, out_map{}, sc_map{};
         DABNN_REQUIRE(halo_input_map(in_u8, n, h, w, cin, hp, &in_map), DABNN_ERR_CUDA, "bconv_u8: cannot encode the halo's tensor map");
         {
@@ -226,6 +240,7 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         }
         HaloParams q{};
         q.w_img = w_img; q.a = a; q.b = b; q.shortcut = shortcut; q.out = out_f32; q.out_u8 = out_u8; q.out_bits = out_bits;
+        q.pool_out = pool_out;
         q.B = n; q.OH = hp.OH; q.OW = hp.OW; q.N = cout; q.cw = cin / 64; q.P = hp.P;
         q.rows = hp.rows; q.tiles_per_img = hp.tiles_per_img; q.ntiles = hp.ntiles;
         q.hslots = hp.hslots; q.halo_stride = hp.halo_stride; q.wstages = hp.wstages; q.wb = hp.wb;
@@ -299,6 +314,20 @@ extern "C" size_t dabnn_bconv_u8_weight_bytes(int cout, int kwords) {
 extern "C" int dabnn_bconv_u8_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int kwords,
                                              unsigned char* dst, dabnn_stream_t s) {
     return bconv_u8_expand_weights(weight, weight_words, cout, kwords, dst, static_cast<cudaStream_t>(s));
+}
+
+extern "C" int dabnn_bconv_u8_block_pooled_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w,
+                                                     int stride_h, int stride_w) {
+    return bconv_u8_pool_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w) ? 1 : 0;
+}
+
+extern "C" int dabnn_bconv_u8_block_pooled(const unsigned char* in_u8, const unsigned char* w_expanded, const float* a, const float* b,
+                                           const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, float* pool_out,
+                                           int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                                           int stride_w, dabnn_stream_t s) {
+    DABNN_REQUIRE(pool_out, DABNN_ERR_ARG, "bconv_u8_block_pooled: null pooled output");
+    return bconv_u8_block_impl(in_u8, w_expanded, a, b, shortcut, out_f32, out_u8, out_bits, n, h, w, cin, cout, kh, kw, pad_h,
+                               pad_w, stride_h, stride_w, static_cast<cudaStream_t>(s), pool_out);
 }
 
 extern "C" int dabnn_bconv_u8_block(const unsigned char* in_u8, const unsigned char* w_expanded, const float* a, const float* b,

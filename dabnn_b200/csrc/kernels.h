@@ -40,10 +40,13 @@ size_t bconv_u8_weight_bytes(int cout, int nboxes);
 int bconv_u8_expand_weights(const uint64_t* weight, size_t weight_words, int cout, int nboxes, unsigned char* dst,
                             cudaStream_t stream);
 int binarize_u8_impl(const float* in, unsigned char* out, size_t count, cudaStream_t stream);
+// pool_out (optional): the 2x2 stride-2 average pooling of the fp32 result, fp32 [n][oh / 2][ow / 2][cout], written by the
+// same kernel; bconv_u8_pool_supported tells for which shapes (3x3, stride 1, padding 1, even height and width).
+bool bconv_u8_pool_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w);
 int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, const float* a, const float* b,
                         const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, int n, int h, int w,
                         int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w,
-                        cudaStream_t stream);
+                        cudaStream_t stream, float* pool_out = nullptr);
 int bconv_u8_status(int* status);
 
 // Device addresses (on the current device) of the words in which the tensor-core kernels record the code of a

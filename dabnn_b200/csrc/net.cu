@@ -72,6 +72,7 @@ struct Op {
     OpKind kind;
     std::string cls;  // reference layer class, for per-class timing
     int in = -1, in2 = -1, out = -1;
+    int out2 = -1;    // BConvBlock: the blob that holds the 2x2 / 2 average pooling of out, written by the same kernel
     const TensorInfo *w = nullptr, *bias = nullptr, *a = nullptr, *b = nullptr, *slope = nullptr;
     int kh = 0, kw = 0, pad_h = 0, pad_w = 0, stride_h = 1, stride_w = 1;
     int relu = 0;
@@ -644,6 +645,28 @@ int NetImpl::build() {
             with_packs.push_back(o);
         }
         plan.swap(with_packs);
+        // A 2x2 stride-2 average pooling (the downsample shortcut of a ResNet stage) whose input was last written by a
+        // fused binary block that the halo kernel takes is computed in that block's epilogue, from the tile still in
+        // shared memory: same four operands in the same order, so the same bits, and the block's output is not re-read.
+        for (size_t k = 0; k < plan.size(); k++) {
+            const Op& q = plan[k];
+            if (q.kind != OpKind::AvePool || q.kh != 2 || q.kw != 2 || q.stride_h != 2 || q.stride_w != 2 || q.pad_h || q.pad_w) continue;
+            int writer = -1;
+            bool clean = true;
+            for (size_t i = 0; i < k; i++) {
+                if (plan[i].kind != OpKind::Pack && plan[i].out == q.in) writer = (int)i;
+                if (plan[i].in == q.out || plan[i].in2 == q.out || plan[i].out == q.out || plan[i].out2 == q.out) clean = false;
+            }
+            if (writer < 0 || !clean) continue;
+            Op& o = plan[writer];
+            const Blob& ib = blobs[o.in];
+            if (o.kind != OpKind::BConvBlock || !o.u8 || o.out2 >= 0 ||
+                !bconv_u8_pool_supported(max_batch, ib.h, ib.w, ib.c, blobs[o.out].c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w))
+                continue;
+            o.out2 = q.out;
+            plan.erase(plan.begin() + k);
+            k--;
+        }
     }
 
     // ---- 3. lifetimes and arena layout ------------------------------------------------------------
@@ -654,7 +677,7 @@ int NetImpl::build() {
             if (blobs[b].def_op < 0) blobs[b].def_op = i;
             blobs[b].last_use = i;
         };
-        touch(o.in); touch(o.in2); touch(o.out);
+        touch(o.in); touch(o.in2); touch(o.out); touch(o.out2);
     }
     blobs[input_blob].def_op = 0;
     if (blobs[input_blob].last_use < 0) blobs[input_blob].last_use = 0;
@@ -893,7 +916,7 @@ int NetImpl::run_plan(int batch) {
                                              o.in2 >= 0 ? f32(o.in2) : nullptr, f32(o.out),
                                              o.write_bits && ob.u8 ? bytes(o.out) : nullptr,
                                              o.write_bits && !ob.u8 ? bits(o.out) : nullptr, batch, ib.h, ib.w, ib.c, ob.c, o.kh,
-                                             o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, stream);
+                                             o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, stream, o.out2 >= 0 ? f32(o.out2) : nullptr);
                     break;
                 }
                 rc = bconv_block_impl(bits(o.in), static_cast<const uint64_t*>(o.w->dev), o.w->count,

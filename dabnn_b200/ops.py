@@ -191,6 +191,26 @@ def bconv_u8_block(x_u8, w_expanded, cout, kh, kw, pad_h, pad_w, stride_h, strid
     return out, o8, bits
 
 
+def bconv_u8_block_pooled_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w):
+    return bool(capi.load().dabnn_bconv_u8_block_pooled_supported(n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w))
+
+
+def bconv_u8_block_pooled(x_u8, w_expanded, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, a=None, b=None, shortcut=None,
+                          want_u8=False):
+    """bconv_u8_block that also returns the 2x2 stride-2 average pooling of its fp32 result (reference
+    layers/AvePool.cpp:84 on the block's output).  Returns (f32, u8 or None, pooled f32)."""
+    x4 = _cuda(x_u8, torch.uint8)
+    n, h, w, cin = x4.shape
+    oh, ow = out_dim(h, pad_h, 1, kh, stride_h), out_dim(w, pad_w, 1, kw, stride_w)
+    dev = x4.device
+    out = torch.empty((n, oh, ow, cout), dtype=torch.float32, device=dev)
+    o8 = torch.empty((n, oh, ow, cout), dtype=torch.uint8, device=dev) if want_u8 else None
+    pooled = torch.empty((n, oh // 2, ow // 2, cout), dtype=torch.float32, device=dev)
+    check(capi.load().dabnn_bconv_u8_block_pooled(_ptr(x4), _ptr(w_expanded), _ptr(a), _ptr(b), _ptr(shortcut), _ptr(out), _ptr(o8), None,
+                                                  _ptr(pooled), n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, _stream()))
+    return out, o8, pooled
+
+
 def affine_(x, a, b):
     """In place x = a[c]*x + b[c]   (reference dabnn/layers/Affine.cpp:10)."""
     c = x.shape[-1]

@@ -127,8 +127,11 @@ int dabnn_binconv_forward(const float* in, const uint64_t* weight, size_t weight
  * GPU that loads the library holds those 16 MiB until the process exits.  Shapes that need more
  * scratch than that (dabnn_binconv_workspace_bytes) are refused with DABNN_ERR_SHAPE.  The call
  * makes no cudaMalloc / cudaFree and uses no allocating library routine.
- *  - The first call made with a given device current looks up the array's device address
- *    (cudaGetSymbolAddress) and caches it; make that first call outside any stream capture.
+ *  - The first call made with a given device current loads the library's device image there (the driver
+ *    materialises the 16 MiB array then and may synchronise), looks up the array's device address
+ *    (cudaGetSymbolAddress) and caches it: make one warm-up call per device at initialisation, outside any
+ *    stream capture; the no-allocation guarantee holds from the second call on.  The cached address does not
+ *    survive cudaDeviceReset or a teardown of the device's primary context.
  *  - All calls on a device share the one array.  Nothing in it needs clearing between calls (each
  *    call overwrites what it reads), but two calls whose kernels can overlap on the GPU - different
  *    streams, or different host threads - race on it: serialise them. */
@@ -166,6 +169,17 @@ int dabnn_bconv_u8_block(const unsigned char* in_u8, const unsigned char* w_expa
                          const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, int n,
                          int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
                          int stride_w, dabnn_stream_t s);
+
+/* dabnn_bconv_u8_block that also writes the 2x2 stride-2 average pooling of its fp32 result (reference
+ * layers/AvePool.cpp:84 ave_pool_fallback on the block's output: the downsample shortcut of the next stage of a
+ * ResNet-shaped net), pool_out fp32 [n][oh / 2][ow / 2][cout], bit-identical to dabnn_avepool on out_f32.  Shapes taken:
+ * 3x3, stride 1, padding 1, even h and w (dabnn_bconv_u8_block_pooled_supported tells). */
+int dabnn_bconv_u8_block_pooled_supported(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w,
+                                          int stride_h, int stride_w);
+int dabnn_bconv_u8_block_pooled(const unsigned char* in_u8, const unsigned char* w_expanded, const float* a, const float* b,
+                                const float* shortcut, float* out_f32, unsigned char* out_u8, uint64_t* out_bits, float* pool_out,
+                                int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h,
+                                int stride_w, dabnn_stream_t s);
 
 /* reference dabnn/layers/Affine.cpp:10 affine_inplace: x = a[c]*x + b[c] (in place). */
 int dabnn_affine(float* x, const float* a, const float* b, size_t pixels, int c, dabnn_stream_t s);

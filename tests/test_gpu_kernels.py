@@ -584,3 +584,28 @@ def test_fconv_maxpool_refuses_other_shapes(ops):
     x, w = torch.zeros((1, 64, 64, 3), device="cuda"), torch.zeros((64, 7, 7, 3), device="cuda")
     with pytest.raises(Exception):
         ops.fconv_maxpool(x, w, None, 3, 3, 2, 2)
+
+
+@pytest.mark.parametrize("n,H,cin,cout", [(3, 56, 64, 64), (5, 28, 128, 128), (4, 14, 256, 256), (2, 14, 256, 48), (150, 28, 128, 128)])
+def test_bconv_u8_block_with_average_pooled_output(ops, port, n, H, cin, cout):
+    """The fused block that also writes the 2x2 / 2 average pooling of its result (the next stage's downsample
+    shortcut, reference layers/AvePool.cpp:84): the block's own outputs are unchanged and the pooled tensor is what
+    dabnn_avepool gives on them, bit for bit; one image against the oracle's AvePool."""
+    rng = np.random.default_rng(H + cout + n)
+    xf = rng.normal(0, 1, (n, H, H, cin)).astype(np.float32)
+    wf = np.where(rng.random((cout, 3, 3, cin)) < 0.5, -1.0, 1.0).astype(np.float32)
+    w = port.pack_weight(wf)
+    a = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    b = rng.normal(0, 1, cout).astype(np.float32)
+    sc = rng.normal(0, 1, (n, H, H, cout)).astype(np.float32)
+    assert ops.bconv_u8_block_pooled_supported(n, H, H, cin, cout, 3, 3, 1, 1, 1, 1)
+    x8 = ops.binarize_u8(dev_f32(xf))
+    we = ops.bconv_u8_expand_weights(dev_bits(w), cout, 9 * cin // 64)
+    f32, o8, _ = ops.bconv_u8_block(x8, we, cout, 3, 3, 1, 1, 1, 1, dev_f32(a), dev_f32(b), dev_f32(sc), want_f32=True, want_u8=True)
+    g32, g8, pooled = ops.bconv_u8_block_pooled(x8, we, cout, 3, 3, 1, 1, 1, 1, dev_f32(a), dev_f32(b), dev_f32(sc), want_u8=True)
+    assert ops.engine_status() == 0
+    assert torch.equal(f32, g32) and torch.equal(o8, g8)
+    assert torch.equal(pooled, ops.avepool(f32, 2, 2, 0, 0, 2, 2))
+    assert same_bits(host(pooled[n - 1]), port.avepool(host(f32[n - 1]), 2, 2, 0, 0, 2, 2))
+    assert not ops.bconv_u8_block_pooled_supported(n, 15, 15, cin, cout, 3, 3, 1, 1, 1, 1)     # odd size
+    assert not ops.bconv_u8_block_pooled_supported(n, H, H, cin, cout, 3, 3, 1, 1, 2, 2)       # stride 2
