@@ -99,9 +99,12 @@ class ClockSampler(threading.Thread):
 
 
 def algorithmic_bytes(spec, batch):
-    """Per layer class: bytes one step must move (each tensor read or written once), from the model
-    description.  fp32 activations 4 B/element, packed bits 1/8 B/element, weights once."""
+    """Per layer class: bytes one step of the fused plan must move (each tensor read or written once), from the model
+    description.  fp32 activations 4 B/element, packed bits 1/8 B/element, weights once.  A 3x3 / 2 max pooling
+    behind a float convolution and a 2x2 / 2 average pooling behind a binary block happen in the producer's epilogue:
+    the pooled tensor is written, the convolution's own output (max pooling) is not, and nothing is re-read."""
     shapes = {spec.input_name: spec.input_shape[1:]}
+    made_by = {}   # blob name -> class of the convolution whose kernel writes it
     t = {x.name: x for x in spec.tensors}
     out = {}
     flops = {}   # multiply-adds * 2 per class (binary: per bit pair)
@@ -118,6 +121,7 @@ def algorithmic_bytes(spec, batch):
             ow = (w + 2 * f["pads"][1] - kw) // f["strides"][1] + 1
             shapes[f["output"]] = (oh, ow, o)
             cls = "Float Conv" if l.type == "FpConv2D" else "Bin Conv block"
+            made_by[f["output"]] = cls
             flops[cls] = flops.get(cls, 0) + 2.0 * batch * oh * ow * o * kh * kw * c
             if l.type == "FpConv2D":
                 add("Float Conv", batch * (h * w * c + oh * ow * o) * 4 + t[f["weight"]].data.size * 4)
@@ -128,11 +132,19 @@ def algorithmic_bytes(spec, batch):
             oh = (h + 2 * f["pads"][0] - f["kernel_shape"][0]) // f["strides"][0] + 1
             ow = (w + 2 * f["pads"][1] - f["kernel_shape"][1]) // f["strides"][1] + 1
             shapes[f["output"]] = (oh, ow, c)
-            add(l.type, batch * (h * w * c + oh * ow * c) * 4)
+            k, st, src = f["kernel_shape"][0], f["strides"][0], made_by.get(f["input"])
+            if l.type == "MaxPool" and src == "Float Conv" and (k, st) == (3, 2):
+                add(src, batch * (oh * ow * c - h * w * c) * 4)
+            elif l.type == "AvePool" and src == "Bin Conv block" and (k, st) == (2, 2):
+                add(src, batch * oh * ow * c * 4)
+            else:
+                add(l.type, batch * (h * w * c + oh * ow * c) * 4)
         elif l.type == "Add":
             shapes[f["output"]] = shapes[f["input1"]]
+            made_by[f["output"]] = made_by.get(f["input1"])
         else:
             shapes[f["output"]] = shapes[f["input"]]
+            made_by[f["output"]] = made_by.get(f["input"])
     return out, flops
 
 
@@ -440,7 +452,9 @@ def run_ours(args):
                     "traffic": traffic.get(top, {}).get("bytes_per_image", 0) * Bs or None}
         else:
             gbps = alg[top] / (classes[top] * 1e-3) / 1e9
-            blk = ("bconv_u8_kernel (16 fused binary conv blocks: {0,1}-byte activations loaded by TMA into tcgen05.mma kind::i8)"
+            blk = ("bconv_halo_kernel (10 launches: 3x3 stride-1 blocks on 56x56 / 28x28 / 14x14, halo tile read through shifted "
+                   "descriptors) + bconv_u8_kernel (6 launches: stride-2 and 7x7 blocks, one TMA box per tap); {0,1}-byte activations "
+                   "loaded by TMA into tcgen05.mma kind::i8, affine + shortcut + signs (+ 2x2 average pooling) in the epilogue"
                    if eng == "tcgen05" else f"bcontract_kernel<{eng}> (16 fused binary conv blocks)")
             names = {"Bin Conv block": blk}
             roof = {"bound": "hbm", "kernel": names.get(top, top), "achieved": round(gbps, 1), "peak": hbm_gbs, "unit": "GB/s",

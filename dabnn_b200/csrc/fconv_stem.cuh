@@ -48,6 +48,7 @@ constexpr int FS_MMA_WARP = (FS_CONVERTERS + FS_EPILOGUE) / 32;
 constexpr int FS_ACCS = 4;
 constexpr int FS_N = 64;          // channel block of a CTA
 constexpr int FS_PREFETCH = 3;    // row jobs whose global loads a converter thread keeps in flight
+constexpr int FS_POOL_TASKS = 2;  // POOL: (pooled column, four channels) tasks of an epilogue thread: pw * 8 <= 256 * FS_POOL_TASKS
 
 struct FsGeom {
     int kxp;                      // taps per window row, rounded up to even
@@ -61,8 +62,8 @@ struct FsGeom {
 };
 
 __host__ __device__ inline int fs_weight_bytes(int kpad) { return 2 * (FS_N / 8) * (kpad / 4) * 128; }
-__host__ __device__ inline int fs_smem_bytes(const FsGeom& g) {   // with POOL: + a running row of column maxima per 32-channel box
-    return 1024 + g.slots * g.slot_bytes + fs_weight_bytes(g.kpad) + 1024 + 2 * g.srows * 128 + 2 * g.pw * 128;
+__host__ __device__ inline int fs_smem_bytes(const FsGeom& g) {
+    return 1024 + g.slots * g.slot_bytes + fs_weight_bytes(g.kpad) + 1024 + 2 * g.srows * 128;
 }
 // the reference's max-pool fold (MaxPool.cpp:209-246): keeps the earlier value on ties, never picks a NaN
 __device__ __forceinline__ float4 fs_sel(const float4 a, const float4 t) {
@@ -137,7 +138,6 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
         g_begin = i0 * p.oh + max(0, 2 * py0 - 1);
         ntiles = i1 * p.oh + min(p.oh - 1, 2 * py1 + 1) - g_begin + 1;
     }
-    float* accrow = reinterpret_cast<float*>(stile + 2 * sbox_bytes);   // POOL: [box][pw][32 channels] running column maxima
 
     // ---- set-up ----
     if (warp == FS_MMA_WARP) {
@@ -347,6 +347,11 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
         const bool staged = r < g.srows;
         const bool elected = (et & 255) == 0;                  // one thread per box issues its stores
         const int bar_id = 1 + h2;
+        // POOL: the running row of column maxima.  A task (pooled column, four channels) belongs to the same thread in every
+        // tile, so the row lives in registers: task k = (et % 256) + 256 i, i < FS_POOL_TASKS.
+        float4 colmax[FS_POOL_TASKS];
+#pragma unroll
+        for (int i = 0; i < FS_POOL_TASKS; i++) colmax[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int t = 0; t < ntiles; t++) {
             const int accbuf = t % FS_ACCS, accuse = t / FS_ACCS;
             const bool okw = __all_sync(0xffffffffu, mbar_wait<200>(&tile_done[accbuf], accuse & 1, abort_flag));   // warp-uniform
@@ -370,13 +375,19 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                              : "r"(t_addr + FS_N));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int e = 0; e < 16; e++) {
-                    const int cl = cq * 16 + e;
-                    float f = __uint_as_float(v[e]) + __uint_as_float(xx[e]);   // + the hi*lo part
-                    if (p.bias) f = __fadd_rn(f, chan_bias[cl]);
-                    if (p.a) f = __fadd_rn(__fmul_rn(chan_a[cl], f), chan_b[cl]);
-                    if (p.relu) f = relu_ref(f);
-                    v[e] = __float_as_uint(f);
+                for (int q = 0; q < 4; q++) {   // the channel constants four at a time: every shared-memory wavefront counts here
+                    const int cl = cq * 16 + q * 4;
+                    const float4 cbias = *reinterpret_cast<const float4*>(chan_bias + cl), ca = *reinterpret_cast<const float4*>(chan_a + cl),
+                                 cb = *reinterpret_cast<const float4*>(chan_b + cl);
+                    const float kb[4] = {cbias.x, cbias.y, cbias.z, cbias.w}, ka[4] = {ca.x, ca.y, ca.z, ca.w}, kc[4] = {cb.x, cb.y, cb.z, cb.w};
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float f = __uint_as_float(v[q * 4 + e]) + __uint_as_float(xx[q * 4 + e]);   // + the hi*lo part
+                        if (p.bias) f = __fadd_rn(f, kb[e]);
+                        if (p.a) f = __fadd_rn(__fmul_rn(ka[e], f), kc[e]);
+                        if (p.relu) f = relu_ref(f);
+                        v[q * 4 + e] = __float_as_uint(f);
+                    }
                 }
             }
             if (okw) {   // the accumulator is in registers: the MMA warp may reuse it
@@ -405,18 +416,18 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                 const bool odd = (oy & 1) != 0, prelude = odd && t == 0;
                 const bool emit = (odd && !prelude) || (!odd && oy == p.oh - 1);
                 const bool init = prelude || oy == 0;
-                const uint32_t acc0 = smem_u32(accrow) + (uint32_t)(h2 * g.pw * 128);
-                for (int k = et & 255; k < g.pw * 8; k += 256) {   // task: pooled column px, four channels
+#pragma unroll
+                for (int i = 0; i < FS_POOL_TASKS; i++) {   // task: pooled column px, four channels
+                    const int k = (et & 255) + 256 * i;
                     const int px = k >> 3, q = k & 7;
-                    if (h2 * 32 + q * 4 >= n_this) continue;
+                    if (k >= g.pw * 8 || h2 * 32 + q * 4 >= n_this) continue;
                     float4 h = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
 #pragma unroll
                     for (int dx = -1; dx <= 1; dx++) {   // the reference skips taps outside the image
                         const int ox = 2 * px + dx;
                         if ((unsigned)ox < (unsigned)p.ow) h = fs_sel(h, lds128f(sbox + ox * 128 + ((q ^ (ox & 7)) << 4)));
                     }
-                    const uint32_t aaddr = acc0 + px * 128 + q * 16;
-                    float4 a = init ? h : fs_sel(lds128f(aaddr), h);
+                    float4 a = init ? h : fs_sel(colmax[i], h);
                     if (emit) {
                         const size_t e = (((size_t)img * g.ph + (oy >> 1)) * g.pw + px) * p.cout + n0 + h2 * 32 + q * 4;
                         *reinterpret_cast<float4*>(pool_out + e) = a;
@@ -425,7 +436,7 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                                 (a.x > 0.f ? 1u : 0u) | (a.y > 0.f ? 0x100u : 0u) | (a.z > 0.f ? 0x10000u : 0u) | (a.w > 0.f ? 0x1000000u : 0u);
                         a = h;   // the row also opens the next pooled row
                     }
-                    sts128f(aaddr, a.x, a.y, a.z, a.w);
+                    colmax[i] = a;
                 }
                 continue;
             }

@@ -552,6 +552,7 @@ static bool fconv_stem_plan(const FconvParams& p, FsGeom& g, bool pool = false) 
     g.ph = pool ? (p.oh - 1) / 2 + 1 : 0;     // 3x3 stride 2 pad 1
     g.pw = pool ? (p.ow - 1) / 2 + 1 : 0;
     g.rows_total = pool ? p.n * g.ph : p.n * p.oh;
+    if (g.pw * 8 > 256 * FS_POOL_TASKS) return false;
     static thread_local int budget_device = -1, budget = 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return false;
