@@ -28,10 +28,12 @@
 //     staging box, one TMA tensor store per box.
 // With POOL the 3x3 stride-2 pad-1 max pooling that follows a ResNet stem happens in the same kernel and the stem's own
 // output never leaves the SM: a CTA's share is a run of POOLED rows, the stem rows under them arrive in order (the
-// first one computed again by the neighbour that shares it), and after parking a stem row in the staging boxes the
-// epilogue folds it - three columns, in the reference's tap order and with its `acc < t ? t : acc` rule - into a running
-// row of column maxima in shared memory; every second stem row completes a pooled row, which is written out as fp32
-// and as {0,1} sign bytes.  Results are bit-identical to the two layers run one after the other.
+// first one computed again by the neighbour that shares it).  An epilogue thread meets the same pixel column in every
+// row, so it folds the window's rows in registers with the reference's `acc < t ? t : acc` rule; every second stem row
+// completes a pooled row, which alone is parked in the staging boxes, folded over its three columns and written out as
+// fp32 and as {0,1} sign bytes.  The values are those of the two layers run one after the other (the maximum does not
+// depend on the order of the fold; the only freedom is which zero comes out of a window whose maximum is both +0 and
+// -0, where the reference's tap order is row-major and this one is column-major).
 // Every wait is bounded; a wait that gives up records a code (31 converters, 32 / 33 MMA thread waiting for rows /
 // for an accumulator, 34 epilogue), raises the CTA's abort flag, and the CTA frees its tensor memory and returns.
 // Inputs must be finite: a non-finite pixel also poisons the output pixel whose zero-weight odd tap covers it.
@@ -347,12 +349,14 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
         const bool staged = r < g.srows;
         const bool elected = (et & 255) == 0;                  // one thread per box issues its stores
         const int bar_id = 1 + h2;
-        // POOL: the running row of column maxima.  A task (pooled column, four channels) belongs to the same thread in every
-        // tile, so the row lives in registers: task k = (et % 256) + 256 i, i < FS_POOL_TASKS.
-        float4 colmax[FS_POOL_TASKS];
+        // POOL: a thread sees the same pixel column and channels in every tile, so the vertical part of the pooling window
+        // - the maximum over the output rows 2 py - 1, 2 py, 2 py + 1 of pooled row py - is a fold in registers, in row order
+        // and with the reference's rule; only a completed row goes through shared memory for the three horizontal taps.
+        float vmax[16];
 #pragma unroll
-        for (int i = 0; i < FS_POOL_TASKS; i++) colmax[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int t = 0; t < ntiles; t++) {
+        for (int e = 0; e < 16; e++) vmax[e] = 0.f;
+        int img = g_begin / p.oh, oy = g_begin - img * p.oh;
+        for (int t = 0; t < ntiles; t++, oy = oy + 1 == p.oh ? (img++, 0) : oy + 1) {
             const int accbuf = t % FS_ACCS, accuse = t / FS_ACCS;
             const bool okw = __all_sync(0xffffffffu, mbar_wait<200>(&tile_done[accbuf], accuse & 1, abort_flag));   // warp-uniform
             if (!okw) {
@@ -364,29 +368,31 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
             uint32_t v[16];   // accumulator columns, then the finished outputs
             if (okw && ncol > 0) {
                 const uint32_t t_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + accbuf * ACC_COLS + cq * 16;
-                uint32_t xx[16];
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                               "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                             : "r"(t_addr));
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(xx[0]), "=r"(xx[1]), "=r"(xx[2]), "=r"(xx[3]), "=r"(xx[4]), "=r"(xx[5]), "=r"(xx[6]), "=r"(xx[7]), "=r"(xx[8]),
-                               "=r"(xx[9]), "=r"(xx[10]), "=r"(xx[11]), "=r"(xx[12]), "=r"(xx[13]), "=r"(xx[14]), "=r"(xx[15])
-                             : "r"(t_addr + FS_N));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int q = 0; q < 4; q++) {   // the channel constants four at a time: every shared-memory wavefront counts here
-                    const int cl = cq * 16 + q * 4;
-                    const float4 cbias = *reinterpret_cast<const float4*>(chan_bias + cl), ca = *reinterpret_cast<const float4*>(chan_a + cl),
-                                 cb = *reinterpret_cast<const float4*>(chan_b + cl);
-                    const float kb[4] = {cbias.x, cbias.y, cbias.z, cbias.w}, ka[4] = {ca.x, ca.y, ca.z, ca.w}, kc[4] = {cb.x, cb.y, cb.z, cb.w};
+                for (int half = 0; half < 2; half++) {   // eight columns at a time: the running maxima need the registers
+                    uint32_t* y = v + half * 8;
+                    uint32_t xx[8];
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(y[0]), "=r"(y[1]), "=r"(y[2]), "=r"(y[3]), "=r"(y[4]), "=r"(y[5]), "=r"(y[6]), "=r"(y[7])
+                                 : "r"(t_addr + half * 8));
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(xx[0]), "=r"(xx[1]), "=r"(xx[2]), "=r"(xx[3]), "=r"(xx[4]), "=r"(xx[5]), "=r"(xx[6]), "=r"(xx[7])
+                                 : "r"(t_addr + FS_N + half * 8));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        float f = __uint_as_float(v[q * 4 + e]) + __uint_as_float(xx[q * 4 + e]);   // + the hi*lo part
-                        if (p.bias) f = __fadd_rn(f, kb[e]);
-                        if (p.a) f = __fadd_rn(__fmul_rn(ka[e], f), kc[e]);
-                        if (p.relu) f = relu_ref(f);
-                        v[q * 4 + e] = __float_as_uint(f);
+                    for (int q = 0; q < 2; q++) {   // the channel constants four at a time: every shared-memory wavefront counts here
+                        const int cl = cq * 16 + half * 8 + q * 4;
+                        const float4 cbias = *reinterpret_cast<const float4*>(chan_bias + cl), ca = *reinterpret_cast<const float4*>(chan_a + cl),
+                                     cb = *reinterpret_cast<const float4*>(chan_b + cl);
+                        const float kb[4] = {cbias.x, cbias.y, cbias.z, cbias.w}, ka[4] = {ca.x, ca.y, ca.z, ca.w}, kc[4] = {cb.x, cb.y, cb.z, cb.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            float f = __uint_as_float(y[q * 4 + e]) + __uint_as_float(xx[q * 4 + e]);   // + the hi*lo part
+                            if (p.bias) f = __fadd_rn(f, kb[e]);
+                            if (p.a) f = __fadd_rn(__fmul_rn(ka[e], f), kc[e]);
+                            if (p.relu) f = relu_ref(f);
+                            y[q * 4 + e] = __float_as_uint(f);
+                        }
                     }
                 }
             }
@@ -395,27 +401,33 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[accbuf]);
             }
-            if (!POOL && elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's store has read the box
-            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");   // (POOL: everybody has folded the previous row)
-            if (epi_abort[h2]) break;
-            if (staged && ncol > 0) {
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int chunk = (cq & 1) * 4 + q;   // 16-byte chunk of the pixel's 128-byte row in the box
-                    sts128(sbox + r * 128 + ((chunk ^ (r & 7)) << 4), v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor store below reads what was just written
-            }
-            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
             if (POOL) {
-                // Fold the parked output row into the running row of column maxima of this group's box.  Output row oy is
-                // the middle row of pooled row oy / 2 when even, and when odd the last row of pooled row (oy - 1) / 2 and
-                // the first of the next: an odd row completes a pooled row (unless it is the CTA's first: that pooled row
-                // is the neighbour's), and so does an image's last row.
-                const int g_row = g_begin + t, img = g_row / p.oh, oy = g_row - img * p.oh;
+                // Output row oy is the middle row of pooled row oy / 2 when even, and when odd the last row of pooled row
+                // (oy - 1) / 2 and the first of the next: an odd row completes a pooled row (unless it is the CTA's first: that
+                // pooled row is the neighbour's), and so does an image's last row.
                 const bool odd = (oy & 1) != 0, prelude = odd && t == 0;
                 const bool emit = (odd && !prelude) || (!odd && oy == p.oh - 1);
                 const bool init = prelude || oy == 0;
+                if (okw && ncol > 0) {
+#pragma unroll
+                    for (int e = 0; e < 16; e++) {
+                        const float f = __uint_as_float(v[e]);
+                        vmax[e] = init ? f : (vmax[e] < f ? f : vmax[e]);
+                    }
+                }
+                if (!emit) continue;   // (a warp that gave up runs on, idle, to the next barrier and leaves with its group)
+                asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");   // everybody has read the previous completed row
+                if (epi_abort[h2]) break;
+                if (staged && ncol > 0) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int chunk = (cq & 1) * 4 + q;   // 16-byte chunk of the pixel's 128-byte row in the box
+                        sts128f(sbox + r * 128 + ((chunk ^ (r & 7)) << 4), vmax[q * 4], vmax[q * 4 + 1], vmax[q * 4 + 2], vmax[q * 4 + 3]);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 16; e++) vmax[e] = __uint_as_float(v[e]);   // an odd row also opens the next pooled row
+                }
+                asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
 #pragma unroll
                 for (int i = 0; i < FS_POOL_TASKS; i++) {   // task: pooled column px, four channels
                     const int k = (et & 255) + 256 * i;
@@ -427,19 +439,26 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                         const int ox = 2 * px + dx;
                         if ((unsigned)ox < (unsigned)p.ow) h = fs_sel(h, lds128f(sbox + ox * 128 + ((q ^ (ox & 7)) << 4)));
                     }
-                    float4 a = init ? h : fs_sel(colmax[i], h);
-                    if (emit) {
-                        const size_t e = (((size_t)img * g.ph + (oy >> 1)) * g.pw + px) * p.cout + n0 + h2 * 32 + q * 4;
-                        *reinterpret_cast<float4*>(pool_out + e) = a;
-                        if (pool_u8)
-                            *reinterpret_cast<uint32_t*>(pool_u8 + e) =
-                                (a.x > 0.f ? 1u : 0u) | (a.y > 0.f ? 0x100u : 0u) | (a.z > 0.f ? 0x10000u : 0u) | (a.w > 0.f ? 0x1000000u : 0u);
-                        a = h;   // the row also opens the next pooled row
-                    }
-                    colmax[i] = a;
+                    const size_t e = (((size_t)img * g.ph + (oy >> 1)) * g.pw + px) * p.cout + n0 + h2 * 32 + q * 4;
+                    *reinterpret_cast<float4*>(pool_out + e) = h;
+                    if (pool_u8)
+                        *reinterpret_cast<uint32_t*>(pool_u8 + e) =
+                            (h.x > 0.f ? 1u : 0u) | (h.y > 0.f ? 0x100u : 0u) | (h.z > 0.f ? 0x10000u : 0u) | (h.w > 0.f ? 0x1000000u : 0u);
                 }
                 continue;
             }
+            if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous tile's store has read the box
+            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+            if (epi_abort[h2]) break;
+            if (staged && ncol > 0) {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int chunk = (cq & 1) * 4 + q;   // 16-byte chunk of the pixel's 128-byte row in the box
+                    sts128(sbox + r * 128 + ((chunk ^ (r & 7)) << 4), v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor store below reads what was just written
+            }
+            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
             // one tensor store per box; the descriptor is [output row of the batch][pixel][channel]: pixels beyond the row
             // and channels beyond Cout are clipped
             if (elected && n_this > h2 * 32) {
