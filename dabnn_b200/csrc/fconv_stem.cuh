@@ -10,19 +10,26 @@
 // overlap between the windows of neighbouring pixels is overlap between operand rows of different instructions.
 // The 32-byte swizzle XORs address bit 4 with address bit 7 of the final shared-memory address, whatever the start
 // address, so the rows are stored with that XOR applied and any start offset reads them back in order.
-// K = kh * (kw rounded up to even) * 4 per output pixel (224 for 7x7x3; the fourth channel and the odd tap have
-// zero weights), against 147 real products: the tensor core has the headroom, the shared-memory pipe does not.
+// K = kh * (kw rounded up to even) * 4 per output pixel (224 for 7x7x3, against 147 real products).
+// 3xTF32 needs  head x [W_head; W_rem]  and  remainder x W_head.  The fourth float of a pixel (the input has at most
+// three channels) carries channel 0's remainder and meets channel 0's weight head there, so the first product brings a
+// third of the second along for nothing; the remainders of channels 1 and 2 form a second plane of 8-byte entries,
+// read the same way without swizzle (row pitch 16 bytes, the row's second 16 bytes addressed as the "next core matrix"
+// 16 bytes on), with half the K.  Per window row of a 7x7 stem: four N = 128 instructions and two N = 64 ones, where
+// full-width remainder planes took four of each - the kernel is bound by the operand bytes the tensor core pulls out of
+// shared memory and by the shared-memory traffic of the other roles, not by the arithmetic.
 //
 // A CTA (one per SM) walks consecutive output rows of consecutive images; a tile is one output row (up to 128
-// pixels).  Input rows live in a ring of slots (hi plane + lo plane of the 3xTF32 split each), so a new output row
+// pixels).  Input rows live in a ring of slots (the two planes of the 3xTF32 split each), so a new output row
 // converts only the stride_h input rows that entered its window.  Roles, meeting only at mbarriers:
 //   * 4 converter warps: thread x loads pixels x and x + 128 of the next input rows straight from global memory
 //     (three row jobs in flight per thread), splits each float into its tf32 head and the remainder, and stores the
 //     two 16-byte entries; once per tile a warp arrives on the tile's "rows ready" barrier.  The ring has room for the
 //     windows of two tiles beyond the one being multiplied; a slot is overwritten only after the tile that last read
 //     it has been committed by the tensor core;
-//   * 1 MMA warp: one lane issues per slice  hi x [W_hi; W_lo]  (one N = 128 instruction, the lo rows of the resident
-//     weights follow the hi rows) and  lo x W_hi  into one of four TMEM accumulators, then one commit per tile;
+//   * 1 MMA warp: one lane issues per slice  head x [W_head; W_rem]  (one N = 128 instruction, the remainder rows of the
+//     resident weights follow the head rows) and per two slices  remainder x W_head  into one of four TMEM accumulators,
+//     then one commit per tile;
 //   * 16 epilogue warps, thread (pixel, 16-channel quarter), in two groups of eight, one per 32-channel box:
 //     tcgen05.ld, add the two column halves, bias, affine, relu, park the row in the group's 128-byte-swizzled
 //     staging box, one TMA tensor store per box.
@@ -54,8 +61,9 @@ constexpr int FS_POOL_TASKS = 2;  // POOL: (pooled column, four channels) tasks 
 
 struct FsGeom {
     int kxp;                      // taps per window row, rounded up to even
-    int kpad;                     // kh * kxp * 4: K of the contraction
-    int plane_bytes, slot_bytes;  // one padded input row as 16-byte entries; hi plane + lo plane
+    int kpad;                     // kh * kxp * 4: K of the main contraction
+    int kxp2, kpad2;              // taps per window row rounded up to a multiple of four; kh * kxp2 * 2: K of the remainder contraction
+    int plane_bytes, slot_bytes;  // one padded input row as 16-byte entries; that plane + the plane of 8-byte remainder entries
     int slots;                    // ring of input-row slots: kh + ahead * stride_h
     int ahead;                    // tiles whose windows may be converted beyond the one being multiplied (1 or 2)
     int srows;                    // rows of a staging box (ow rounded up to 8)
@@ -64,8 +72,12 @@ struct FsGeom {
 };
 
 __host__ __device__ inline int fs_weight_bytes(int kpad) { return 2 * (FS_N / 8) * (kpad / 4) * 128; }
+__host__ __device__ inline int fs_weight2_bytes(int kpad2) { return (FS_N / 8) * (kpad2 / 4) * 128; }
 __host__ __device__ inline int fs_smem_bytes(const FsGeom& g) {
-    return 1024 + g.slots * g.slot_bytes + fs_weight_bytes(g.kpad) + 1024 + 2 * g.srows * 128;
+    return 1024 + g.slots * g.slot_bytes + fs_weight_bytes(g.kpad) + fs_weight2_bytes(g.kpad2) + 1024 + 2 * g.srows * 128;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(x), "r"(y) : "memory");
 }
 // the reference's max-pool fold (MaxPool.cpp:209-246): keeps the earlier value on ties, never picks a NaN
 __device__ __forceinline__ float4 fs_sel(const float4 a, const float4 t) {
@@ -122,7 +134,9 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
     unsigned char* patch = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* wbase = patch + g.slots * g.slot_bytes;
     const int w_sbo = (g.kpad / 4) * 128, w_half = (FS_N / 8) * w_sbo;
-    unsigned char* stile = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(wbase + 2 * w_half) + 1023) & ~uintptr_t(1023));
+    unsigned char* w2base = wbase + 2 * w_half;                 // the remainder contraction's weights: heads of channels 1 and 2
+    const int w2_sbo = (g.kpad2 / 4) * 128;
+    unsigned char* stile = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(w2base + (FS_N / 8) * w2_sbo) + 1023) & ~uintptr_t(1023));
     const int sbox_bytes = g.srows * 128;
     const volatile int* abort_flag = &s_abort;
     constexpr int ACC_COLS = 2 * FS_N, TMEM_COLS = FS_ACCS * ACC_COLS;   // 512 columns: all of the tensor memory
@@ -173,7 +187,8 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
             const int idx = idx0 + u * FS_THREADS;
             const int n = idx / g.kpad, k = idx - n * g.kpad;
             const int c = k & 3, tap = k >> 2, ky = tap / g.kxp, kx = tap - ky * g.kxp;
-            v[u] = (idx < FS_N * g.kpad && n < n_this && kx < p.kw && c < p.cin) ? __ldg(p.wgt + ((size_t)(n0 + n) * p.kh * p.kw + ky * p.kw + kx) * p.cin + c) : 0.f;
+            const int cs = c == 3 ? 0 : c;   // the fourth entry of a pixel carries channel 0's remainder: it meets channel 0's head
+            v[u] = (idx < FS_N * g.kpad && n < n_this && kx < p.kw && cs < p.cin) ? __ldg(p.wgt + ((size_t)(n0 + n) * p.kh * p.kw + ky * p.kw + kx) * p.cin + cs) : 0.f;
             off[u] = idx < FS_N * g.kpad ? (n >> 3) * w_sbo + (k >> 2) * 128 + (n & 7) * 16 + (k & 3) * 4 : -1;
         }
 #pragma unroll
@@ -182,8 +197,17 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
             uint32_t hi, lo;
             split_tf32(v[u], hi, lo);
             *reinterpret_cast<uint32_t*>(wbase + off[u]) = hi;
-            *reinterpret_cast<uint32_t*>(wbase + w_half + off[u]) = lo;
+            *reinterpret_cast<uint32_t*>(wbase + w_half + off[u]) = (off[u] & 12) == 12 ? 0u : lo;   // remainder x remainder is dropped
         }
+    }
+    // the remainder contraction, K order (ky, kx < kxp2, channel 1 or 2): heads of the weights only
+    for (int idx = tid; idx < FS_N * g.kpad2; idx += FS_THREADS) {
+        const int n = idx / g.kpad2, k = idx - n * g.kpad2;
+        const int c = 1 + (k & 1), tap = k >> 1, ky = tap / g.kxp2, kx = tap - ky * g.kxp2;
+        const float v = (n < n_this && kx < p.kw && c < p.cin) ? __ldg(p.wgt + ((size_t)(n0 + n) * p.kh * p.kw + ky * p.kw + kx) * p.cin + c) : 0.f;
+        uint32_t hi, lo;
+        split_tf32(v, hi, lo);
+        *reinterpret_cast<uint32_t*>(w2base + (n >> 3) * w2_sbo + (k >> 2) * 128 + (n & 7) * 16 + (k & 3) * 4) = hi;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -197,6 +221,7 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
         const int x = tid;                       // and x + FS_CONVERTERS
         const bool have_px[2] = {x < p.w, x + FS_CONVERTERS < p.w};
         const uint32_t entry0 = smem_u32(patch) + (uint32_t)(x + p.pad_w) * 16u;
+        const uint32_t rem0 = smem_u32(patch) + (uint32_t)g.plane_bytes + (uint32_t)(x + p.pad_w) * 8u;
         const long long row_floats = (long long)p.w * p.cin;
         // a cursor over the row jobs (tile by tile, the tile's new rows in order)
         struct Cursor {
@@ -262,9 +287,9 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                         uint32_t hi[4], lo[4];
 #pragma unroll
                         for (int ch = 0; ch < 4; ch++) split_tf32(pf[d][h * 4 + ch], hi[ch], lo[ch]);
-                        const uint32_t a = entry0 + (uint32_t)st.slot * (uint32_t)g.slot_bytes + (uint32_t)h * (FS_CONVERTERS * 16u);
-                        sts128(sw32(a), hi[0], hi[1], hi[2], hi[3]);
-                        sts128(sw32(a + g.plane_bytes), lo[0], lo[1], lo[2], lo[3]);
+                        const uint32_t so = (uint32_t)st.slot * (uint32_t)g.slot_bytes;
+                        sts128(sw32(entry0 + so + (uint32_t)h * (FS_CONVERTERS * 16u)), hi[0], hi[1], hi[2], lo[0]);
+                        sts64(rem0 + so + (uint32_t)h * (FS_CONVERTERS * 8u), lo[1], lo[2]);
                     }
                 if (st.q == st.ti.q0 + p.kh - 1) {   // the tile's window is complete
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -284,8 +309,14 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
             const bool stacked = n_this == FS_N;
             const uint32_t idesc2 = idesc_m | ((uint32_t)((2 * FS_N) >> 3) << 17);
             const uint64_t d_a = umma_desc_sw32(smem_u32(patch));
+            // the remainder plane: 8-byte entries, no swizzle; an operand row is 32 bytes = four taps of two channels, consecutive
+            // output pixels lie 16 bytes apart (the row pitch of the plain K-major layout) and the row's second half is the
+            // "next core matrix", 16 bytes on
+            const uint64_t d_r = umma_desc_kmajor(smem_u32(patch) + g.plane_bytes, 16, 128);
+            const uint64_t d_w2 = umma_desc_kmajor(smem_u32(w2base), 128, w2_sbo);
+            constexpr int SLICES2 = (SLICES + 1) / 2;
             const uint64_t d_wh = umma_desc_kmajor(smem_u32(wbase), 128, w_sbo), d_wl = umma_desc_kmajor(smem_u32(wbase) + w_half, 128, w_sbo);
-            const uint32_t slot_units = (uint32_t)g.slot_bytes >> 4, plane_units = (uint32_t)g.plane_bytes >> 4;
+            const uint32_t slot_units = (uint32_t)g.slot_bytes >> 4;
             // The issuing thread is one instruction stream and an MMA of this size executes in 50 - 65 cycles: the loop
             // must cost less than that per instruction, so the slices of a window row are unrolled (descriptors advance
             // by constants) and the two forms of the hi product get their own loops.
@@ -305,34 +336,36 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + accbuf * ACC_COLS;
-                uint64_t bh = d_wh, bl = d_wl;
+                uint64_t bh = d_wh, bl = d_wl, b2 = d_w2;
                 uint32_t accum = 0;
                 int slot = it.s0;
                 // one slice = eight floats = two 16-byte units per row: 32 bytes of a window row, 256 bytes of the weight layout
                 if (stacked) {
                     for (int ky = 0; ky < p.kh; ky++) {
-                        const uint64_t ah = d_a + (uint64_t)(slot * slot_units), al = ah + plane_units;
+                        const uint64_t ah = d_a + (uint64_t)(slot * slot_units), ar = d_r + (uint64_t)(slot * slot_units);
 #pragma unroll
-                        for (int j = 0; j < SLICES; j++) {
-                            mma_tf32_ss(d_tmem, ah + 2 * j, bh + 16 * j, idesc2, j ? 1u : accum);
-                            mma_tf32_ss(d_tmem, al + 2 * j, bh + 16 * j, idesc, 1u);
-                        }
+                        for (int j = 0; j < SLICES; j++) mma_tf32_ss(d_tmem, ah + 2 * j, bh + 16 * j, idesc2, j ? 1u : accum);
+#pragma unroll
+                        for (int j = 0; j < SLICES2; j++) mma_tf32_ss(d_tmem, ar + 2 * j, b2 + 16 * j, idesc, 1u);
                         accum = 1u;
                         bh += 16 * SLICES;
+                        b2 += 16 * SLICES2;
                         if (++slot == g.slots) slot = 0;
                     }
                 } else {
                     for (int ky = 0; ky < p.kh; ky++) {
-                        const uint64_t ah = d_a + (uint64_t)(slot * slot_units), al = ah + plane_units;
+                        const uint64_t ah = d_a + (uint64_t)(slot * slot_units), ar = d_r + (uint64_t)(slot * slot_units);
 #pragma unroll
                         for (int j = 0; j < SLICES; j++) {
                             mma_tf32_ss(d_tmem, ah + 2 * j, bh + 16 * j, idesc, j ? 1u : accum);
                             mma_tf32_ss(d_tmem + FS_N, ah + 2 * j, bl + 16 * j, idesc, j ? 1u : accum);
-                            mma_tf32_ss(d_tmem, al + 2 * j, bh + 16 * j, idesc, 1u);
                         }
+#pragma unroll
+                        for (int j = 0; j < SLICES2; j++) mma_tf32_ss(d_tmem, ar + 2 * j, b2 + 16 * j, idesc, 1u);
                         accum = 1u;
                         bh += 16 * SLICES;
                         bl += 16 * SLICES;
+                        b2 += 16 * SLICES2;
                         if (++slot == g.slots) slot = 0;
                     }
                 }

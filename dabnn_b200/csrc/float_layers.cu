@@ -538,14 +538,18 @@ namespace dabnn {
 // The window-reading kernel (fconv_stem.cuh) takes thin inputs with horizontal stride 2 whose output rows fill
 // most of a 128-row tile: the stem of a ResNet.  Returns false for every other shape.
 static bool fconv_stem_plan(const FconvParams& p, FsGeom& g, bool pool = false) {
-    if (p.cin > 4 || p.stride_w != 2 || p.dil_h != 1 || p.dil_w != 1 || (p.cout % 16) != 0) return false;
+    if (p.cin > 3 || p.stride_w != 2 || p.dil_h != 1 || p.dil_w != 1 || (p.cout % 16) != 0) return false;
     if (p.ow < 64 || p.ow > 128 || p.w > FS_MAX_W || p.kh > 16 || p.kw > 8) return false;
     if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (reinterpret_cast<uintptr_t>(p.in) & 3) != 0) return false;
     g.kxp = (p.kw + 1) & ~1;
     g.kpad = p.kh * g.kxp * 4;
-    const int entries = std::max(p.w + 2 * p.pad_w, 2 * (p.ow - 1) + g.kxp);
+    g.kxp2 = (p.kw + 3) & ~3;
+    g.kpad2 = p.kh * g.kxp2 * 2;
+    // a multiple of four entries: both planes of every slot then start on a 32-byte boundary, so that the 32-byte swizzle
+    // pairs up entries of the same plane
+    const int entries = (std::max(p.w + 2 * p.pad_w, 2 * (p.ow - 1) + g.kxp2) + 3) & ~3;
     g.plane_bytes = entries * 16;
-    g.slot_bytes = 2 * g.plane_bytes;
+    g.slot_bytes = g.plane_bytes + entries * 8;
     g.ahead = 2;
     g.slots = p.kh + 2 * std::min(p.stride_h, p.kh);
     g.srows = (p.ow + 7) & ~7;

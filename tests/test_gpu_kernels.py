@@ -498,7 +498,8 @@ def test_batchnorm_fold_identity(ops, port, cin, cout, ks):
     (2, 224, 3, 64, 7, 3, True, None),        # the stem itself
     (37, 224, 3, 64, 7, 3, False, None),      # 4144 output rows on 148 CTAs: 28 per CTA, windows rolling through the slot ring, image changes inside a CTA
     (300, 130, 3, 32, 5, 2, True, (0, 1, 149, 298, 299)),   # 65-pixel output rows, one 32-channel box
-    (3, 256, 4, 64, 3, 1, True, None),        # 128-pixel output rows, four real channels, 256 converter threads busy
+    (3, 256, 3, 64, 3, 1, True, None),        # 128-pixel output rows, 256 converter threads busy, a one-instruction remainder contraction per window row
+    (3, 256, 4, 64, 3, 1, True, None),        # four channels: not this kernel's (no spare entry per pixel), the staged-rows kernel takes it
     (2, 200, 1, 16, 7, 3, False, None),       # one channel, one 16-channel box (the three-instruction form)
     (2, 224, 3, 128, 7, 3, True, None),       # two channel blocks
     (5, 160, 2, 48, 4, 1, True, None),        # even kernel width (no dummy tap), 48 channels
@@ -546,7 +547,8 @@ def test_fconv_1x1_gemm_kernel(ops, port, n, h, cin, cout, bias):
     (2, 224, 3, 64, 7, 3, True),        # the stem and its pool
     (37, 224, 3, 64, 7, 3, True),       # 2072 pooled rows on 148 CTAs: shares that start and end inside images
     (149, 130, 3, 32, 5, 2, False),     # 65-pixel rows (odd: the last column has a two-tap window), 33 pooled rows, no relu (negative maxima)
-    (3, 255, 4, 64, 3, 1, True),        # 128 x 128 outputs from an odd-sized image
+    (3, 255, 3, 64, 3, 1, True),        # 128 x 128 outputs from an odd-sized image
+    (4, 180, 2, 32, 6, 2, True),        # two channels, six taps per window row (the remainder contraction pads them to eight)
     (5, 226, 1, 16, 7, 3, True),        # 113 output rows: an image's last pooled row ends on an even row
     (2, 224, 3, 128, 7, 3, True),       # two channel blocks
 ])
@@ -579,7 +581,7 @@ def test_fconv_maxpool_fused_is_bit_identical(ops, port, n, h, cin, cout, ks, pa
 
 def test_fconv_maxpool_refuses_other_shapes(ops):
     assert not ops.fconv_maxpool_supported(1, 64, 64, 3, 64, 7, 7, 3, 3, 2, 2)      # 32-pixel output rows: too short for the kernel
-    assert not ops.fconv_maxpool_supported(1, 224, 224, 8, 64, 7, 7, 3, 3, 2, 2)    # more than four channels
+    assert not ops.fconv_maxpool_supported(1, 224, 224, 4, 64, 7, 7, 3, 3, 2, 2)    # more than three channels
     assert not ops.fconv_maxpool_supported(1, 224, 224, 3, 64, 7, 7, 3, 3, 1, 1)    # stride 1
     x, w = torch.zeros((1, 64, 64, 3), device="cuda"), torch.zeros((64, 7, 7, 3), device="cuda")
     with pytest.raises(Exception):
