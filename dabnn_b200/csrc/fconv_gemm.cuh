@@ -208,13 +208,20 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
                                  : "r"(t_addr));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int e = 0; e < 16; e++) {
-                        const int ch = min(n0 + c0 + e, p.cout - 1);   // columns beyond Cout are clipped by the store
-                        float f = __uint_as_float(v[e]);
-                        if (p.bias) f = __fadd_rn(f, __ldg(p.bias + ch));
-                        if (p.a) f = __fadd_rn(__fmul_rn(__ldg(p.a + ch), f), __ldg(p.b + ch));
-                        if (p.relu) f = relu_ref(f);
-                        v[e] = __float_as_uint(f);
+                    for (int q = 0; q < 4; q++) {   // channel constants four at a time (Cout is a multiple of four)
+                        const int ch = min(n0 + c0 + q * 4, p.cout - 4);   // columns beyond Cout are clipped by the store
+                        float4 kb = make_float4(0.f, 0.f, 0.f, 0.f), ka = kb, kc = kb;
+                        if (p.bias) kb = __ldg(reinterpret_cast<const float4*>(p.bias + ch));
+                        if (p.a) { ka = __ldg(reinterpret_cast<const float4*>(p.a + ch)); kc = __ldg(reinterpret_cast<const float4*>(p.b + ch)); }
+                        const float b4[4] = {kb.x, kb.y, kb.z, kb.w}, a4[4] = {ka.x, ka.y, ka.z, ka.w}, c4[4] = {kc.x, kc.y, kc.z, kc.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            float f = __uint_as_float(v[q * 4 + e]);
+                            if (p.bias) f = __fadd_rn(f, b4[e]);
+                            if (p.a) f = __fadd_rn(__fmul_rn(a4[e], f), c4[e]);
+                            if (p.relu) f = relu_ref(f);
+                            v[q * 4 + e] = __float_as_uint(f);
+                        }
                     }
                 }
                 if (blk == nblk64 - 1 && okw) {   // the accumulator is in registers: the MMA warp may reuse it

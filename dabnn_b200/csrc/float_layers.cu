@@ -702,7 +702,7 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
                           stride_h, stride_w, dil_h, dil_w, oh, ow};
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (kh == 1 && kw == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 && cin % FG_CHUNK == 0 && cout % 4 == 0 &&
-        al16(in) && al16(weight) && al16(out)) {
+        al16(in) && al16(weight) && al16(out) && al16(bias) && al16(a) && al16(b)) {
         // a 1x1 convolution is a GEMM over [pixels][cin]: TMA-fed (fconv_gemm.cuh)
         static thread_local int gemm_device = -1, gemm_stages = 0;
         int dev = 0;
