@@ -16,6 +16,12 @@
 // row, tile, tap, so a halo buffer is released after its 18 (36 with two tiles: each its own) MMAs and the ring refills
 // while the other groups compute.
 //
+// Small images (7x7: the last stage of a ResNet) go two to a tile.  The pitch is then P = OW + 1: the zero column left of
+// a row doubles as the zero column right of the row above, the second image's halo starts (OH + 1) * P pixels after
+// the first one's - its top padding row is the first image's bottom padding row - and one zero pixel, written once at
+// start-up, stands behind the second halo for the last pixel's lower right tap.  The two images' boxes are two TMA loads
+// into one slot; 98 of the MMA's 128 rows carry pixels, and the nine taps of a pixel cost one load instead of nine.
+//
 // A block whose result also feeds a 2x2 stride-2 average pooling (the downsample shortcut of the next stage: reference
 // layers/AvePool.cpp:84) can write the pooled tensor as well: tiles are then an even number of output rows, and after a
 // block of 64 channels is staged every thread folds one pooled pixel x four channels out of the staging tile, in the
@@ -44,7 +50,8 @@ struct HaloParams {
     float* pool_out;              // or null: fp32 [B][OH / 2][OW / 2][N], the 2x2 stride-2 average pooling of `out` (OH, OW, rows even)
     int B, OH, OW, N;
     int cw;                       // 64-channel groups of the input
-    int P;                        // halo pitch in pixels: OW + 2
+    int P;                        // halo pitch in pixels: OW + 2 (OW + 1 with two images per tile)
+    int imgs, img_pitch;          // images per tile (1 or 2) and, with two, the accumulator rows between them: (OH + 1) * P
     int rows, tiles_per_img, ntiles;
     int hslots, halo_stride;      // halo ring: slots and bytes between them (a multiple of 1024)
     int wstages;                  // weight ring stages of three boxes (streamed weights)
@@ -78,9 +85,9 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
     int tmem_cols = 32;
     while (tmem_cols < U8_ACCS * n_mma) tmem_cols <<= 1;
     const volatile int* abort_flag = &s_abort;
-    const int box_px = p.rows * p.OW;               // pixels a tile's stores cover
+    const int box_px = p.imgs * p.rows * p.OW;      // pixels a tile's stores cover
     const int srows = u8_staging_rows(box_px), sbox_bytes = srows * 128, stile_bytes = 2 * sbox_bytes;
-    const uint32_t halo_tx = (uint32_t)((p.rows + 2) * p.P * 64);
+    const uint32_t halo_tx = (uint32_t)(p.imgs * (p.rows + 2) * p.P * 64);
 
     if (warp == 2) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(tmem_cols));
@@ -96,12 +103,15 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
         s_abort = 0;
         epi_abort = 0;
     }
+    if (p.imgs == 2 && tid < p.hslots * 4)   // the zero pixel behind the second image's halo (never written again)
+        sts128(smem_u32(halo0) + (tid >> 2) * p.halo_stride + (p.img_pitch + (p.rows + 2) * p.P) * 64 + (tid & 3) * 16, 0u, 0u, 0u, 0u);
     if (tid < TC5_MAX_N) {
         popw[tid] = __ldg(reinterpret_cast<const int*>(p.w_img + u8_weight_image_bytes(p.N, nboxes)) + n0 + tid);
         const bool have = p.a && tid < n_this;
         chan_a[tid] = have ? __ldg(p.a + n0 + tid) : 1.f;
         chan_b[tid] = have ? __ldg(p.b + n0 + tid) : 0.f;
     }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -119,7 +129,8 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
                 int img[2], oh0[2];   // a tile past the last one lies outside the tensor: its load delivers zeros
                 for (int t = 0; t < np; t++) {
                     const int tile = unit * np + t;
-                    img[t] = tile / p.tiles_per_img; oh0[t] = (tile - img[t] * p.tiles_per_img) * p.rows;
+                    if (p.imgs == 2) { img[t] = tile * 2; oh0[t] = 0; }
+                    else { img[t] = tile / p.tiles_per_img; oh0[t] = (tile - img[t] * p.tiles_per_img) * p.rows; }
                 }
                 for (int cg = 0; cg < p.cw && ok; cg++)
                     for (int t = 0; t < np; t++) {
@@ -131,9 +142,10 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
                         }
                         const uint32_t bar = smem_u32(&halo_full[hs]);
                         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(halo_tx) : "memory");
-                        asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-                                     ::"r"(halo0_addr + hs * p.halo_stride), "l"(reinterpret_cast<uint64_t>(&in_map)), "r"(cg * 64), "r"(-1),
-                                       "r"(oh0[t] - 1), "r"(img[t]), "r"(0), "r"(bar) : "memory");
+                        for (int j = 0; j < p.imgs; j++)   // (an image past the last one lies outside the tensor: zeros)
+                            asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                                         ::"r"(halo0_addr + hs * p.halo_stride + j * p.img_pitch * 64), "l"(reinterpret_cast<uint64_t>(&in_map)), "r"(cg * 64), "r"(-1),
+                                           "r"(oh0[t] - 1), "r"(img[t] + j), "r"(0), "r"(bar) : "memory");
                         if (++hs == (uint32_t)p.hslots) { hs = 0; huse++; }
                     }
             }
@@ -257,9 +269,10 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
         // halo pixel r: output row r / P of the tile, column r % P; it has a pixel when the column is below OW.
         const int et = tid - 96, ew = warp - 3;
         const int r = (warp & 3) * 32 + lane, hq = ew >> 2;   // TMEM lane quarter of a warp = warp % 4; column quarter 0..3
-        const int orow = r / p.P, ocol = r - orow * p.P;
+        const int second = (p.imgs == 2 && r >= p.img_pitch) ? 1 : 0, rr = r - second * p.img_pitch;   // which image of the tile
+        const int orow = rr / p.P, ocol = rr - orow * p.P;
         const bool has_px = ocol < p.OW && orow < p.rows;
-        const int m = orow * p.OW + ocol;                     // the pixel's index within the tile (dense), its staging row
+        const int m = (second * p.rows + orow) * p.OW + ocol;   // the pixel's index within the tile (dense), its staging row
         const uint32_t sbuf0_addr = smem_u32(sbuf0);
         const int nblk = (n_this + 63) >> 6;
         const int first_tile = blockIdx.x * np;
@@ -270,6 +283,12 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
         for (int t = first_tile, k = 0; t < p.ntiles; t = next_tile(t, k++)) my_tiles++;
         const int total_blocks = my_tiles * nblk;
         auto tile_span = [&](int tile, long long& base, int& nvalid, int& img0, int& oh0) {
+            if (p.imgs == 2) {   // whole images, the last tile may hold one
+                img0 = tile * 2; oh0 = 0;
+                base = (long long)img0 * p.OH * p.OW;
+                nvalid = max(0, min(2, p.B - img0)) * p.OH * p.OW;
+                return;
+            }
             img0 = tile / p.tiles_per_img; oh0 = (tile - img0 * p.tiles_per_img) * p.rows;
             base = ((long long)img0 * p.OH + oh0) * p.OW;
             nvalid = min(p.rows, p.OH - oh0) * p.OW;
@@ -279,7 +298,7 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
         int pkb = 0, ptile = first_tile, pti = 0, pblk = 0, pst = 0;
         auto prefetch_next = [&]() {   // thread et == 0 only
             if (p.shortcut && pkb < total_blocks) {
-                const int pimg = ptile / p.tiles_per_img, poh0 = (ptile - pimg * p.tiles_per_img) * p.rows;
+                const int pimg = p.imgs == 2 ? ptile * 2 : ptile / p.tiles_per_img, poh0 = p.imgs == 2 ? 0 : (ptile - pimg * p.tiles_per_img) * p.rows;
                 const int cb = pblk * 64, boxes = n_this - cb > 32 ? 2 : 1;
                 const uint32_t bar = smem_u32(&sc_full[pst]), dst = sbuf0_addr + pst * stile_bytes;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(boxes * box_px * 128)) : "memory");

@@ -93,6 +93,7 @@ bool u8_input_maps(const unsigned char* in, int n, int h, int w, int cin, int st
 struct HaloPlan {
     int OH = 0, OW = 0, P = 0, rows = 0, tiles_per_img = 0, ntiles = 0, hslots = 0, halo_stride = 0, wstages = 0, wb = 0;
     int resident = 0, stiles = 2, pair = 0, smem = 0;
+    int imgs = 1, img_pitch = 0;   // two whole images per tile (small images): accumulator rows between them
 };
 
 int g_halo_mode = 1;   // 0: never, 1: wherever the shape allows (dabnn_debug_set_halo)
@@ -104,25 +105,36 @@ bool halo_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h
     if (n <= 0 || h <= 0 || w <= 0 || cin % 64 || cout % 16 || cin <= 0 || cout <= 0 || w + 2 > 128) return false;
     if ((long long)n * h * w >= (1ll << 31)) return false;
     pl.OH = h; pl.OW = w; pl.P = w + 2;
-    int rmax = 128 / pl.P;
-    if (even_rows) {
-        rmax &= ~1;
-        if (rmax < 2 || (h & 1) || (w & 1) || (rmax / 2) * (w / 2) * 16 > U8_EPILOGUE) return false;
+    pl.imgs = 1; pl.img_pitch = 0;
+    // Two whole images per tile when both fit the MMA's 128 rows at a pitch of OW + 1 (7x7: 64 + 56 rows) and the second
+    // halo starts on a swizzle-atom boundary (eight pixels).
+    const bool two = !even_rows && n >= 2 && (2 * h + 1) * (w + 1) <= 128 && ((h + 1) * (w + 1)) % 8 == 0;
+    if (two) {
+        pl.P = w + 1;
+        pl.imgs = 2; pl.img_pitch = (h + 1) * pl.P;
+        pl.tiles_per_img = 1;
+        pl.rows = h;
+        pl.ntiles = (n + 1) / 2;
+    } else {
+        int rmax = 128 / pl.P;
+        if (even_rows) {
+            rmax &= ~1;
+            if (rmax < 2 || (h & 1) || (w & 1) || (rmax / 2) * (w / 2) * 16 > U8_EPILOGUE) return false;
+        }
+        pl.tiles_per_img = (h + rmax - 1) / rmax;
+        pl.rows = (h + pl.tiles_per_img - 1) / pl.tiles_per_img;
+        if (even_rows) pl.rows = (pl.rows + 1) & ~1;   // still at most rmax, and every tile starts on an even row
+        pl.ntiles = n * pl.tiles_per_img;
+        // an image smaller than half a tile that cannot share it with a second one is better served by the per-tap kernel
+        if (pl.rows * pl.P < 96) return false;
     }
-    pl.tiles_per_img = (h + rmax - 1) / rmax;
-    pl.rows = (h + pl.tiles_per_img - 1) / pl.tiles_per_img;
-    if (even_rows) pl.rows = (pl.rows + 1) & ~1;   // still at most rmax, and every tile starts on an even row
-    pl.ntiles = n * pl.tiles_per_img;
-    // an image smaller than half a tile (7x7: 63 halo pixels of the MMA's 128 rows) is better served by the per-tap kernel,
-    // which packs two images into a tile
-    if (pl.rows * pl.P < 96) return false;
     const int cw = cin / 64;
     pl.wb = u8_weight_rows(cout);
     const int wbox = pl.wb * 64, res_bytes = 9 * cw * wbox;
     pl.resident = res_bytes <= 48 * 1024;
     pl.stiles = pl.resident ? 3 : 2;
-    pl.halo_stride = ((pl.rows + 2) * pl.P * 64 + 1023) & ~1023;
-    const int stile_bytes = u8_staging_tile_bytes(pl.rows * pl.OW);
+    pl.halo_stride = (((pl.img_pitch + (pl.rows + 2) * pl.P + (two ? 1 : 0)) * 64) + 1023) & ~1023;
+    const int stile_bytes = u8_staging_tile_bytes(pl.imgs * pl.rows * pl.OW);
     int avail = U8_MAX_SMEM - 1024 - pl.stiles * stile_bytes - 3072 /* static shared memory */;
     {
         const int ctas = std::max(1, sm_count() / ((cout + TC5_MAX_N - 1) / TC5_MAX_N));
@@ -232,7 +244,7 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         {
             const unsigned long long dims[3] = {(unsigned long long)cout, (unsigned long long)hp.OH * hp.OW, (unsigned long long)n};
             const unsigned long long strides[2] = {(unsigned long long)cout * 4, (unsigned long long)cout * 4 * hp.OH * hp.OW};
-            const unsigned box[3] = {32u, (unsigned)(hp.rows * hp.OW), 1u};
+            const unsigned box[3] = {32u, (unsigned)(hp.rows * hp.OW), (unsigned)hp.imgs};
             DABNN_REQUIRE(!out_f32 || make_f32_tensor_map(&out_map, out_f32, 3, dims, strides, box), DABNN_ERR_CUDA,
                           "bconv_u8: cannot encode the output's tensor map");
             DABNN_REQUIRE(!shortcut || make_f32_tensor_map(&sc_map, const_cast<float*>(shortcut), 3, dims, strides, box), DABNN_ERR_CUDA,
@@ -241,7 +253,7 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         HaloParams q{};
         q.w_img = w_img; q.a = a; q.b = b; q.shortcut = shortcut; q.out = out_f32; q.out_u8 = out_u8; q.out_bits = out_bits;
         q.pool_out = pool_out;
-        q.B = n; q.OH = hp.OH; q.OW = hp.OW; q.N = cout; q.cw = cin / 64; q.P = hp.P;
+        q.B = n; q.OH = hp.OH; q.OW = hp.OW; q.N = cout; q.cw = cin / 64; q.P = hp.P; q.imgs = hp.imgs; q.img_pitch = hp.img_pitch;
         q.rows = hp.rows; q.tiles_per_img = hp.tiles_per_img; q.ntiles = hp.ntiles;
         q.hslots = hp.hslots; q.halo_stride = hp.halo_stride; q.wstages = hp.wstages; q.wb = hp.wb;
         q.resident = hp.resident; q.stiles = hp.stiles; q.pair = hp.pair;

@@ -298,7 +298,10 @@ U8_SHAPES = [  # n, H, W, cin, cout, k, pad, stride
     (3, 10, 20, 64, 32, 3, 1, 1),      # not square, rows per tile do not divide the height
     (2, 56, 56, 64, 128, 3, 1, 1),     # 128 output channels on 64 inputs: weights too large to stay resident, one group
     (301, 14, 14, 256, 256, 3, 1, 1),  # 602 tiles in pairs over 74 CTAs per channel block: every ring wraps many times
-    (1200, 7, 7, 512, 512, 3, 1, 1),   # four channel blocks, eight channel groups
+    (1200, 7, 7, 512, 512, 3, 1, 1),   # four channel blocks, eight channel groups; two whole images per halo tile (pitch OW + 1)
+    (7, 3, 3, 64, 64, 3, 1, 1),        # 3x3 images, two per tile, odd batch
+    (1, 7, 7, 128, 128, 3, 1, 1),      # a single small image: the per-tap kernel
+    (6, 7, 7, 64, 64, 3, 1, 1),        # two images per tile with resident weights
 ]
 
 
