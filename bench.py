@@ -452,8 +452,8 @@ def run_ours(args):
                     "traffic": traffic.get(top, {}).get("bytes_per_image", 0) * Bs or None}
         else:
             gbps = alg[top] / (classes[top] * 1e-3) / 1e9
-            blk = ("bconv_halo_kernel (10 launches: 3x3 stride-1 blocks on 56x56 / 28x28 / 14x14, halo tile read through shifted "
-                   "descriptors) + bconv_u8_kernel (6 launches: stride-2 and 7x7 blocks, one TMA box per tap); {0,1}-byte activations "
+            blk = ("bconv_halo_kernel (13 launches: the 3x3 stride-1 blocks, halo tile read through shifted descriptors) + "
+                   "bconv_u8_kernel (3 launches: the stride-2 blocks, one TMA box per tap); {0,1}-byte activations "
                    "loaded by TMA into tcgen05.mma kind::i8, affine + shortcut + signs (+ 2x2 average pooling) in the epilogue"
                    if eng == "tcgen05" else f"bcontract_kernel<{eng}> (16 fused binary conv blocks)")
             names = {"Bin Conv block": blk}
