@@ -56,6 +56,8 @@ struct HaloParams {
     int hslots, halo_stride;      // halo ring: slots and bytes between them (a multiple of 1024)
     int wstages;                  // weight ring stages of three boxes (streamed weights)
     int wb;                       // rows of a weight box image
+    int nb;                       // output channels per CTA: TC5_MAX_N, or 64 / 32 when there are too few tiles to fill the SMs
+                                  // (streamed weights only: a CTA then copies its rows out of every box image)
     int resident, stiles, pair;
 };
 
@@ -73,12 +75,12 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
     __shared__ __align__(16) float chan_b[TC5_MAX_N];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.y * TC5_MAX_N;
-    const int n_this = min(TC5_MAX_N, p.N - n0);   // multiple of 16 (host-checked)
+    const int n0 = blockIdx.y * p.nb;
+    const int n_this = min(p.nb, p.N - n0);        // multiple of 16 (host-checked)
     const int n_mma = n_this;
     constexpr int np = PAIR ? 2 : 1;
     const int nunits = (p.ntiles + np - 1) / np;
-    const int nboxes = 9 * p.cw, wbox_bytes = p.wb * 64;
+    const int nboxes = 9 * p.cw, gbox_bytes = p.wb * 64, wbox_bytes = min(p.nb, p.wb) * 64;   // a box image in global / this CTA's rows of it
     unsigned char* halo0 = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* wbase = halo0 + p.hslots * p.halo_stride;                                   // resident weights or the weight ring
     unsigned char* sbuf0 = wbase + (p.resident ? nboxes * wbox_bytes : p.wstages * 3 * wbox_bytes);   // a multiple of 1024 bytes further
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
     if (p.imgs == 2 && tid < p.hslots * 4)   // the zero pixel behind the second image's halo (never written again)
         sts128(smem_u32(halo0) + (tid >> 2) * p.halo_stride + (p.img_pitch + (p.rows + 2) * p.P) * 64 + (tid & 3) * 16, 0u, 0u, 0u, 0u);
     if (tid < TC5_MAX_N) {
-        popw[tid] = __ldg(reinterpret_cast<const int*>(p.w_img + u8_weight_image_bytes(p.N, nboxes)) + n0 + tid);
+        popw[tid] = tid < n_this ? __ldg(reinterpret_cast<const int*>(p.w_img + u8_weight_image_bytes(p.N, nboxes)) + n0 + tid) : 0;
         const bool have = p.a && tid < n_this;
         chan_a[tid] = have ? __ldg(p.a + n0 + tid) : 1.f;
         chan_b[tid] = have ? __ldg(p.b + n0 + tid) : 0.f;
@@ -116,7 +118,8 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
-    const unsigned char* wsrc = p.w_img + (size_t)blockIdx.y * nboxes * wbox_bytes;   // this channel block's box images
+    // this CTA's rows of its channel block's box images
+    const unsigned char* wsrc = p.w_img + (size_t)(n0 / TC5_MAX_N) * nboxes * gbox_bytes + (size_t)(n0 % TC5_MAX_N) * 64;
     if (warp != 1) grid_dependency_wait();   // the weight loader reads constants only and may run ahead of the previous kernel's end
 
     if (warp == 0) {
@@ -175,7 +178,7 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
                             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(3u * wbox_bytes) : "memory");
                             for (int kx = 0; kx < 3; kx++)   // the three taps of window row ky of this channel group
                                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                             ::"r"(dst + kx * wbox_bytes), "l"(wsrc + (size_t)((ky * 3 + kx) * p.cw + cg) * wbox_bytes), "r"((uint32_t)wbox_bytes),
+                                             ::"r"(dst + kx * wbox_bytes), "l"(wsrc + (size_t)((ky * 3 + kx) * p.cw + cg) * gbox_bytes), "r"((uint32_t)wbox_bytes),
                                                "r"(bar) : "memory");
                             if (++ws == (uint32_t)p.wstages) { ws = 0; wuse++; }
                         }
@@ -385,7 +388,8 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
                         signs |= ((o[0] > 0.f ? 1u : 0u) | (o[1] > 0.f ? 2u : 0u) | (o[2] > 0.f ? 4u : 0u) | (o[3] > 0.f ? 8u : 0u)) << (q * 4);
                     }
                     const long long row = base + m;
-                    if (p.out_bits) reinterpret_cast<unsigned short*>(p.out_bits + row * (p.N >> 6) + ((n0 + cb) >> 6))[hq] = (unsigned short)signs;
+                    if (p.out_bits)   // 16 channels = a quarter of a packed word (a narrow channel block may start inside a word)
+                        reinterpret_cast<unsigned short*>(p.out_bits + row * (p.N >> 6) + ((n0 + cb) >> 6))[(((n0 + cb) & 63) >> 4) + hq] = (unsigned short)signs;
                     if (p.out_u8) {
                         uint32_t w8[4];
 #pragma unroll

@@ -94,6 +94,7 @@ struct HaloPlan {
     int OH = 0, OW = 0, P = 0, rows = 0, tiles_per_img = 0, ntiles = 0, hslots = 0, halo_stride = 0, wstages = 0, wb = 0;
     int resident = 0, stiles = 2, pair = 0, smem = 0;
     int imgs = 1, img_pitch = 0;   // two whole images per tile (small images): accumulator rows between them
+    int nb = TC5_MAX_N;            // output channels per CTA
 };
 
 int g_halo_mode = 1;   // 0: never, 1: wherever the shape allows (dabnn_debug_set_halo)
@@ -108,7 +109,7 @@ bool halo_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h
     pl.imgs = 1; pl.img_pitch = 0;
     // Two whole images per tile when both fit the MMA's 128 rows at a pitch of OW + 1 (7x7: 64 + 56 rows) and the second
     // halo starts on a swizzle-atom boundary (eight pixels).
-    const bool two = !even_rows && n >= 2 && (2 * h + 1) * (w + 1) <= 128 && ((h + 1) * (w + 1)) % 8 == 0;
+    const bool two = !even_rows && (2 * h + 1) * (w + 1) <= 128 && ((h + 1) * (w + 1)) % 8 == 0;
     if (two) {
         pl.P = w + 1;
         pl.imgs = 2; pl.img_pitch = (h + 1) * pl.P;
@@ -143,6 +144,10 @@ bool halo_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h
         if (force_pair >= 0) pl.pair = !pl.resident && force_pair;
     }
     const int np = pl.pair ? 2 : 1;
+    // Too few tiles for the SMs (a handful of images): narrower channel blocks, so that more CTAs share the weight stream.
+    pl.nb = TC5_MAX_N;
+    if (!pl.resident && !pl.pair)
+        while (pl.nb > 32 && cout > pl.nb / 2 && 2 * pl.ntiles * ((cout + pl.nb - 1) / pl.nb) <= sm_count()) pl.nb >>= 1;
     if (pl.resident) {
         avail -= res_bytes;
         pl.wstages = 0;
@@ -253,11 +258,11 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
         HaloParams q{};
         q.w_img = w_img; q.a = a; q.b = b; q.shortcut = shortcut; q.out = out_f32; q.out_u8 = out_u8; q.out_bits = out_bits;
         q.pool_out = pool_out;
-        q.B = n; q.OH = hp.OH; q.OW = hp.OW; q.N = cout; q.cw = cin / 64; q.P = hp.P; q.imgs = hp.imgs; q.img_pitch = hp.img_pitch;
+        q.B = n; q.OH = hp.OH; q.OW = hp.OW; q.N = cout; q.cw = cin / 64; q.P = hp.P; q.imgs = hp.imgs; q.img_pitch = hp.img_pitch; q.nb = hp.nb;
         q.rows = hp.rows; q.tiles_per_img = hp.tiles_per_img; q.ntiles = hp.ntiles;
         q.hslots = hp.hslots; q.halo_stride = hp.halo_stride; q.wstages = hp.wstages; q.wb = hp.wb;
         q.resident = hp.resident; q.stiles = hp.stiles; q.pair = hp.pair;
-        const int tiles_n = (cout + TC5_MAX_N - 1) / TC5_MAX_N;
+        const int tiles_n = (cout + hp.nb - 1) / hp.nb;
         const int per_n = std::max(1, sm_count() / tiles_n);
         const int nunits = hp.pair ? (hp.ntiles + 1) / 2 : hp.ntiles;
         dim3 grid(std::min(nunits, per_n), tiles_n);
