@@ -10,7 +10,7 @@ namespace {
 
 struct U8Plan {
     int OH = 0, OW = 0, rows = 0, imgs = 0, tiles_per_img = 0, ntiles = 0, G = 0, stages = 0, wb = 0, nboxes = 0;
-    int smem = 0, resident = 0, stiles = 2, wide = 0, pair = 0;
+    int smem = 0, resident = 0, stiles = 2, wide = 0, pair = 0, nbc = TC5_MAX_N;
 };
 
 // Shapes the engine takes: whole 64-channel groups, channel counts in 16s, stride 1 or 2 (even H and W), no
@@ -63,6 +63,10 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
         if (force_pair >= 0) pl.pair = can_pair && force_pair;
     }
     if (pl.pair) pl.G = 2;
+    // Too few tiles for the SMs (a handful of images): narrower channel blocks, so that more CTAs share the weight stream.
+    pl.nbc = TC5_MAX_N;
+    if (!pl.resident && !pl.pair)
+        while (pl.nbc > 32 && cout > pl.nbc / 2 && 2 * pl.ntiles * ((cout + pl.nbc - 1) / pl.nbc) <= sm_count()) pl.nbc >>= 1;
     const int stage_bytes = pl.G * ((pl.pair ? 2 : 1) * U8_BOX_BYTES + (pl.resident ? 0 : pl.wb * 64));
     pl.stages = std::min(8, avail / stage_bytes);
     if (pl.stages < 2) return false;
@@ -286,8 +290,8 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     p.B = n; p.OH = pl.OH; p.OW = pl.OW; p.N = cout;
     p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w; p.stride = stride_h; p.cw = cin / 64;
     p.rows = pl.rows; p.imgs = pl.imgs; p.tiles_per_img = pl.tiles_per_img; p.ntiles = pl.ntiles;
-    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles; p.wide = pl.wide; p.pair = pl.pair;
-    const int tiles_n = (cout + TC5_MAX_N - 1) / TC5_MAX_N;
+    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles; p.wide = pl.wide; p.pair = pl.pair; p.nbc = pl.nbc;
+    const int tiles_n = (cout + pl.nbc - 1) / pl.nbc;
     const int per_n = std::max(1, sm_count() / tiles_n);
     const int nunits = pl.pair ? (pl.ntiles + 1) / 2 : pl.ntiles;
     dim3 grid(std::min(nunits, per_n), tiles_n);

@@ -66,6 +66,8 @@ struct U8Params {
     int stiles;                   // staging tiles (2 or 3): the shortcut is prefetched stiles - 1 blocks ahead
     int wide;                     // cin % 128 == 0: one TMA load covers two K boxes (128-byte rows, SWIZZLE_128B)
     int pair;                     // two pixel tiles share every weight stage (streamed weights: halves their bytes)
+    int nbc;                      // output channels per CTA: TC5_MAX_N, or 64 / 32 when there are too few tiles to fill the SMs
+                                  // (streamed weights only: a CTA then copies its rows out of every box image)
 };
 
 __host__ __device__ inline int u8_weight_rows(int N) { return min(N, TC5_MAX_N); }
@@ -147,13 +149,14 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     __shared__ __align__(16) float chan_b[TC5_MAX_N];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.y * TC5_MAX_N;
-    const int n_this = min(TC5_MAX_N, p.N - n0);   // multiple of 16 (host-checked)
+    const int n0 = blockIdx.y * p.nbc;
+    const int n_this = min(p.nbc, p.N - n0);        // multiple of 16 (host-checked)
     const int n_mma = n_this;
     constexpr int np = PAIR ? 2 : 1;                // pixel tiles per unit of work (they share the unit's weight stages)
     const int nunits = (p.ntiles + np - 1) / np;
     const int a_bytes1 = p.G * U8_BOX_BYTES, a_bytes = np * a_bytes1;   // one tile's boxes of a stage, all of them
-    const int wbox_bytes = p.wb * 64, stage_bytes = a_bytes + (p.resident ? 0 : p.G * wbox_bytes);
+    const int gbox_bytes = p.wb * 64, wbox_bytes = min(p.nbc, p.wb) * 64;   // a box image in global / this CTA's rows of it
+    const int stage_bytes = a_bytes + (p.resident ? 0 : p.G * wbox_bytes);
     unsigned char* wres = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
     unsigned char* stage0 = wres + (p.resident ? p.nboxes * wbox_bytes : 0);   // a multiple of 1024 bytes further
     const int nst = (p.nboxes + p.G - 1) / p.G;     // stages per tile
@@ -178,7 +181,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
         epi_abort = 0;
     }
     if (tid < TC5_MAX_N) {
-        popw[tid] = __ldg(reinterpret_cast<const int*>(p.w_img + u8_weight_image_bytes(p.N, p.nboxes)) + n0 + tid);
+        popw[tid] = tid < n_this ? __ldg(reinterpret_cast<const int*>(p.w_img + u8_weight_image_bytes(p.N, p.nboxes)) + n0 + tid) : 0;
         const bool have = p.a && tid < n_this;
         chan_a[tid] = have ? __ldg(p.a + n0 + tid) : 1.f;
         chan_b[tid] = have ? __ldg(p.b + n0 + tid) : 0.f;
@@ -192,7 +195,8 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     if (warp == 0) {
         // =========================== loads: one lane ===========================
         if (lane == 0) {
-            const unsigned char* wsrc = p.w_img + (size_t)blockIdx.y * p.nboxes * wbox_bytes;
+            // this CTA's rows of its channel block's box images
+            const unsigned char* wsrc = p.w_img + (size_t)(n0 / TC5_MAX_N) * p.nboxes * gbox_bytes + (size_t)(n0 % TC5_MAX_N) * 64;
             const uint32_t stage0_addr = smem_u32(stage0);
             const uint32_t box_tx = (uint32_t)box_px * 64u;   // a load always delivers its whole box (zeros outside the tensor)
             uint32_t s = 0, use = 0;
@@ -221,9 +225,17 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                     const uint32_t bar = smem_u32(&bar_full[s]), sa = stage0_addr + s * stage_bytes;
                     const uint32_t wbytes = p.resident ? 0u : (uint32_t)(nb * wbox_bytes);
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(wbytes + np * nb * box_tx) : "memory");
-                    if (!p.resident)
-                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                     ::"r"(sa + a_bytes), "l"(wsrc + (size_t)st * p.G * wbox_bytes), "r"(wbytes), "r"(bar) : "memory");
+                    if (!p.resident) {
+                        if (wbox_bytes == gbox_bytes) {   // whole box images: the stage's boxes are one run
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                         ::"r"(sa + a_bytes), "l"(wsrc + (size_t)st * p.G * gbox_bytes), "r"(wbytes), "r"(bar) : "memory");
+                        } else {
+                            for (int b = 0; b < nb; b++)
+                                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                             ::"r"(sa + a_bytes + b * wbox_bytes), "l"(wsrc + (size_t)(st * p.G + b) * gbox_bytes), "r"((uint32_t)wbox_bytes),
+                                               "r"(bar) : "memory");
+                        }
+                    }
                     const int bstep = p.wide ? 2 : 1;   // a wide load fills two K boxes (16 KB: 128 rows of 128 bytes)
                     for (int b = 0; b < nb; b += bstep) {
                         const int dy = ky - p.pad_h, dx = kx - p.pad_w;
@@ -436,7 +448,8 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
                 }
                 if (r < nvalid) {
                     const long long row = base + r;
-                    if (p.out_bits) reinterpret_cast<unsigned short*>(p.out_bits + row * (p.N >> 6) + ((n0 + cb) >> 6))[hq] = (unsigned short)signs;
+                    if (p.out_bits)   // 16 channels = a quarter of a packed word (a narrow channel block may start inside a word)
+                        reinterpret_cast<unsigned short*>(p.out_bits + row * (p.N >> 6) + ((n0 + cb) >> 6))[(((n0 + cb) & 63) >> 4) + hq] = (unsigned short)signs;
                     if (p.out_u8) {
                         uint32_t w8[4];
 #pragma unroll

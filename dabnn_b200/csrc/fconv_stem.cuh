@@ -201,13 +201,24 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
         }
     }
     // the remainder contraction, K order (ky, kx < kxp2, channel 1 or 2): heads of the weights only
-    for (int idx = tid; idx < FS_N * g.kpad2; idx += FS_THREADS) {
-        const int n = idx / g.kpad2, k = idx - n * g.kpad2;
-        const int c = 1 + (k & 1), tap = k >> 1, ky = tap / g.kxp2, kx = tap - ky * g.kxp2;
-        const float v = (n < n_this && kx < p.kw && c < p.cin) ? __ldg(p.wgt + ((size_t)(n0 + n) * p.kh * p.kw + ky * p.kw + kx) * p.cin + c) : 0.f;
-        uint32_t hi, lo;
-        split_tf32(v, hi, lo);
-        *reinterpret_cast<uint32_t*>(w2base + (n >> 3) * w2_sbo + (k >> 2) * 128 + (n & 7) * 16 + (k & 3) * 4) = hi;
+    for (int idx0 = tid; idx0 < FS_N * g.kpad2; idx0 += 4 * FS_THREADS) {
+        float v[4];
+        int off[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int idx = idx0 + u * FS_THREADS;
+            const int n = idx / g.kpad2, k = idx - n * g.kpad2;
+            const int c = 1 + (k & 1), tap = k >> 1, ky = tap / g.kxp2, kx = tap - ky * g.kxp2;
+            v[u] = (idx < FS_N * g.kpad2 && n < n_this && kx < p.kw && c < p.cin) ? __ldg(p.wgt + ((size_t)(n0 + n) * p.kh * p.kw + ky * p.kw + kx) * p.cin + c) : 0.f;
+            off[u] = idx < FS_N * g.kpad2 ? (n >> 3) * w2_sbo + (k >> 2) * 128 + (n & 7) * 16 + (k & 3) * 4 : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (off[u] < 0) continue;
+            uint32_t hi, lo;
+            split_tf32(v[u], hi, lo);
+            *reinterpret_cast<uint32_t*>(w2base + off[u]) = hi;
+        }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
