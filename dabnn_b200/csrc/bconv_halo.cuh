@@ -38,7 +38,7 @@
 namespace dabnn {
 
 constexpr int HL_THREADS = 96 + U8_EPILOGUE;   // warps 0, 1, 2 + the epilogue warps
-constexpr int HL_MAX_HSLOTS = 8, HL_MAX_WSTAGES = 4;
+constexpr int HL_MAX_HSLOTS = 8, HL_MAX_WSTAGES = 8;   // (more than four weight stages only with narrow channel blocks)
 
 struct HaloParams {
     const unsigned char* w_img;   // expanded weights (bconv_u8_expand_weights_kernel): box (tap * cw + cg)
@@ -120,6 +120,7 @@ __global__ void __launch_bounds__(HL_THREADS, 1)
     const uint32_t tmem_base = tmem_base_s;
     // this CTA's rows of its channel block's box images
     const unsigned char* wsrc = p.w_img + (size_t)(n0 / TC5_MAX_N) * nboxes * gbox_bytes + (size_t)(n0 % TC5_MAX_N) * 64;
+    grid_launch_dependents();
     if (warp != 1) grid_dependency_wait();   // the weight loader reads constants only and may run ahead of the previous kernel's end
 
     if (warp == 0) {

@@ -152,20 +152,22 @@ bool halo_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h
     pl.nb = TC5_MAX_N;
     if (!pl.resident && !pl.pair)
         while (pl.nb > 32 && cout > pl.nb / 2 && 2 * pl.ntiles * ((cout + pl.nb - 1) / pl.nb) <= sm_count()) pl.nb >>= 1;
+    const int wboxs = std::min(pl.nb, pl.wb) * 64;   // this CTA's rows of a box image
     if (pl.resident) {
         avail -= res_bytes;
         pl.wstages = 0;
     } else {
         // weight ring first (two to four stages of three boxes), the halo ring gets the rest
         pl.wstages = 0;
-        for (int ws = HL_MAX_WSTAGES; ws >= 2 && !pl.wstages; ws--)
-            if ((avail - ws * 3 * wbox) / pl.halo_stride >= std::min(HL_MAX_HSLOTS, 2 * np * std::min(cw, 2))) pl.wstages = ws;
+        // (narrow channel blocks: small stages, and the launch is a race against L2 latency - keep more of them in flight)
+        for (int ws = pl.nb < TC5_MAX_N ? HL_MAX_WSTAGES : 4; ws >= 2 && !pl.wstages; ws--)
+            if ((avail - ws * 3 * wboxs) / pl.halo_stride >= std::min(HL_MAX_HSLOTS, 2 * np * std::min(cw, 2))) pl.wstages = ws;
         if (!pl.wstages) pl.wstages = 2;
-        avail -= pl.wstages * 3 * wbox;
+        avail -= pl.wstages * 3 * wboxs;
     }
     pl.hslots = std::min(HL_MAX_HSLOTS, avail / pl.halo_stride);
     if (pl.hslots < 2 * np) return false;
-    pl.smem = 1024 + pl.hslots * pl.halo_stride + (pl.resident ? res_bytes : pl.wstages * 3 * wbox) + pl.stiles * stile_bytes;
+    pl.smem = 1024 + pl.hslots * pl.halo_stride + (pl.resident ? res_bytes : pl.wstages * 3 * wboxs) + pl.stiles * stile_bytes;
     return true;
 }
 

@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    grid_launch_dependents();
     grid_dependency_wait();   // set-up touched constants only; activations come next
 
     if (warp == 0) {

@@ -42,6 +42,12 @@ int sm_count();
 // visible.  Only kernels that make that call before they touch activations may be launched this way.
 extern int g_overlap_launches;   // 1 (default): on; dabnn_debug_set_launch_overlap
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the kernel that follows in the stream (if it was launched with launch_overlapped) start as soon as every CTA of
+// this grid has made the call: its CTAs take the SMs this grid leaves free and run their own set-up while this grid
+// still computes; their grid_dependency_wait() still holds them until this grid has completed.  For kernels whose
+// whole grid is resident at once (one persistent CTA per SM): a grid with CTAs still waiting for an SM would have to
+// share it with the newcomers.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 template <class... KArgs, class... Args>
 inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg{};

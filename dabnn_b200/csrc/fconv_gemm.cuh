@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    grid_launch_dependents();
     grid_dependency_wait();
 
     if (warp == 0) {

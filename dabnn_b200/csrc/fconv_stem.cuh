@@ -225,6 +225,7 @@ __global__ void __launch_bounds__(FS_THREADS, 1)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    grid_launch_dependents();
     grid_dependency_wait();   // everything above touched constants only; the images and the output buffers come next
 
     if (tid < FS_CONVERTERS) {
