@@ -128,6 +128,7 @@ __global__ void __launch_bounds__(256) pool_kernel(const float* __restrict__ in,
     const IDX total = (IDX)n * oh * ow * c_vec;
     const IDX stride = (IDX)gridDim.x * blockDim.x;
     const IDX bound = bits ? (total + 31) / 32 * 32 : total;
+    grid_launch_dependents();   // (a grid-stride kernel: blocks that are not resident yet share the SMs with the newcomers, which only wait)
     grid_dependency_wait();
     for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < bound; i += stride) {
         const bool valid = i < total;
