@@ -284,6 +284,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     numa_bound = bind_to_gpu_cpus(local)   # before any pinned allocation
     if world > 1:
+        # NCCL writes its banner and debug lines to stdout unless told otherwise; stdout carries the one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     def barrier():
