@@ -46,7 +46,7 @@ constexpr int U8_THREADS = 64 + U8_EPILOGUE;  // warp 0: loads, warp 1: MMA, the
 // Staging tile of a 64-channel block: two boxes of (a tile's pixels, rounded up to 8) x 32 channels of fp32, 128-byte-swizzled.
 __host__ __device__ inline int u8_staging_rows(int tile_pixels) { return (tile_pixels + 7) & ~7; }
 __host__ __device__ inline int u8_staging_tile_bytes(int tile_pixels) { return 2 * u8_staging_rows(tile_pixels) * 128; }
-constexpr int U8_MAX_STILES = 3;             // staging tiles: one being drained and stored, the others being prefetched
+constexpr int U8_MAX_STILES = 6;             // staging tiles: one being drained and stored, the others being prefetched
 constexpr int U8_MAX_SMEM = 227 * 1024;
 
 __device__ int g_u8_status;   // 0 = ok; 21 loader, 22 MMA (accumulator), 23 MMA (stage), 24 epilogue
