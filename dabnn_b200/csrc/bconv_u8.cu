@@ -10,7 +10,7 @@ namespace {
 
 struct U8Plan {
     int OH = 0, OW = 0, rows = 0, imgs = 0, tiles_per_img = 0, ntiles = 0, G = 0, stages = 0, wb = 0, nboxes = 0;
-    int smem = 0, resident = 0, stiles = 2, wide = 0, pair = 0, nbc = TC5_MAX_N;
+    int smem = 0, resident = 0, stiles = 2, wide = 0, pair = 0, nbc = TC5_MAX_N, lag = 0;
 };
 
 // Shapes the engine takes: whole 64-channel groups, channel counts in 16s, stride 1 or 2 (even H and W), no
@@ -48,7 +48,8 @@ bool u8_plan(int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, 
     const int res_bytes = pl.nboxes * pl.wb * 64;
     pl.resident = res_bytes <= 48 * 1024;   // a channel block's weights stay in shared memory
     // with resident weights the ring carries pixel boxes only and there is room for a third staging tile
-    pl.stiles = pl.resident ? 3 : 2;
+    pl.stiles = pl.resident ? 4 : 3;   // one more than the look-ahead needs: the latest tensor store may still be reading its tile
+    pl.lag = 1;
     const int stile_bytes = u8_staging_tile_bytes(pl.rows * pl.OW * pl.imgs);
     int avail = U8_MAX_SMEM - 1024 - pl.stiles * stile_bytes - 3072 /* static shared memory */;
     if (pl.resident) avail -= res_bytes;
@@ -299,7 +300,7 @@ int bconv_u8_block_impl(const unsigned char* in_u8, const unsigned char* w_img, 
     p.B = n; p.OH = pl.OH; p.OW = pl.OW; p.N = cout;
     p.kh = kh; p.kw = kw; p.pad_h = pad_h; p.pad_w = pad_w; p.stride = stride_h; p.cw = cin / 64;
     p.rows = pl.rows; p.imgs = pl.imgs; p.tiles_per_img = pl.tiles_per_img; p.ntiles = pl.ntiles;
-    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles; p.wide = pl.wide; p.pair = pl.pair; p.nbc = pl.nbc;
+    p.G = pl.G; p.stages = pl.stages; p.wb = pl.wb; p.nboxes = pl.nboxes; p.resident = pl.resident; p.stiles = pl.stiles; p.wide = pl.wide; p.pair = pl.pair; p.nbc = pl.nbc; p.lag = pl.lag;
     const int tiles_n = (cout + pl.nbc - 1) / pl.nbc;
     const int per_n = std::max(1, sm_count() / tiles_n);
     const int nunits = pl.pair ? (pl.ntiles + 1) / 2 : pl.ntiles;

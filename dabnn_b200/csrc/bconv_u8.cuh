@@ -66,6 +66,8 @@ struct U8Params {
     int stiles;                   // staging tiles (2 or 3): the shortcut is prefetched stiles - 1 blocks ahead
     int wide;                     // cin % 128 == 0: one TMA load covers two K boxes (128-byte rows, SWIZZLE_128B)
     int pair;                     // two pixel tiles share every weight stage (streamed weights: halves their bytes)
+    int lag;                      // tensor stores that may still be reading their staging tile when the next shortcut is fetched
+                                  // (0 or 1): the shortcut runs stiles - 1 - lag blocks ahead
     int nbc;                      // output channels per CTA: TC5_MAX_N, or 64 / 32 when there are too few tiles to fill the SMs
                                   // (streamed weights only: a CTA then copies its rows out of every box image)
 };
@@ -379,7 +381,7 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             }
         };
         if (et == 0)
-            for (int d = 0; d + 1 < p.stiles; d++) prefetch_next();
+            for (int d = 0; d + 1 + p.lag < p.stiles; d++) prefetch_next();
         bool okw = true;
         uint32_t sc_par = 0;
         int tile = first_tile, ti = 0, blk = 0, st_idx = 0, accbuf = 0, accuse = 0, nvalid = 0, img0 = 0, oh0 = 0;
@@ -390,7 +392,9 @@ __global__ void __launch_bounds__(U8_THREADS, 1)
             const int width = min(64, n_this - cb);
             const uint32_t sb = sbuf0_addr + st_idx * stile_bytes;
             if (et == 0) {
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the tensor stores of block kb - 1 have read its tile: it is idle
+                // the tile the next shortcut goes to is idle once the stores of block kb - 1 - lag have read it
+                if (p.lag) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 prefetch_next();
             }
             if (p.shortcut && okw) {   // the shortcut of block kb has landed in its tile
