@@ -310,8 +310,10 @@ int dabnn_engine_status(int* status);
  * fall back to IMMA for channel counts and alignments the tensor-memory kernel does not take. */
 int dabnn_last_engine(void);
 
-/* Tuning hook: mode 0 keeps 3x3 stride-1 blocks of dabnn_bconv_u8_block on the kernel that loads one box per tap;
- * the default (1) runs them on the kernel that loads a tile's halo once.  Both give identical results. */
+/* Tuning hook.  Bits 0..3: 0 keeps 3x3 stride-1 blocks of dabnn_bconv_u8_block on the kernel that loads one box per
+ * tap; the default (1) runs them on the kernel that loads a tile's halo once.  Bits 4..6: staging tiles of the halo
+ * kernel (0 = the plan's choice), bit 7: whether the latest tensor store may still be reading its tile when the next
+ * shortcut is fetched.  Every setting gives identical results. */
 int dabnn_debug_set_halo(int mode);
 
 /* Tuning hook: 0 launches every kernel strictly after the one before it; the default (1) lets the hot kernels of a Net
