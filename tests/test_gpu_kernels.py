@@ -614,3 +614,34 @@ def test_bconv_u8_block_with_average_pooled_output(ops, port, n, H, cin, cout):
     assert same_bits(host(pooled[n - 1]), port.avepool(host(f32[n - 1]), 2, 2, 0, 0, 2, 2))
     assert not ops.bconv_u8_block_pooled_supported(n, 15, 15, cin, cout, 3, 3, 1, 1, 1, 1)     # odd size
     assert not ops.bconv_u8_block_pooled_supported(n, H, H, cin, cout, 3, 3, 1, 1, 2, 2)       # stride 2
+
+
+@pytest.mark.parametrize("n,H,cin,cout", [(9, 56, 64, 64), (33, 14, 256, 256), (150, 7, 512, 512)])
+def test_block_kernels_and_their_tunings_agree(ops, n, H, cin, cout):
+    """The two kernels a 3x3 stride-1 block can run on (one TMA box per tap / the tile's halo loaded once), every
+    staging-tile setting of the halo kernel, and launches with and without programmatic overlap give the same bits
+    (the reference has one result per layer: dabnn/layers/BinConv.cpp:144 + Affine.cpp:10 + Add.cpp:7)."""
+    from dabnn_b200 import capi
+    lib = capi.load()
+    rng = np.random.default_rng(n + H)
+    x8 = torch.from_numpy((rng.random((n, H, H, cin)) < 0.5).astype(np.uint8)).cuda()
+    wbits = torch.from_numpy(rng.integers(-2**62, 2**62, cout * 9 * cin // 64, dtype=np.int64)).cuda()
+    we = ops.bconv_u8_expand_weights(wbits, cout, 9 * cin // 64)
+    a, b = dev_f32(rng.uniform(-0.1, 0.1, cout).astype(np.float32)), dev_f32(rng.normal(0, 1, cout).astype(np.float32))
+    sc = dev_f32(rng.normal(0, 1, (n, H, H, cout)).astype(np.float32))
+    run = lambda: ops.bconv_u8_block(x8, we, cout, 3, 3, 1, 1, 1, 1, a, b, sc, want_f32=True, want_u8=True, want_bits=True)
+    try:
+        lib.dabnn_debug_set_halo(0)
+        base = run()
+        for mode in (1, 1 | (2 << 4), 1 | (3 << 4), 1 | ((8 | 3) << 4), 1 | ((8 | 5) << 4)):
+            lib.dabnn_debug_set_halo(mode)
+            got = run()
+            assert ops.engine_status() == 0
+            assert all(torch.equal(g, e) for g, e in zip(got, base)), hex(mode)
+        lib.dabnn_debug_set_halo(1)
+        lib.dabnn_debug_set_launch_overlap(0)
+        got = run()
+        assert all(torch.equal(g, e) for g, e in zip(got, base))
+    finally:
+        lib.dabnn_debug_set_halo(1)
+        lib.dabnn_debug_set_launch_overlap(1)
