@@ -119,12 +119,18 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
                     const uint32_t hi0 = sa + half * 2 * FG_TILE_BYTES + ct * 16, lo0 = hi0 + FG_TILE_BYTES;
+                    // eight units per thread and tile, their loads issued together (the shared-memory accesses are ordered
+                    // as written: one load, one store at a time would pay the load's latency eight times)
+                    constexpr int UNITS = FG_TILE_BYTES / 16 / FG_CONVERTERS;
+                    float4 v[UNITS];
 #pragma unroll
-                    for (int j = 0; j < FG_TILE_BYTES / 16 / FG_CONVERTERS; j++) {
-                        if (half == 1 && (uint32_t)(j * FG_CONVERTERS * 16) >= w_bytes) break;   // a weight tile has n_blk rows
-                        const float4 v = lds128f(hi0 + j * FG_CONVERTERS * 16);
+                    for (int j = 0; j < UNITS; j++)
+                        if (half == 0 || (uint32_t)(j * FG_CONVERTERS * 16) < w_bytes) v[j] = lds128f(hi0 + j * FG_CONVERTERS * 16);   // a weight tile has n_blk rows
+#pragma unroll
+                    for (int j = 0; j < UNITS; j++) {
+                        if (half == 1 && (uint32_t)(j * FG_CONVERTERS * 16) >= w_bytes) break;
                         uint32_t h, l0, l1, l2, l3;
-                        split_tf32(v.x, h, l0); split_tf32(v.y, h, l1); split_tf32(v.z, h, l2); split_tf32(v.w, h, l3);
+                        split_tf32(v[j].x, h, l0); split_tf32(v[j].y, h, l1); split_tf32(v[j].z, h, l2); split_tf32(v[j].w, h, l3);
                         sts128(lo0 + j * FG_CONVERTERS * 16, l0, l1, l2, l3);
                     }
                 }
