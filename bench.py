@@ -284,8 +284,6 @@ def run_ours(args):
     torch.cuda.set_device(local)
     numa_bound = bind_to_gpu_cpus(local)   # before any pinned allocation
     if world > 1:
-        # NCCL writes its banner and debug lines to stdout unless told otherwise; stdout carries the one JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     def barrier():
@@ -540,6 +538,11 @@ def main():
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
+    # stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1 on their own (NCCL
+    # prints its version banner there) are pointed at stderr, and the line goes out through a copy of the real stdout
+    sys.stdout.flush()
+    out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         if rank != 0:
             return
@@ -552,14 +555,14 @@ def main():
                                        "sample of the 1024-image batch on the host cores", "global_batch": GLOBAL_BATCH},
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=out, flush=True)
         return
 
     if args.gpus > 1 and world == 1:   # convenience: launch the ranks ourselves
         import subprocess
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29517", str(Path(__file__).resolve()), *sys.argv[1:]]
-        raise SystemExit(subprocess.call(cmd))
+        raise SystemExit(subprocess.call(cmd, stdout=out))
 
     result, world, rank = run_ours(args)
     if rank == 0:
@@ -568,7 +571,7 @@ def main():
                 result["cpu_baseline"], _ = run_reference(args, rounds=2, warmup=1)
             except Exception as e:  # the GPU numbers stand on their own
                 result["cpu_baseline"] = {"unavailable": str(e)}
-        print(json.dumps(result), flush=True)
+        print(json.dumps(result), file=out, flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()

@@ -38,7 +38,7 @@ __host__ __device__ inline int fg_smem_bytes(int stages) { return 1024 + stages 
 
 __global__ void __launch_bounds__(FG_THREADS, 1)
     fconv_gemm_kernel(const FconvParams p, const int M, const int stages, const int n_blk, const __grid_constant__ CUtensorMap a_map,
-                      const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap out_map) {
+                      const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap wr_map, const __grid_constant__ CUtensorMap out_map) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bar_loaded[FG_MAX_STAGES], bar_ready[FG_MAX_STAGES], bar_empty[FG_MAX_STAGES];
     __shared__ __align__(8) uint64_t bar_acc_full[FG_ACCS], bar_acc_empty[FG_ACCS];
@@ -90,12 +90,15 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
                         break;
                     }
                     const uint32_t bar = smem_u32(&bar_loaded[s]), sa = stage0_addr + s * FG_STAGE_BYTES;
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(FG_TILE_BYTES + w_bytes) : "memory");
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(FG_TILE_BYTES + (p.wgt_rem ? 2u : 1u) * w_bytes) : "memory");
                     // rows beyond M / beyond Cout read as zeros; a load always delivers its whole box
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                                  ::"r"(sa), "l"(reinterpret_cast<uint64_t>(&a_map)), "r"(c * FG_CHUNK), "r"(tile * 128), "r"(bar) : "memory");
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                                  ::"r"(sa + 2 * FG_TILE_BYTES), "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(c * FG_CHUNK), "r"(nb * n_blk), "r"(bar) : "memory");
+                    if (p.wgt_rem)   // the weights' remainders were computed once, ahead of the launch
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                     ::"r"(sa + 3 * FG_TILE_BYTES), "l"(reinterpret_cast<uint64_t>(&wr_map)), "r"(c * FG_CHUNK), "r"(nb * n_blk), "r"(bar) : "memory");
                     if (++s == (uint32_t)stages) { s = 0; use++; }
                 }
             }
@@ -117,7 +120,7 @@ __global__ void __launch_bounds__(FG_THREADS, 1)
                 const uint32_t sa = stage0_addr + s * FG_STAGE_BYTES;
                 // 16-byte unit u of a hi tile -> the same unit of its lo tile (identical layouts)
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
+                for (int half = 0; half < (p.wgt_rem ? 1 : 2); half++) {
                     const uint32_t hi0 = sa + half * 2 * FG_TILE_BYTES + ct * 16, lo0 = hi0 + FG_TILE_BYTES;
                     // eight units per thread and tile, their loads issued together (the shared-memory accesses are ordered
                     // as written: one load, one store at a time would pay the load's latency eight times)

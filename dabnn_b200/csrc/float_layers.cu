@@ -367,6 +367,7 @@ struct FconvParams {
     const float *in, *wgt, *bias, *a, *b;
     float* out;
     int relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, oh, ow;
+    const float* wgt_rem;   // or null: w - trunc_tf32(w) for every weight, computed once by fconv_split_weights (1x1 GEMM kernel)
 };
 
 __global__ void __launch_bounds__(FNT, 2) fconv_kernel(const FconvParams p) {
@@ -686,9 +687,29 @@ int fconv_status_word(int** addr) {
     return DABNN_OK;
 }
 
+// remainders of the 3xTF32 split of constant weights: rem = w - (w with its low 13 mantissa bits cleared)
+__global__ void split_weights_kernel(const float* __restrict__ w, float* __restrict__ rem, size_t count) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t hi, lo;
+        split_tf32(w[i], hi, lo);
+        rem[i] = __uint_as_float(lo);
+    }
+}
+
+int fconv_split_weights(const float* weight, float* rem, size_t count, cudaStream_t stream) {
+    DABNN_REQUIRE(weight && rem, DABNN_ERR_ARG, "fconv_split_weights: null pointer");
+    if (!count) return DABNN_OK;
+    split_weights_kernel<<<(int)std::min<size_t>((count + 255) / 256, 1024), 256, 0, stream>>>(weight, rem, count);
+    return check_launch("split_weights_kernel");
+}
+
+bool fconv_uses_weight_remainders(int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w) {
+    return kh == 1 && kw == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 && cin % FG_CHUNK == 0 && cout % 4 == 0;
+}
+
 int fconv_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b, int relu,
                float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h, int pad_w,
-               int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream) {
+               int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream, const float* weight_rem) {
     DABNN_REQUIRE(in && weight && out, DABNN_ERR_ARG, "fconv: null pointer");
     DABNN_REQUIRE(n > 0 && h > 0 && w > 0 && cin > 0 && cout > 0 && kh > 0 && kw > 0 && stride_h > 0 &&
                       stride_w > 0 && dil_h > 0 && dil_w > 0 && pad_h >= 0 && pad_w >= 0, DABNN_ERR_ARG,
@@ -700,7 +721,7 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
     DABNN_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7) == 0, DABNN_ERR_ARG, "fconv: output must be 8-byte aligned");
     dim3 grid((n * oh * ow + FTM - 1) / FTM, (cout + FTN - 1) / FTN);
     const FconvParams prm{in, weight, bias, a, b, out, relu, n, h, w, cin, cout, kh, kw, pad_h, pad_w,
-                          stride_h, stride_w, dil_h, dil_w, oh, ow};
+                          stride_h, stride_w, dil_h, dil_w, oh, ow, (reinterpret_cast<uintptr_t>(weight_rem) & 15) == 0 ? weight_rem : nullptr};
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (kh == 1 && kw == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 && cin % FG_CHUNK == 0 && cout % 4 == 0 &&
         al16(in) && al16(weight) && al16(out) && al16(bias) && al16(a) && al16(b)) {
@@ -723,16 +744,17 @@ int fconv_impl(const float* in, const float* weight, const float* bias, const fl
         // channels per work item: as large as leaves every SM a work item
         int n_blk = FG_N;
         while (n_blk > 32 && tiles_m * ((cout + n_blk - 1) / n_blk) < sm_count()) n_blk >>= 1;
-        CUtensorMap a_map, w_map, o_map;
+        CUtensorMap a_map, w_map, wr_map{}, o_map;
         const unsigned box[2] = {32, 128}, wbox[2] = {32, (unsigned)n_blk};
         const unsigned long long adims[2] = {(unsigned long long)cin, (unsigned long long)Mpx}, astr[1] = {(unsigned long long)cin * 4};
         const unsigned long long wdims[2] = {(unsigned long long)cin, (unsigned long long)cout};
         const unsigned long long odims[2] = {(unsigned long long)cout, (unsigned long long)Mpx}, ostr[1] = {(unsigned long long)cout * 4};
         if (gemm_stages >= 2 && make_f32_tensor_map(&a_map, const_cast<float*>(in), 2, adims, astr, box) &&
-            make_f32_tensor_map(&w_map, const_cast<float*>(weight), 2, wdims, astr, wbox) && make_f32_tensor_map(&o_map, out, 2, odims, ostr, box)) {
+            make_f32_tensor_map(&w_map, const_cast<float*>(weight), 2, wdims, astr, wbox) && make_f32_tensor_map(&o_map, out, 2, odims, ostr, box) &&
+            (!prm.wgt_rem || make_f32_tensor_map(&wr_map, const_cast<float*>(prm.wgt_rem), 2, wdims, astr, wbox))) {
             const int items = tiles_m * ((cout + n_blk - 1) / n_blk);
             launch_overlapped(fconv_gemm_kernel, std::min(items, sm_count()), FG_THREADS, fg_smem_bytes(gemm_stages), stream, prm, Mpx, gemm_stages, n_blk, a_map,
-                              w_map, o_map);
+                              w_map, wr_map, o_map);
             return check_launch("fconv_gemm_kernel");
         }
     }

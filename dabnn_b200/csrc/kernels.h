@@ -65,7 +65,12 @@ int elementwise_chain(const float* x, const float* a, const float* b, const floa
 int fconv_tc5_status(int* status);
 int fconv_impl(const float* in, const float* weight, const float* bias, const float* a, const float* b,
                int relu, float* out, int n, int h, int w, int cin, int cout, int kh, int kw, int pad_h,
-               int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream);
+               int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, cudaStream_t stream, const float* weight_rem = nullptr);
+// weight_rem (optional, 16-byte aligned): the remainders w - trunc_tf32(w) of constant weights, computed once by
+// fconv_split_weights; the 1x1 GEMM kernel then loads them by TMA instead of recomputing them for every tile.
+// fconv_uses_weight_remainders tells for which convolutions they are read.
+int fconv_split_weights(const float* weight, float* rem, size_t count, cudaStream_t stream);
+bool fconv_uses_weight_remainders(int cin, int cout, int kh, int kw, int pad_h, int pad_w, int stride_h, int stride_w);
 
 // The same followed by a 3x3 stride-2 pad-1 max pooling, in one kernel, for the shapes fconv_pool_supported accepts (thin
 // inputs with horizontal stride 2: a ResNet stem); the convolution's own output is never written.

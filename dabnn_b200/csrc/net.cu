@@ -78,6 +78,7 @@ struct Op {
     int relu = 0;
     bool write_f32 = true, write_bits = false;
     const unsigned char* w_expanded = nullptr;   // BConvBlock: the weights in the TCGEN05 engine's stage layout
+    const float* w_rem = nullptr;                // FConv on the 1x1 GEMM kernel: the weights' 3xTF32 remainders, computed at load time
     bool u8 = false;                             // BConvBlock: runs on the byte-activation engine (its input blob is u8)
 };
 
@@ -110,6 +111,8 @@ struct NetImpl {
     unsigned char* weights = nullptr;
     unsigned char* expanded = nullptr;   // all binary convolution weights expanded to bytes, once, at load time
     size_t expanded_bytes = 0;
+    float* remainders = nullptr;         // 3xTF32 remainders of the 1x1 float convolutions' weights
+    size_t remainders_bytes = 0;
     const float* cur_input = nullptr;  // device pointer of the images the plan is currently reading
     int cur_batch = 0;
     int input_blob = -1;
@@ -150,6 +153,7 @@ struct NetImpl {
         if (arena) cudaFree(arena);
         if (weights) cudaFree(weights);
         if (expanded) cudaFree(expanded);
+        if (remainders) cudaFree(remainders);
         if (stream) cudaStreamDestroy(stream);
     }
 
@@ -775,6 +779,31 @@ int NetImpl::build() {
             DABNN_CUDA_OK(cudaStreamSynchronize(stream));
         }
     }
+    if (optimize) {
+        // 1x1 float convolutions run as a TMA-fed GEMM whose tensor core wants x = head + remainder of both operands: the
+        // weights' remainders are constants, computed here once instead of once per pixel tile
+        std::vector<size_t> offs;
+        for (const Op& o : plan) {
+            if (o.kind != OpKind::FConv || !fconv_uses_weight_remainders(blobs[o.in].c, blobs[o.out].c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w)) continue;
+            offs.push_back(remainders_bytes);
+            remainders_bytes += (o.w->count * sizeof(float) + 255) / 256 * 256;
+        }
+        if (remainders_bytes) {
+            if (cudaMalloc(&remainders, remainders_bytes) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(DABNN_ERR_OOM, "cannot allocate the float convolutions' weight remainders");
+            }
+            size_t k = 0;
+            for (Op& o : plan) {
+                if (o.kind != OpKind::FConv || !fconv_uses_weight_remainders(blobs[o.in].c, blobs[o.out].c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w)) continue;
+                float* dst = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(remainders) + offs[k++]);
+                const int rc = fconv_split_weights(static_cast<const float*>(o.w->dev), dst, o.w->count, stream);
+                if (rc) return rc;
+                o.w_rem = dst;
+            }
+            DABNN_CUDA_OK(cudaStreamSynchronize(stream));
+        }
+    }
     if (profiling) {
         events.resize(plan.size() + 1);
         for (auto& e : events) DABNN_CUDA_OK(cudaEventCreate(&e));
@@ -940,7 +969,7 @@ int NetImpl::run_plan(int batch) {
                                 o.bias ? static_cast<const float*>(o.bias->dev) : nullptr,
                                 o.a ? static_cast<const float*>(o.a->dev) : nullptr,
                                 o.b ? static_cast<const float*>(o.b->dev) : nullptr, o.relu, f32(o.out), batch, ib.h,
-                                ib.w, ib.c, ob.c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, 1, 1, stream);
+                                ib.w, ib.c, ob.c, o.kh, o.kw, o.pad_h, o.pad_w, o.stride_h, o.stride_w, 1, 1, stream, o.w_rem);
                 break;
             }
             case OpKind::FConvPool: {
@@ -1148,7 +1177,7 @@ extern "C" int dabnn_net_stats(dabnn_net* net, int* kernels_per_run, size_t* are
     for (const auto& o : net->impl.plan) k += o.kind == OpKind::BinConvIm2col ? 2 : 1;
     if (net->impl.status_dev) k += 1;   // the status collector that ends every plan
     if (kernels_per_run) *kernels_per_run = k;
-    if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes + net->impl.arena_bytes_extra + net->impl.expanded_bytes;
+    if (arena_bytes) *arena_bytes = net->impl.arena_bytes + net->impl.weights_bytes + net->impl.arena_bytes_extra + net->impl.expanded_bytes + net->impl.remainders_bytes;
     return DABNN_OK;
 }
 extern "C" int dabnn_net_set_profiling(dabnn_net* net, int on) {
